@@ -1,0 +1,117 @@
+// Host-side plumbing of the cpmk_b200 C-ABI library: thread-local error text, per-device
+// capability check and the (device, stream)-keyed workspace.
+#include <stdarg.h>
+#include <string.h>
+
+#include <map>
+#include <mutex>
+#include <utility>
+
+#include "cpmk_common.cuh"
+
+namespace cpmk {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+static std::mutex g_mutex;
+static std::map<int, DeviceInfo> g_devices;
+static std::map<std::pair<int, cudaStream_t>, Workspace> g_workspaces;
+
+int32_t current_device_info(DeviceInfo *info) {
+    int dev = 0;
+    CPMK_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto it = g_devices.find(dev);
+    if (it == g_devices.end()) {
+        DeviceInfo d;
+        d.device = dev;
+        int major = 0, minor = 0;
+        CPMK_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        CPMK_CUDA_TRY(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev));
+        CPMK_CUDA_TRY(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        CPMK_CUDA_TRY(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        d.arch = major * 10 + minor;
+        it = g_devices.emplace(dev, d).first;
+    }
+    *info = it->second;
+    if (info->arch / 10 != 10) {
+        set_error("cpmk_b200 kernels are built for sm_100a only; device %d is compute capability %d.%d",
+                  dev, info->arch / 10, info->arch % 10);
+        return CPMK_EARCH;
+    }
+    return CPMK_OK;
+}
+
+int32_t get_workspace(cudaStream_t stream, Workspace *ws) {
+    int dev = 0;
+    CPMK_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto key = std::make_pair(dev, stream);
+    auto it = g_workspaces.find(key);
+    if (it == g_workspaces.end()) {
+        if (g_workspaces.size() >= 64) {
+            set_error("more than 64 (device, stream) pairs asked for a cpmk workspace");
+            return CPMK_ENOMEM;
+        }
+        Workspace w;
+        void *p = nullptr;
+        cudaError_t e = cudaMalloc(&p, Workspace::kBytes);
+        if (e != cudaSuccess) {
+            set_error("workspace allocation of %zu bytes failed: %s", Workspace::kBytes, cudaGetErrorString(e));
+            return CPMK_ENOMEM;
+        }
+        w.base = static_cast<char *>(p);
+        // status words and tickets start at zero; kernels leave the tickets at zero when they finish
+        CPMK_CUDA_TRY(cudaMemset(w.base, 0, Workspace::kScratchOffset));
+        it = g_workspaces.emplace(key, w).first;
+    }
+    *ws = it->second;
+    return CPMK_OK;
+}
+
+}  // namespace cpmk
+
+extern "C" {
+
+int32_t cpmk_abi_version(void) { return CPMK_ABI_VERSION; }
+
+const char *cpmk_last_error(void) { return cpmk::g_error; }
+
+int32_t cpmk_check_device(int32_t *arch_out) {
+    cpmk::DeviceInfo info;
+    int32_t rc = cpmk::current_device_info(&info);
+    if (arch_out) *arch_out = info.arch;
+    return rc;
+}
+
+int32_t cpmk_read_status(uint32_t *status_out) {
+    if (!status_out) {
+        cpmk::set_error("status_out is null");
+        return CPMK_EINVAL;
+    }
+    int dev = 0;
+    CPMK_CUDA_TRY(cudaGetDevice(&dev));
+    CPMK_CUDA_TRY(cudaDeviceSynchronize());
+    uint32_t worst = 0;
+    std::lock_guard<std::mutex> lock(cpmk::g_mutex);
+    for (auto &kv : cpmk::g_workspaces) {
+        if (kv.first.first != dev) continue;
+        uint32_t word = 0;
+        CPMK_CUDA_TRY(cudaMemcpy(&word, kv.second.status(), sizeof(word), cudaMemcpyDeviceToHost));
+        if (word != 0) {
+            if (worst == 0) worst = word;
+            CPMK_CUDA_TRY(cudaMemset(kv.second.status(), 0, sizeof(word)));
+        }
+    }
+    *status_out = worst;
+    return CPMK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,592 @@
+// int8 x int8 -> int32 GEMM for sm_100a with the fp16 dequantisation fused into its epilogue.
+//
+// Replaces the cublasLtMatmul call of cpm_kernels/kernels/gemm.py:127-186 (and, when fused, the
+// cu_gemm_scale pass of cuda/gemm.cu:37-57 that follows it in cpm_kernels/torch/gemm.py:40-64).
+//
+// Two kernels:
+//   * gemm_i8_tc_kernel  -- tcgen05.mma kind::i8, accumulators in tensor memory, operands staged in
+//     shared memory by TMA through a 4-stage mbarrier pipeline, one persistent CTA per SM with
+//     warp-specialised roles (TMA producer / MMA issuer / 4 epilogue warps) and two accumulator
+//     buffers so that the epilogue of tile i overlaps the main loop of tile i+1.  It handles the
+//     layout in which both operands are contiguous along k (aT && !bT: the nn.Linear case).
+//   * gemm_i8_simt_kernel -- dp4a, any layout, any size that the interface admits.
+//
+// Every device-side wait is bounded: when one runs out the CTA records a code in the status word,
+// raises its abort flag, lets copies in flight land, frees its tensor memory and returns.
+#include <cuda.h>
+#include <stdlib.h>
+
+#include <mutex>
+
+#include "cpmk_common.cuh"
+
+namespace cpmk {
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// tile configuration of the tensor-core kernel
+// ------------------------------------------------------------------------------------------------
+constexpr int kBM = 128;                 // output rows per tile   (UMMA M; TMEM lanes)
+constexpr int kBN = 256;                 // output cols per tile   (UMMA N; TMEM columns per accumulator)
+constexpr int kBK = 128;                 // int8 elements (= bytes) of k per stage: one 128-byte swizzle row
+constexpr int kUmmaK = 32;               // k per tcgen05.mma kind::i8
+constexpr int kStages = 4;
+constexpr int kPBytes = kBM * kBK;       // 16 KiB
+constexpr int kQBytes = kBN * kBK;       // 32 KiB
+constexpr int kStageBytes = kPBytes + kQBytes;
+constexpr int kTmemCols = 512;           // two 256-column accumulators
+constexpr int kTcThreads = 192;          // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int kBarrierBytes = 256;
+constexpr int kTcSmemBytes = kStages * kStageBytes + 1024 + kBarrierBytes;
+
+constexpr uint32_t kWaitLimitNs = 2000000000u;   // a wait longer than 2 s is a failure
+
+// status codes written to the status word (first failure wins)
+constexpr uint32_t kErrProducerWait = 0x101;
+constexpr uint32_t kErrMmaWaitFull = 0x102;
+constexpr uint32_t kErrMmaWaitTmem = 0x103;
+constexpr uint32_t kErrEpilogueWait = 0x104;
+
+struct GemmParams {
+    int32_t R, C, K;              // out is (batch, R, C); reduction length K
+    int32_t batch;
+    int32_t p_batched, q_batched; // 0: operand has a single batch that is broadcast
+    int32_t tiles_r, tiles_c, num_kb;
+    int32_t total_tiles;
+    void *out;
+    const __half *scale_r;        // (bcast_r ? 1 : batch, R)   multiplies first
+    const __half *scale_c;        // (bcast_c ? 1 : batch, C)
+    int32_t bcast_r, bcast_c;
+    uint32_t *status;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Waits for the phase of `bar` with the given parity.  Returns false when the CTA is aborting or the
+// wait exceeded its limit (in which case it raises the abort flag and records `code`).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint32_t *status, uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = 0;
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 0xffu) == 0) {
+            if (*abort_flag) return false;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) {
+                *abort_flag = 1u;
+                atomicCAS(status, 0u, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int32_t c0, int32_t c1, int32_t c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]^T, int8 operands, int32 accumulator
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives on `bar` once all tcgen05.mma issued so far by this thread have completed
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a k-major tile whose rows are 128 bytes, stored with the 128-byte
+// swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): 8-row groups are 1024 bytes apart.
+//   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4 (unused here: 1)
+//   bits [32,46) stride byte offset >> 4   bits [46,48) descriptor version (1 on sm_100)
+//   bits [61,64) layout type (2 = 128-byte swizzle)
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)1u << 16;
+    d |= (uint64_t)(1024u >> 4) << 32;
+    d |= (uint64_t)1u << 46;
+    d |= (uint64_t)2u << 61;
+    return d;
+}
+
+// Instruction descriptor of tcgen05.mma kind::i8: int32 accumulator (bits 4-5 = 2), signed 8-bit A and B
+// (bits 7-9 = 1, 10-12 = 1), both k-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+constexpr uint32_t kInstrDesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+template <bool DEQUANT>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, const GemmParams prm) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars_base = tiles_base + kStages * kStageBytes;
+    // barrier block: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], then tmem slot, abort flag
+    const uint32_t full_bar = bars_base;
+    const uint32_t empty_bar = bars_base + 8 * kStages;
+    const uint32_t tmem_full_bar = bars_base + 16 * kStages;
+    const uint32_t tmem_empty_bar = tmem_full_bar + 16;
+    uint8_t *bars_generic = smem_raw + (bars_base - smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars_generic + 16 * kStages + 32);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tmem_full_bar + 8 * a, 1);
+            mbar_init(tmem_empty_bar + 8 * a, 4);      // one arrival per epilogue warp
+        }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles_per_batch = prm.tiles_r * prm.tiles_c;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; alive && tile < prm.total_tiles; tile += gridDim.x) {
+                const int b = tile / tiles_per_batch;
+                const int rem = tile - b * tiles_per_batch;
+                const int c_blk = rem / prm.tiles_r, r_blk = rem - c_blk * prm.tiles_r;
+                for (int kb = 0; kb < prm.num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, prm.status, kErrProducerWait)) { alive = false; break; }
+                    const uint32_t p_dst = tiles_base + stage * kStageBytes;
+                    mbar_expect_tx(full_bar + 8 * stage, kStageBytes);
+                    tma_load_3d(p_dst, &tmap_p, kb * kBK, r_blk * kBM, prm.p_batched ? b : 0, full_bar + 8 * stage);
+                    tma_load_3d(p_dst + kPBytes, &tmap_q, kb * kBK, c_blk * kBN, prm.q_batched ? b : 0, full_bar + 8 * stage);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; alive && tile < prm.total_tiles; tile += gridDim.x) {
+                if (!mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, prm.status, kErrMmaWaitTmem)) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * kBN;
+                for (int kb = 0; kb < prm.num_kb; ++kb) {
+                    if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, prm.status, kErrMmaWaitFull)) { alive = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t p_src = tiles_base + stage * kStageBytes;
+                    const uint64_t p_desc = make_kmajor_sw128_desc(p_src);
+                    const uint64_t q_desc = make_kmajor_sw128_desc(p_src + kPBytes);
+#pragma unroll
+                    for (int j = 0; j < kBK / kUmmaK; ++j) {
+                        // advancing k inside the swizzle row: +32 bytes = +2 in the (address >> 4) field
+                        umma_i8(d_tmem, p_desc + (uint64_t)(2 * j), q_desc + (uint64_t)(2 * j), kInstrDesc, (kb | j) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar + 8 * stage);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!alive) break;
+                umma_commit(tmem_full_bar + 8 * acc);
+                acc ^= 1u;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ---------------- epilogue: TMEM -> registers -> (dequantise) -> global ----------------
+        const int quarter = warp & 3;                       // TMEM lanes [32*quarter, 32*quarter + 32)
+        uint32_t acc = 0, acc_phase = 0;
+        for (int tile = blockIdx.x; tile < prm.total_tiles; tile += gridDim.x) {
+            const int b = tile / tiles_per_batch;
+            const int rem = tile - b * tiles_per_batch;
+            const int c_blk = rem / prm.tiles_r, r_blk = rem - c_blk * prm.tiles_r;
+            if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, prm.status, kErrEpilogueWait)) break;
+            tcgen05_fence_after();
+            const int row = r_blk * kBM + quarter * 32 + lane;
+            const bool row_ok = row < prm.R;
+            const int64_t out_row = ((int64_t)b * prm.R + (row_ok ? row : 0)) * prm.C;
+            float sr = 0.f;
+            if (DEQUANT && row_ok) sr = __half2float(__ldg(prm.scale_r + (prm.bcast_r ? 0 : (int64_t)b * prm.R) + row));
+            const __half *sc = DEQUANT ? prm.scale_c + (prm.bcast_c ? 0 : (int64_t)b * prm.C) : nullptr;
+#pragma unroll 1
+            for (int chunk = 0; chunk < kBN / 32; ++chunk) {
+                const int col0 = c_blk * kBN + chunk * 32;
+                if (col0 >= prm.C) break;                    // uniform across the warp
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN + chunk * 32, v);
+                tmem_ld_wait();
+                if (!row_ok) continue;
+                if (DEQUANT) {
+                    __half *dst = static_cast<__half *>(prm.out) + out_row + col0;
+                    if ((prm.C & 7) == 0) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if (col0 + g * 8 < prm.C) {
+                                const uint4 s8 = __ldg(reinterpret_cast<const uint4 *>(sc + col0 + g * 8));
+                                const __half2 *sh = reinterpret_cast<const __half2 *>(&s8);
+                                uint4 o;
+                                uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float2 s2 = __half22float2(sh[e]);
+                                    const float a0 = __fmul_rn(__fmul_rn((float)(int32_t)v[g * 8 + 2 * e], sr), s2.x);
+                                    const float a1 = __fmul_rn(__fmul_rn((float)(int32_t)v[g * 8 + 2 * e + 1], sr), s2.y);
+                                    ow[e] = pack_half2(a0, a1);
+                                }
+                                *reinterpret_cast<uint4 *>(dst + g * 8) = o;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            if (col0 + e < prm.C) {
+                                const float a = __fmul_rn(__fmul_rn((float)(int32_t)v[e], sr), __half2float(__ldg(sc + col0 + e)));
+                                dst[e] = __float2half_rn(a);
+                            }
+                        }
+                    }
+                } else {
+                    int32_t *dst = static_cast<int32_t *>(prm.out) + out_row + col0;
+                    if ((prm.C & 3) == 0) {
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) {
+                            if (col0 + g * 4 < prm.C)
+                                *reinterpret_cast<uint4 *>(dst + g * 4) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e)
+                            if (col0 + e < prm.C) dst[e] = (int32_t)v[e];
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty_bar + 8 * acc);
+            acc ^= 1u;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tcgen05_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // give copies and MMAs that were in flight when the CTA gave up time to land before the
+        // shared and tensor memory they target are released
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Generic kernel: out[b, j, i] = sum_l Aop[b, l, i] * Bop[b, j, l] for any layout.
+// 64 x 64 output tile per 256-thread block, 4 x 4 outputs per thread, k in chunks of 32 packed four to a
+// word so that the inner product is dp4a.
+// ------------------------------------------------------------------------------------------------
+constexpr int kSimtTile = 64;
+constexpr int kSimtK = 32;
+
+template <bool DEQUANT>
+__global__ void __launch_bounds__(256) gemm_i8_simt_kernel(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int aT, int bT,
+                                                           const int8_t *__restrict__ A, const int8_t *__restrict__ B, void *__restrict__ out,
+                                                           const __half *__restrict__ scale_x, const __half *__restrict__ scale_y, int bx, int by) {
+    __shared__ int32_t As[kSimtK / 4][kSimtTile + 4];   // [k4][i]
+    __shared__ int32_t Bs[kSimtK / 4][kSimtTile + 4];   // [k4][j]
+    const int b = blockIdx.z;
+    const int i0 = blockIdx.x * kSimtTile, j0 = blockIdx.y * kSimtTile;
+    const int8_t *a = A + (batchA == 1 ? 0 : (int64_t)b * m * k);
+    const int8_t *bb = B + (batchB == 1 ? 0 : (int64_t)b * n * k);
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+
+    int32_t acc[4][4];
+#pragma unroll
+    for (int y = 0; y < 4; ++y)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) acc[y][x] = 0;
+
+    for (int l0 = 0; l0 < k; l0 += kSimtK) {
+        // 8 x 64 words per operand, 2 per thread
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+            const int idx = threadIdx.x + w * 256;
+            const int kk = idx >> 6, c = idx & 63;
+            const int l = l0 + kk * 4;
+            int32_t wa = 0, wb = 0;
+            const int i = i0 + c, j = j0 + c;
+            if (i < m && l < k) {                            // k % 4 == 0: a word is wholly inside or outside
+                if (aT) {
+                    wa = *reinterpret_cast<const int32_t *>(a + (int64_t)i * k + l);
+                } else {
+                    const uint32_t e0 = (uint8_t)a[(int64_t)l * m + i], e1 = (uint8_t)a[(int64_t)(l + 1) * m + i];
+                    const uint32_t e2 = (uint8_t)a[(int64_t)(l + 2) * m + i], e3 = (uint8_t)a[(int64_t)(l + 3) * m + i];
+                    wa = (int32_t)(e0 | (e1 << 8) | (e2 << 16) | (e3 << 24));
+                }
+            }
+            if (j < n && l < k) {
+                if (!bT) {
+                    wb = *reinterpret_cast<const int32_t *>(bb + (int64_t)j * k + l);
+                } else {
+                    const uint32_t e0 = (uint8_t)bb[(int64_t)l * n + j], e1 = (uint8_t)bb[(int64_t)(l + 1) * n + j];
+                    const uint32_t e2 = (uint8_t)bb[(int64_t)(l + 2) * n + j], e3 = (uint8_t)bb[(int64_t)(l + 3) * n + j];
+                    wb = (int32_t)(e0 | (e1 << 8) | (e2 << 16) | (e3 << 24));
+                }
+            }
+            As[kk][c] = wa;
+            Bs[kk][c] = wb;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kSimtK / 4; ++kk) {
+            int32_t av[4], bv[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) av[x] = As[kk][tx * 4 + x];
+#pragma unroll
+            for (int y = 0; y < 4; ++y) bv[y] = Bs[kk][ty * 4 + y];
+#pragma unroll
+            for (int y = 0; y < 4; ++y)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) acc[y][x] = __dp4a(av[x], bv[y], acc[y][x]);
+        }
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int y = 0; y < 4; ++y) {
+        const int j = j0 + ty * 4 + y;
+        if (j >= n) continue;
+        float sx = 0.f;
+        if (DEQUANT) sx = __half2float(scale_x[(bx ? 0 : (int64_t)b * n) + j]);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int i = i0 + tx * 4 + x;
+            if (i >= m) continue;
+            const int64_t o = ((int64_t)b * n + j) * m + i;
+            if (DEQUANT) {
+                const float v = __fmul_rn(__fmul_rn((float)acc[y][x], sx), __half2float(scale_y[(by ? 0 : (int64_t)b * m) + i]));
+                static_cast<__half *>(out)[o] = __float2half_rn(v);
+            } else {
+                static_cast<int32_t *>(out)[o] = acc[y][x];
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        (void)cudaGetLastError();
+    });
+    return fn;
+}
+
+// int8 operand (batch, rows, k) with k contiguous, as a 3-d tensor map whose box is box_rows x 128 bytes.
+bool encode_operand(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int32_t box_rows) {
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)batch};
+    const cuuint64_t strides[2] = {(cuuint64_t)k, (cuuint64_t)rows * (cuuint64_t)k};
+    const cuuint32_t box[3] = {(cuuint32_t)kBK, (cuuint32_t)box_rows, 1u};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+thread_local int32_t g_last_path = 0;
+
+bool force_generic() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char *e = getenv("CPMK_FORCE_GENERIC_GEMM");
+        cached = (e && e[0] && e[0] != '0') ? 1 : 0;
+    }
+    return cached == 1;
+}
+
+template <bool DEQUANT>
+int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int aT, int bT, const void *A, const void *B,
+                    const void *scale_x, const void *scale_y, int bx, int by, void *out, cudaStream_t stream) {
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    CPMK_REQUIRE(m >= 0 && n >= 0 && k >= 0 && batchA >= 1 && batchB >= 1, "bad size: m=%d k=%d n=%d batchA=%d batchB=%d", m, k, n, batchA, batchB);
+    // kernels/gemm.py:139-140
+    CPMK_REQUIRE(m % 4 == 0 && n % 4 == 0 && k % 4 == 0, "m, n, k must be multiples of 4 (m=%d k=%d n=%d)", m, k, n);
+    CPMK_REQUIRE(batchA == batchB || batchA == 1 || batchB == 1, "batch sizes must match or be 1 (batchA=%d batchB=%d)", batchA, batchB);
+    const int32_t batch = batchA > batchB ? batchA : batchB;
+    CPMK_REQUIRE(batch <= 65535, "batch %d exceeds 65535", batch);
+    if (m == 0 || n == 0) return CPMK_OK;
+    CPMK_REQUIRE(out, "null output pointer");
+    const size_t out_elem = DEQUANT ? sizeof(__half) : sizeof(int32_t);
+    if (k == 0) {
+        CPMK_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)batch * n * m * out_elem, stream));
+        return CPMK_OK;
+    }
+    CPMK_REQUIRE(A && B, "null operand pointer");
+    CPMK_REQUIRE((reinterpret_cast<uintptr_t>(A) & 3u) == 0 && (reinterpret_cast<uintptr_t>(B) & 3u) == 0, "operands must be 4-byte aligned");
+    if (DEQUANT) CPMK_REQUIRE(scale_x && scale_y, "null scale pointer");
+
+    // tensor-core path: both operands contiguous along k, TMA-compatible strides and addresses
+    const int64_t tiles_r = (n + kBM - 1) / kBM, tiles_c = (m + kBN - 1) / kBN;
+    const int64_t total_tiles = tiles_r * tiles_c * batch;
+    bool tc = aT && !bT && !force_generic() && k % 16 == 0 && aligned16(A) && aligned16(B) && aligned16(out) &&
+              total_tiles < (int64_t(1) << 31) && (!DEQUANT || aligned16(scale_y)) && info.max_smem_optin >= kTcSmemBytes;
+    CUtensorMap tmap_p, tmap_q;
+    if (tc) {
+        // rows of the output come from B (n x k), columns from A (m x k)
+        tc = encode_operand(&tmap_p, B, n, k, batchB, kBM) && encode_operand(&tmap_q, A, m, k, batchA, kBN);
+    }
+    if (tc) {
+        static std::once_flag attr_once[64];
+        static cudaError_t attr_err[64];
+        const int dev = info.device & 63;
+        std::call_once(attr_once[dev], [dev] {
+            cudaError_t e1 = cudaFuncSetAttribute(gemm_i8_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
+            cudaError_t e2 = cudaFuncSetAttribute(gemm_i8_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
+            attr_err[dev] = e1 != cudaSuccess ? e1 : e2;
+        });
+        if (attr_err[dev] != cudaSuccess) {
+            set_error("cudaFuncSetAttribute(max dynamic shared memory) failed: %s", cudaGetErrorString(attr_err[dev]));
+            return CPMK_ECUDA;
+        }
+        Workspace ws;
+        rc = get_workspace(stream, &ws);
+        if (rc) return rc;
+        GemmParams prm;
+        prm.R = n; prm.C = m; prm.K = k; prm.batch = batch;
+        prm.p_batched = batchB > 1; prm.q_batched = batchA > 1;
+        prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.num_kb = (k + kBK - 1) / kBK;
+        prm.total_tiles = (int32_t)total_tiles;
+        prm.out = out;
+        prm.scale_r = static_cast<const __half *>(scale_x); prm.scale_c = static_cast<const __half *>(scale_y);
+        prm.bcast_r = bx; prm.bcast_c = by;
+        prm.status = ws.status();
+        const int grid = (int)(total_tiles < info.sm_count ? total_tiles : info.sm_count);
+        gemm_i8_tc_kernel<DEQUANT><<<grid, kTcThreads, kTcSmemBytes, stream>>>(tmap_p, tmap_q, prm);
+        CPMK_LAUNCH_CHECK();
+        g_last_path = 1;
+        return CPMK_OK;
+    }
+    const dim3 grid((m + kSimtTile - 1) / kSimtTile, (n + kSimtTile - 1) / kSimtTile, batch);
+    CPMK_REQUIRE(grid.y <= 65535, "n = %d is too large for the generic kernel", n);
+    gemm_i8_simt_kernel<DEQUANT><<<grid, 256, 0, stream>>>(m, k, n, batchA, batchB, aT, bT, static_cast<const int8_t *>(A),
+                                                          static_cast<const int8_t *>(B), out, static_cast<const __half *>(scale_x),
+                                                          static_cast<const __half *>(scale_y), bx, by);
+    CPMK_LAUNCH_CHECK();
+    g_last_path = 2;
+    return CPMK_OK;
+}
+
+}  // namespace
+}  // namespace cpmk
+
+using namespace cpmk;
+
+extern "C" {
+
+int32_t cpmk_gemm_int8(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT, const void *A, const void *B,
+                       void *out, cpmk_stream_t stream) {
+    return launch_gemm<false>(m, k, n, batchA, batchB, aT != 0, bT != 0, A, B, nullptr, nullptr, 0, 0, out, as_stream(stream));
+}
+
+int32_t cpmk_gemm_int8_dequant(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT, const void *A,
+                               const void *B, const void *scale_x, const void *scale_y, int32_t broad_cast_x, int32_t broad_cast_y, void *out,
+                               cpmk_stream_t stream) {
+    return launch_gemm<true>(m, k, n, batchA, batchB, aT != 0, bT != 0, A, B, scale_x, scale_y, broad_cast_x != 0, broad_cast_y != 0, out,
+                             as_stream(stream));
+}
+
+int32_t cpmk_last_gemm_path(void) { return g_last_path; }
+
+}  // extern "C"

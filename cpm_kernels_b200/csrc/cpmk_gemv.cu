@@ -1,0 +1,407 @@
+// fp16 decode GEMV for sm_100a: HBM-bound streaming of the weight matrix with 128-bit loads and fp32
+// accumulation.
+//
+// Replaces cuda/gemv.cu:57-164 of the reference (one block per output element with half2 accumulation;
+// 32x32 blocks reading 64-byte row segments for the transposed form) and the cublasLt n=1 GEMMs of
+// cpm_kernels/kernels/gemv.py:82-262.
+#include "cpmk_common.cuh"
+
+namespace cpmk {
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kWarps = kBlock / 32;
+
+__device__ __forceinline__ float dot8(const uint4 &a, const uint4 &b, float acc) {
+    const __half2 *x = reinterpret_cast<const __half2 *>(&a);
+    const __half2 *y = reinterpret_cast<const __half2 *>(&b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 fx = __half22float2(x[i]);
+        const float2 fy = __half22float2(y[i]);
+        acc = fmaf(fx.x, fy.x, acc);
+        acc = fmaf(fx.y, fy.y, acc);
+    }
+    return acc;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ------------------------------------------------------------------------------------------------
+// out[b, o] = sum_i mat[b?, o, i] * vec[b, i]: one warp per matrix row, NB vectors per pass.
+// SHARED = false: mat is (batch, dim_out, dim_in) and NB == 1 (gemv_fp16);
+// SHARED = true : mat is (dim_out, dim_in), read once for NB vectors (gemv_broadcast_mat_fp16).
+// ------------------------------------------------------------------------------------------------
+template <int NB, bool SHARED>
+__global__ void __launch_bounds__(kBlock) gemv_rows_kernel(int32_t batch, int32_t dim_out, int32_t dim_in, int32_t batch_begin,
+                                                           const __half *__restrict__ mat, const __half *__restrict__ vec,
+                                                           __half *__restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp_id = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const int64_t total_rows = SHARED ? (int64_t)dim_out : (int64_t)batch * dim_out;
+    if (warp_id >= total_rows) return;
+    const int nvec = dim_in >> 3;
+    const uint4 *row = reinterpret_cast<const uint4 *>(mat + warp_id * (int64_t)dim_in);
+    const int b0 = SHARED ? batch_begin : (int)(warp_id / dim_out);
+    const int o = SHARED ? (int)warp_id : (int)(warp_id - (int64_t)b0 * dim_out);
+
+    float acc[NB];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) acc[j] = 0.f;
+
+    int i = lane;
+    // four independent 128-bit loads in flight per lane
+    for (; i + 96 < nvec; i += 128) {
+        uint4 w[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) w[u] = __ldcs(row + i + 32 * u);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const uint4 x = __ldg(reinterpret_cast<const uint4 *>(vec + (int64_t)(b0 + j) * dim_in) + i + 32 * u);
+                acc[j] = dot8(w[u], x, acc[j]);
+            }
+        }
+    }
+    for (; i < nvec; i += 32) {
+        const uint4 w = __ldcs(row + i);
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            const uint4 x = __ldg(reinterpret_cast<const uint4 *>(vec + (int64_t)(b0 + j) * dim_in) + i);
+            acc[j] = dot8(w, x, acc[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+        const float v = warp_sum(acc[j]);
+        if (lane == 0) out[(int64_t)(b0 + j) * dim_out + o] = __float2half_rn(v);
+    }
+}
+
+// Any dim_in / alignment: one warp per row, scalar loads.
+__global__ void __launch_bounds__(kBlock) gemv_rows_generic_kernel(int32_t batch, int32_t dim_out, int32_t dim_in, int shared,
+                                                                   const __half *__restrict__ mat, const __half *__restrict__ vec,
+                                                                   __half *__restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp_id = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+    if (warp_id >= (int64_t)batch * dim_out) return;
+    const int b = (int)(warp_id / dim_out);
+    const int o = (int)(warp_id - (int64_t)b * dim_out);
+    const __half *row = mat + (shared ? (int64_t)o : warp_id) * dim_in;
+    const __half *x = vec + (int64_t)b * dim_in;
+    float acc = 0.f;
+    for (int i = lane; i < dim_in; i += 32) acc = fmaf(__half2float(row[i]), __half2float(x[i]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) out[warp_id] = __float2half_rn(acc);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Transposed form: out[b, o] = sum_i mat[b, i, o] * vec[b, i], mat (batch, dim_in, dim_out).
+// A block owns a strip of 256 columns (32 lanes x 8 halves) and a chunk of rows; its 8 warps take
+// rows w, w+8, ...  Chunks are combined through fp32 partials in scratch; the block that takes the
+// last ticket of a strip adds them in chunk order (deterministic) and writes the fp16 result.
+// ------------------------------------------------------------------------------------------------
+constexpr int kTStripCols = 256;
+
+__global__ void __launch_bounds__(kBlock) gemv_transpose_kernel(int32_t dim_out, int32_t dim_in, int32_t rows_per_split, int32_t splits,
+                                                                const __half *__restrict__ mat, const __half *__restrict__ vec,
+                                                                __half *__restrict__ out, float *__restrict__ partial,
+                                                                uint32_t *__restrict__ tickets) {
+    __shared__ float red[kWarps][kTStripCols];
+    __shared__ uint32_t is_last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int strip = blockIdx.x, split = blockIdx.y, b = blockIdx.z, batch = gridDim.z;
+    const int col = strip * kTStripCols + lane * 8;
+    const int r_begin = split * rows_per_split;
+    const int r_end = min(dim_in, r_begin + rows_per_split);
+    const __half *base = mat + (int64_t)b * dim_in * dim_out;
+    const __half *x = vec + (int64_t)b * dim_in;
+
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (col < dim_out) {
+        int r = r_begin + warp;
+        for (; r + 3 * kWarps < r_end; r += 4 * kWarps) {
+            uint4 w[4];
+            float xv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                w[u] = __ldcs(reinterpret_cast<const uint4 *>(base + (int64_t)(r + u * kWarps) * dim_out + col));
+                xv[u] = __half2float(__ldg(x + r + u * kWarps));
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const __half2 *h = reinterpret_cast<const __half2 *>(&w[u]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(h[j]);
+                    acc[2 * j] = fmaf(f.x, xv[u], acc[2 * j]);
+                    acc[2 * j + 1] = fmaf(f.y, xv[u], acc[2 * j + 1]);
+                }
+            }
+        }
+        for (; r < r_end; r += kWarps) {
+            const uint4 w = __ldcs(reinterpret_cast<const uint4 *>(base + (int64_t)r * dim_out + col));
+            const float xv = __half2float(__ldg(x + r));
+            const __half2 *h = reinterpret_cast<const __half2 *>(&w);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                acc[2 * j] = fmaf(f.x, xv, acc[2 * j]);
+                acc[2 * j + 1] = fmaf(f.y, xv, acc[2 * j + 1]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[warp][lane * 8 + j] = acc[j];
+    __syncthreads();
+    const int c = strip * kTStripCols + threadIdx.x;
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) total += red[w][threadIdx.x];
+
+    if (splits == 1) {
+        if (c < dim_out) out[(int64_t)b * dim_out + c] = __float2half_rn(total);
+        return;
+    }
+    // partial[(split * batch + b) * dim_out + c]
+    if (c < dim_out) partial[((int64_t)split * batch + b) * dim_out + c] = total;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t t = atomicAdd(&tickets[b * gridDim.x + strip], 1u);
+        is_last = (t == (uint32_t)splits - 1u);
+        if (is_last) tickets[b * gridDim.x + strip] = 0u;          // leave the ticket at zero for the next call
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (c < dim_out) {
+        float sum = 0.f;
+        for (int s = 0; s < splits; ++s) sum += __ldcg(partial + ((int64_t)s * batch + b) * dim_out + c);
+        out[(int64_t)b * dim_out + c] = __float2half_rn(sum);
+    }
+}
+
+__global__ void __launch_bounds__(kBlock) gemv_transpose_generic_kernel(int32_t batch, int32_t dim_out, int32_t dim_in,
+                                                                        const __half *__restrict__ mat, const __half *__restrict__ vec,
+                                                                        __half *__restrict__ out) {
+    const int64_t idx = (int64_t)blockIdx.x * kBlock + threadIdx.x;
+    if (idx >= (int64_t)batch * dim_out) return;
+    const int b = (int)(idx / dim_out), o = (int)(idx % dim_out);
+    const __half *base = mat + (int64_t)b * dim_in * dim_out + o;
+    const __half *x = vec + (int64_t)b * dim_in;
+    float acc = 0.f;
+    for (int i = 0; i < dim_in; ++i) acc = fmaf(__half2float(base[(int64_t)i * dim_out]), __half2float(x[i]), acc);
+    out[idx] = __float2half_rn(acc);
+}
+
+// ------------------------------------------------------------------------------------------------
+// int8 shared-matrix GEMV: out[b,o] = half(((float)sum_i mat[o,i]*vec[b,i]) * scale_vec[b] * scale_mat[o])
+// One warp per matrix row, dp4a on 128-bit loads, NB vectors per pass.
+// ------------------------------------------------------------------------------------------------
+template <int NB>
+__global__ void __launch_bounds__(kBlock) gemv_int8_kernel(int32_t dim_out, int32_t dim_in, int32_t batch_begin,
+                                                           const __half *__restrict__ scale_mat, const int8_t *__restrict__ mat,
+                                                           const __half *__restrict__ scale_vec, const int8_t *__restrict__ vec,
+                                                           __half *__restrict__ out, int vec16) {
+    const int lane = threadIdx.x & 31;
+    const int64_t o = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+    if (o >= dim_out) return;
+    int32_t acc[NB];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) acc[j] = 0;
+    if (vec16) {
+        const int nvec = dim_in >> 4;
+        const int4 *row = reinterpret_cast<const int4 *>(mat + o * (int64_t)dim_in);
+        for (int i = lane; i < nvec; i += 32) {
+            const int4 w = __ldcs(row + i);
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const int4 x = __ldg(reinterpret_cast<const int4 *>(vec + (int64_t)(batch_begin + j) * dim_in) + i);
+                acc[j] = __dp4a(w.x, x.x, acc[j]);
+                acc[j] = __dp4a(w.y, x.y, acc[j]);
+                acc[j] = __dp4a(w.z, x.z, acc[j]);
+                acc[j] = __dp4a(w.w, x.w, acc[j]);
+            }
+        }
+    } else {
+        const int nword = dim_in >> 2;
+        const int *row = reinterpret_cast<const int *>(mat + o * (int64_t)dim_in);
+        for (int i = lane; i < nword; i += 32) {
+            const int w = __ldg(row + i);
+#pragma unroll
+            for (int j = 0; j < NB; ++j)
+                acc[j] = __dp4a(w, __ldg(reinterpret_cast<const int *>(vec + (int64_t)(batch_begin + j) * dim_in) + i), acc[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+        int32_t v = acc[j];
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+        if (lane == 0) {
+            const float f = __fmul_rn(__fmul_rn((float)v, __half2float(scale_vec[batch_begin + j])), __half2float(scale_mat[o]));
+            out[(int64_t)(batch_begin + j) * dim_out + o] = __float2half_rn(f);
+        }
+    }
+}
+
+int32_t check_gemv(int32_t batch, int32_t dim_out, int32_t dim_in) {
+    CPMK_REQUIRE(batch >= 0 && dim_out >= 0 && dim_in >= 0, "negative size: batch=%d dim_out=%d dim_in=%d", batch, dim_out, dim_in);
+    return CPMK_OK;
+}
+
+template <bool SHARED>
+int32_t launch_gemv_rows(int32_t batch, int32_t dim_out, int32_t dim_in, const void *mat, const void *vec, void *out, cudaStream_t stream) {
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    rc = check_gemv(batch, dim_out, dim_in);
+    if (rc) return rc;
+    if ((int64_t)batch * dim_out == 0) return CPMK_OK;
+    CPMK_REQUIRE(mat && vec && out, "null tensor pointer");
+    const __half *w = static_cast<const __half *>(mat);
+    const __half *x = static_cast<const __half *>(vec);
+    __half *y = static_cast<__half *>(out);
+    const bool vec_ok = dim_in % 8 == 0 && aligned16(mat) && aligned16(vec);
+    if (!vec_ok) {
+        const int64_t blocks = ceil_div64((int64_t)batch * dim_out, kWarps);
+        gemv_rows_generic_kernel<<<(unsigned)blocks, kBlock, 0, stream>>>(batch, dim_out, dim_in, SHARED ? 1 : 0, w, x, y);
+        CPMK_LAUNCH_CHECK();
+        return CPMK_OK;
+    }
+    if (!SHARED) {
+        const int64_t blocks = ceil_div64((int64_t)batch * dim_out, kWarps);
+        CPMK_REQUIRE(blocks < (int64_t(1) << 31), "too many rows");
+        gemv_rows_kernel<1, false><<<(unsigned)blocks, kBlock, 0, stream>>>(batch, dim_out, dim_in, 0, w, x, y);
+        CPMK_LAUNCH_CHECK();
+        return CPMK_OK;
+    }
+    const unsigned blocks = (unsigned)ceil_div64(dim_out, kWarps);
+    int b = 0;
+    while (b < batch) {
+        const int left = batch - b;
+        if (left >= 8) { gemv_rows_kernel<8, true><<<blocks, kBlock, 0, stream>>>(batch, dim_out, dim_in, b, w, x, y); b += 8; }
+        else if (left >= 4) { gemv_rows_kernel<4, true><<<blocks, kBlock, 0, stream>>>(batch, dim_out, dim_in, b, w, x, y); b += 4; }
+        else if (left >= 2) { gemv_rows_kernel<2, true><<<blocks, kBlock, 0, stream>>>(batch, dim_out, dim_in, b, w, x, y); b += 2; }
+        else { gemv_rows_kernel<1, true><<<blocks, kBlock, 0, stream>>>(batch, dim_out, dim_in, b, w, x, y); b += 1; }
+        CPMK_LAUNCH_CHECK();
+    }
+    return CPMK_OK;
+}
+
+}  // namespace
+}  // namespace cpmk
+
+using namespace cpmk;
+
+extern "C" {
+
+int32_t cpmk_gemv_fp16(int32_t batch, int32_t dim_out, int32_t dim_in, const void *mat, const void *vec, void *out, cpmk_stream_t stream) {
+    return launch_gemv_rows<false>(batch, dim_out, dim_in, mat, vec, out, as_stream(stream));
+}
+
+int32_t cpmk_gemv_broadcast_mat_fp16(int32_t batch, int32_t dim_out, int32_t dim_in, const void *mat, const void *vec, void *out,
+                                     cpmk_stream_t stream) {
+    return launch_gemv_rows<true>(batch, dim_out, dim_in, mat, vec, out, as_stream(stream));
+}
+
+int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in, const void *mat, const void *vec, void *out,
+                                 cpmk_stream_t stream) {
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    rc = check_gemv(batch, dim_out, dim_in);
+    if (rc) return rc;
+    if ((int64_t)batch * dim_out == 0) return CPMK_OK;
+    CPMK_REQUIRE(mat && vec && out, "null tensor pointer");
+    cudaStream_t st = as_stream(stream);
+    const __half *w = static_cast<const __half *>(mat);
+    const __half *x = static_cast<const __half *>(vec);
+    __half *y = static_cast<__half *>(out);
+    if (dim_in == 0) {
+        CPMK_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)batch * dim_out * sizeof(__half), st));
+        return CPMK_OK;
+    }
+    const int strips = (dim_out + kTStripCols - 1) / kTStripCols;
+    const bool vec_ok = dim_out % 8 == 0 && aligned16(mat) && batch <= 65535 &&
+                        (size_t)batch * strips * sizeof(uint32_t) <= Workspace::kTicketBytes;
+    if (!vec_ok) {
+        const int64_t blocks = ceil_div64((int64_t)batch * dim_out, kBlock);
+        gemv_transpose_generic_kernel<<<(unsigned)blocks, kBlock, 0, st>>>(batch, dim_out, dim_in, w, x, y);
+        CPMK_LAUNCH_CHECK();
+        return CPMK_OK;
+    }
+    // enough blocks to keep ~6 per SM streaming; at least 8 rows per warp in a chunk
+    int64_t splits = ((int64_t)info.sm_count * 6) / ((int64_t)strips * batch);
+    const int64_t max_by_rows = (dim_in + 63) / 64;
+    if (splits > max_by_rows) splits = max_by_rows;
+    const int64_t max_by_scratch = (int64_t)(Workspace::kScratchBytes / (sizeof(float) * (size_t)batch * (size_t)dim_out));
+    if (splits > max_by_scratch) splits = max_by_scratch;
+    if (splits > 65535) splits = 65535;
+    if (splits < 1) splits = 1;
+    int rps = (int)((dim_in + splits - 1) / splits);
+    rps = (rps + kWarps - 1) / kWarps * kWarps;
+    const int nsplit = (dim_in + rps - 1) / rps;
+    Workspace ws;
+    ws.base = nullptr;
+    if (nsplit > 1) {
+        rc = get_workspace(st, &ws);
+        if (rc) return rc;
+    }
+    const dim3 grid(strips, nsplit, batch);
+    gemv_transpose_kernel<<<grid, kBlock, 0, st>>>(dim_out, dim_in, rps, nsplit, w, x, y,
+                                                   nsplit > 1 ? reinterpret_cast<float *>(ws.scratch()) : nullptr,
+                                                   nsplit > 1 ? ws.tickets() : nullptr);
+    CPMK_LAUNCH_CHECK();
+    return CPMK_OK;
+}
+
+int32_t cpmk_gemv_calc_scale(int32_t batch, int32_t n, const void *vec, void *out, cpmk_stream_t stream) {
+    return cpmk_gemm_calc_scale(1, batch, n, vec, out, stream);
+}
+
+int32_t cpmk_gemv_round(int32_t batch, int32_t n, const void *vec, const void *scale, void *out, cpmk_stream_t stream) {
+    return cpmk_gemm_round(1, batch, n, vec, scale, out, stream);
+}
+
+int32_t cpmk_gemv_broadcast_mat_int8(int32_t batch, int32_t dim_out, int32_t dim_in, const void *scale_mat, const void *mat,
+                                     const void *scale_vec, const void *vec, void *out, cpmk_stream_t stream) {
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    rc = check_gemv(batch, dim_out, dim_in);
+    if (rc) return rc;
+    if ((int64_t)batch * dim_out == 0) return CPMK_OK;
+    CPMK_REQUIRE(scale_mat && mat && scale_vec && vec && out, "null tensor pointer");
+    // kernels/gemv.py:65
+    CPMK_REQUIRE(dim_in % 4 == 0, "dim_in must be a multiple of 4 (got %d)", dim_in);
+    CPMK_REQUIRE((reinterpret_cast<uintptr_t>(mat) & 3u) == 0 && (reinterpret_cast<uintptr_t>(vec) & 3u) == 0, "int8 tensors must be 4-byte aligned");
+    cudaStream_t st = as_stream(stream);
+    const int vec16 = (dim_in % 16 == 0 && aligned16(mat) && aligned16(vec)) ? 1 : 0;
+    const unsigned blocks = (unsigned)ceil_div64(dim_out, kWarps);
+    const __half *sm = static_cast<const __half *>(scale_mat);
+    const __half *sv = static_cast<const __half *>(scale_vec);
+    const int8_t *w = static_cast<const int8_t *>(mat);
+    const int8_t *x = static_cast<const int8_t *>(vec);
+    __half *y = static_cast<__half *>(out);
+    int b = 0;
+    while (b < batch) {
+        const int left = batch - b;
+        if (left >= 8) { gemv_int8_kernel<8><<<blocks, kBlock, 0, st>>>(dim_out, dim_in, b, sm, w, sv, x, y, vec16); b += 8; }
+        else if (left >= 4) { gemv_int8_kernel<4><<<blocks, kBlock, 0, st>>>(dim_out, dim_in, b, sm, w, sv, x, y, vec16); b += 4; }
+        else if (left >= 2) { gemv_int8_kernel<2><<<blocks, kBlock, 0, st>>>(dim_out, dim_in, b, sm, w, sv, x, y, vec16); b += 2; }
+        else { gemv_int8_kernel<1><<<blocks, kBlock, 0, st>>>(dim_out, dim_in, b, sm, w, sv, x, y, vec16); b += 1; }
+        CPMK_LAUNCH_CHECK();
+    }
+    return CPMK_OK;
+}
+
+}  // extern "C"

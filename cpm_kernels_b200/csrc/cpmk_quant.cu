@@ -1,0 +1,660 @@
+// Quantisation passes of the int8 linear layer for sm_100a: absmax scale, int8 rounding, their fused
+// forms, and the int32 -> fp16 dequantisation.  All of them are HBM-bound streaming kernels: 128-bit
+// coalesced loads, registers as the only staging, shuffle reductions, no division per element
+// (see cpmk_round_rule.h).
+//
+// Replaces cuda/gemm.cu:6-205 of the reference (one 1024-thread block per row, 2-byte loads, 1-byte
+// stores, an fp32 division per element, grid.y = n <= 65535).
+#include "cpmk_common.cuh"
+#include "cpmk_round_rule.h"
+
+namespace cpmk {
+namespace {
+
+constexpr int kBlock = 256;
+
+// half(amax / 127.0): the reference divides in double and narrows to float, then to half
+// (cuda/gemm.cu:74).  A binary32 division gives the same float for every binary32 amax: x/127 has a
+// period-7 binary expansion, so the double quotient never sits on a binary32 rounding boundary.
+__device__ __forceinline__ __half scale_from_amax(float amax) { return __float2half_rn(__fdiv_rn(amax, 127.0f)); }
+
+// The reference expression, used wherever the division-free rule does not apply.
+__device__ __forceinline__ int8_t round_reference(float x, float s) { return (int8_t)nearbyintf(x / s); }
+
+__device__ __forceinline__ float half2_max_to_float(__half2 m) { return __half2float(__hmax(__low2half(m), __high2half(m))); }
+
+// max(|v|) over the 8 halves of a 128-bit vector, NaN elements dropped as fmaxf does.
+__device__ __forceinline__ __half2 absmax8(const uint4 &v, __half2 m) {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+    m = __hmax2(__habs2(h[0]), m);
+    m = __hmax2(__habs2(h[1]), m);
+    m = __hmax2(__habs2(h[2]), m);
+    m = __hmax2(__habs2(h[3]), m);
+    return m;
+}
+
+// Rounds the 8 halves of `v` with one scale.  r_up is NaN when the scale is outside the rule's
+// domain, which sends every element to the reference expression.
+__device__ __forceinline__ uint2 round8_one_scale(const uint4 &v, float s, float r_up, float r_dn) {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+    uint32_t b[8];
+    int ok = 1;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 f = __half22float2(h[i]);
+        ok &= cpmk_round_pair(f.x, r_up, r_dn, &b[2 * i]);
+        ok &= cpmk_round_pair(f.y, r_up, r_dn, &b[2 * i + 1]);
+    }
+    if (!ok) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __half22float2(h[i]);
+            b[2 * i] = (uint8_t)round_reference(f.x, s);
+            b[2 * i + 1] = (uint8_t)round_reference(f.y, s);
+        }
+    }
+    uint2 out;
+    out.x = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+    out.y = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
+    return out;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Row quantisation: `group` threads share one row (group = 8..256, a power of two), each holding up
+// to NV 128-bit vectors of it in registers, so the row is read from HBM exactly once.
+// MODE 0: scale and codes (fused);  1: scale only;  2: codes only, scale given.
+// ------------------------------------------------------------------------------------------------
+template <int NV, int MODE>
+__global__ void __launch_bounds__(kBlock) quant_rows_kernel(int64_t rows, int32_t m, int group, const __half *__restrict__ mat,
+                                                            __half *__restrict__ scale, int8_t *__restrict__ out) {
+    __shared__ float warp_max[kBlock / 32];
+    const int tid = threadIdx.x;
+    const int rows_per_block = kBlock / group;
+    const int lane_in_row = tid & (group - 1);
+    const int64_t row = (int64_t)blockIdx.x * rows_per_block + tid / group;
+    const bool row_ok = row < rows;
+    const int nvec = m >> 3;
+    const uint4 *src = reinterpret_cast<const uint4 *>(mat + (row_ok ? row : 0) * (int64_t)m);
+
+    uint4 v[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int idx = lane_in_row + j * group;
+        v[j] = (row_ok && idx < nvec) ? __ldcs(src + idx) : make_uint4(0, 0, 0, 0);
+    }
+
+    __half2 m2 = __float2half2_rn(0.f);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) m2 = absmax8(v[j], m2);
+    const float local_max = half2_max_to_float(m2);
+
+    float s;
+    if (MODE == 2) {
+        s = row_ok ? __half2float(scale[row]) : 1.0f;
+    } else {
+        float amax = local_max;
+        const int shuffle_span = group < 32 ? group : 32;
+        for (int o = shuffle_span >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (group > 32) {
+            if ((tid & 31) == 0) warp_max[tid >> 5] = amax;
+            __syncthreads();
+            const int first_warp = (tid / group) * (group >> 5);
+            amax = warp_max[first_warp];
+            for (int w = 1; w < (group >> 5); ++w) amax = fmaxf(amax, warp_max[first_warp + w]);
+        }
+        const __half sh = scale_from_amax(amax);
+        if (row_ok && lane_in_row == 0) scale[row] = sh;
+        s = __half2float(sh);
+    }
+    if (MODE == 1) return;
+
+    float r_up, r_dn;
+    cpmk_round_prepare(s, &r_up, &r_dn);
+    if (!(cpmk_scale_in_domain(s) && cpmk_round_domain_ok(local_max, r_up))) r_up = __int_as_float(0x7fc00000);
+
+    uint2 *dst = reinterpret_cast<uint2 *>(out + (row_ok ? row : 0) * (int64_t)m);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int idx = lane_in_row + j * group;
+        if (row_ok && idx < nvec) dst[idx] = round8_one_scale(v[j], s, r_up, r_dn);
+    }
+}
+
+// Any row length / alignment: one block per row, scalar accesses, the reference expressions.
+template <int MODE>
+__global__ void __launch_bounds__(kBlock) quant_rows_generic_kernel(int64_t rows, int32_t m, const __half *__restrict__ mat,
+                                                                    __half *__restrict__ scale, int8_t *__restrict__ out) {
+    __shared__ float warp_max[kBlock / 32];
+    __shared__ float row_scale;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const __half *src = mat + row * (int64_t)m;
+        float s;
+        if (MODE == 2) {
+            s = __half2float(scale[row]);
+        } else {
+            float amax = 0.f;
+            for (int i = threadIdx.x; i < m; i += kBlock) amax = fmaxf(fabsf(__half2float(src[i])), amax);
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                for (int w = 1; w < kBlock / 32; ++w) amax = fmaxf(amax, warp_max[w]);
+                const __half sh = scale_from_amax(amax);
+                scale[row] = sh;
+                row_scale = __half2float(sh);
+            }
+            __syncthreads();
+            s = row_scale;
+        }
+        if (MODE != 1) {
+            for (int i = threadIdx.x; i < m; i += kBlock) out[row * (int64_t)m + i] = round_reference(__half2float(src[i]), s);
+        }
+        __syncthreads();
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Column quantisation (reduction over the slow axis n of a (batch, n, m) tensor).
+// A block covers a strip of 64 columns (8 threads x 8 halves) and 32 rows per step; the rows are cut
+// into `splits` chunks so that the grid fills the machine.  Pass 1 writes per-chunk column maxima
+// to scratch; pass 2 folds them, derives the scale and rounds.  Pass 2 walks chunks and rows in the
+// opposite order to pass 1 so that it meets the most recently read lines in L2 first.
+// ------------------------------------------------------------------------------------------------
+constexpr int kStripCols = 64;
+constexpr int kStripRows = 32;
+
+__global__ void __launch_bounds__(kBlock) colmax_partial_kernel(int32_t n, int32_t m, int32_t rows_per_split,
+                                                                const __half *__restrict__ mat, __half *__restrict__ partial) {
+    __shared__ __half2 red[kStripRows][kStripCols / 2 + 1];
+    const int cl = threadIdx.x & 7, rl = threadIdx.x >> 3;
+    const int col = blockIdx.x * kStripCols + cl * 8;
+    const int split = blockIdx.y, b = blockIdx.z, splits = gridDim.y;
+    const int r_begin = split * rows_per_split;
+    const int r_end = min(n, r_begin + rows_per_split);
+    const __half *base = mat + (int64_t)b * n * m;
+
+    __half2 m2[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) m2[i] = __float2half2_rn(0.f);
+    if (col < m) {
+        int r = r_begin + rl;
+#pragma unroll 4
+        for (; r < r_end; r += kStripRows) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(base + (int64_t)r * m + col));
+            const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) m2[i] = __hmax2(__habs2(h[i]), m2[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) red[rl][cl * 4 + i] = m2[i];
+    __syncthreads();
+    if (threadIdx.x < kStripCols / 2) {
+        __half2 acc = red[0][threadIdx.x];
+#pragma unroll 8
+        for (int r = 1; r < kStripRows; ++r) acc = __hmax2(acc, red[r][threadIdx.x]);
+        const int c = blockIdx.x * kStripCols + threadIdx.x * 2;
+        if (c < m) *reinterpret_cast<__half2 *>(partial + ((int64_t)split * gridDim.z + b) * m + c) = acc;
+    }
+    (void)splits;
+}
+
+// scale[b, c] = half(max over splits / 127)
+__global__ void __launch_bounds__(kBlock) colmax_finish_kernel(int32_t batch, int32_t m, int32_t splits,
+                                                               const __half *__restrict__ partial, __half *__restrict__ scale) {
+    const int64_t idx = (int64_t)blockIdx.x * kBlock + threadIdx.x;
+    if (idx >= (int64_t)batch * m) return;
+    float amax = 0.f;
+    for (int s = 0; s < splits; ++s) amax = fmaxf(amax, __half2float(partial[(int64_t)s * batch * m + idx]));
+    scale[idx] = scale_from_amax(amax);
+}
+
+// SRC 0: fold the partial maxima, write the scale (blocks of split 0) and round.
+// SRC 1: scale given by the caller (gemm_round_transpose); validity of the rule is checked per code.
+template <int SRC>
+__global__ void __launch_bounds__(kBlock) quant_cols_round_kernel(int32_t n, int32_t m, int32_t rows_per_split, int32_t splits,
+                                                                  const __half *__restrict__ mat, const __half *__restrict__ partial,
+                                                                  __half *__restrict__ scale, int8_t *__restrict__ out) {
+    const int cl = threadIdx.x & 7, rl = threadIdx.x >> 3;
+    const int col = blockIdx.x * kStripCols + cl * 8;
+    if (col >= m) return;
+    const int split = gridDim.y - 1 - blockIdx.y, b = blockIdx.z, batch = gridDim.z;
+    const int r_begin = split * rows_per_split;
+    const int r_end = min(n, r_begin + rows_per_split);
+
+    float s[8], r_up[8], r_dn[8];
+    if (SRC == 0) {
+        __half2 m2[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) m2[i] = __float2half2_rn(0.f);
+        for (int sp = 0; sp < splits; ++sp) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(partial + ((int64_t)sp * batch + b) * m + col));
+            const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) m2[i] = __hmax2(h[i], m2[i]);
+        }
+        __align__(16) __half sh[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 a = __half22float2(m2[i]);
+            sh[2 * i] = scale_from_amax(a.x);
+            sh[2 * i + 1] = scale_from_amax(a.y);
+            s[2 * i] = __half2float(sh[2 * i]);
+            s[2 * i + 1] = __half2float(sh[2 * i + 1]);
+            cpmk_round_prepare(s[2 * i], &r_up[2 * i], &r_dn[2 * i]);
+            cpmk_round_prepare(s[2 * i + 1], &r_up[2 * i + 1], &r_dn[2 * i + 1]);
+            if (!(cpmk_scale_in_domain(s[2 * i]) && cpmk_round_domain_ok(a.x, r_up[2 * i]))) r_up[2 * i] = __int_as_float(0x7fc00000);
+            if (!(cpmk_scale_in_domain(s[2 * i + 1]) && cpmk_round_domain_ok(a.y, r_up[2 * i + 1]))) r_up[2 * i + 1] = __int_as_float(0x7fc00000);
+        }
+        if (split == 0 && rl == 0) *reinterpret_cast<uint4 *>(scale + (int64_t)b * m + col) = *reinterpret_cast<const uint4 *>(sh);
+    } else {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(scale + (int64_t)b * m + col));
+        const __half *h = reinterpret_cast<const __half *>(&v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            s[i] = __half2float(h[i]);
+            cpmk_round_prepare(s[i], &r_up[i], &r_dn[i]);
+            if (!cpmk_scale_in_domain(s[i])) r_up[i] = __int_as_float(0x7fc00000);
+        }
+    }
+
+    const __half *base = mat + (int64_t)b * n * m;
+    int8_t *obase = out + (int64_t)b * n * m;
+    // rows of this thread, walked downwards: r = r_last, r_last - 32, ...
+    const int count = (r_end - r_begin - rl + kStripRows - 1) / kStripRows;   // rows r_begin + rl + 32 i < r_end
+#pragma unroll 2
+    for (int i = count - 1; i >= 0; --i) {
+        const int r = r_begin + rl + i * kStripRows;
+        const uint4 v = __ldcs(reinterpret_cast<const uint4 *>(base + (int64_t)r * m + col));
+        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+        uint32_t bits[8];
+        int ok = 1;
+        uint32_t range = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(h[j]);
+            ok &= cpmk_round_pair(f.x, r_up[2 * j], r_dn[2 * j], &bits[2 * j]);
+            ok &= cpmk_round_pair(f.y, r_up[2 * j + 1], r_dn[2 * j + 1], &bits[2 * j + 1]);
+            if (SRC == 1) {
+                // a code is valid iff its pattern is 0x4B400000 + q with -128 <= q <= 127
+                range |= ((bits[2 * j] + 0x80u) ^ 0x4B400000u) | ((bits[2 * j + 1] + 0x80u) ^ 0x4B400000u);
+            }
+        }
+        if (SRC == 1) ok &= (range < 0x100u);
+        if (!ok) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                bits[2 * j] = (uint8_t)round_reference(f.x, s[2 * j]);
+                bits[2 * j + 1] = (uint8_t)round_reference(f.y, s[2 * j + 1]);
+            }
+        }
+        uint2 q;
+        q.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+        q.y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
+        *reinterpret_cast<uint2 *>(obase + (int64_t)r * m + col) = q;
+    }
+}
+
+// Any shape: one thread per column, the reference expressions (m not a multiple of 8).
+template <int MODE>
+__global__ void __launch_bounds__(kBlock) quant_cols_generic_kernel(int32_t batch, int32_t n, int32_t m, const __half *__restrict__ mat,
+                                                                    __half *__restrict__ scale, int8_t *__restrict__ out) {
+    const int64_t idx = (int64_t)blockIdx.x * kBlock + threadIdx.x;
+    if (idx >= (int64_t)batch * m) return;
+    const int b = (int)(idx / m), c = (int)(idx % m);
+    const __half *base = mat + (int64_t)b * n * m + c;
+    float s;
+    if (MODE == 2) {
+        s = __half2float(scale[idx]);
+    } else {
+        float amax = 0.f;
+        for (int r = 0; r < n; ++r) amax = fmaxf(fabsf(__half2float(base[(int64_t)r * m])), amax);
+        const __half sh = scale_from_amax(amax);
+        scale[idx] = sh;
+        s = __half2float(sh);
+    }
+    if (MODE != 1)
+        for (int r = 0; r < n; ++r) out[(int64_t)b * n * m + (int64_t)r * m + c] = round_reference(__half2float(base[(int64_t)r * m]), s);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Dequantisation: out = half(((float)acc * sx) * sy).  MODE 0: both scales; 1: scale_x only
+// (out = half(sx * (float)acc)); 2: scale_y only.
+// ------------------------------------------------------------------------------------------------
+template <int MODE>
+__global__ void __launch_bounds__(kBlock) dequant_kernel(int64_t total_vec, int32_t n, int32_t m, const int32_t *__restrict__ mat,
+                                                         const __half *__restrict__ scale_x, const __half *__restrict__ scale_y,
+                                                         __half *__restrict__ out, int bx, int by) {
+    const int64_t g = (int64_t)blockIdx.x * kBlock + threadIdx.x;
+    if (g >= total_vec) return;
+    const int vec_per_row = m >> 3;
+    const int64_t row = g / vec_per_row;              // b * n + r
+    const int col = (int)(g - row * vec_per_row) << 3;
+    const int b = (int)(row / n);
+    const int r = (int)(row - (int64_t)b * n);
+    float sx = 1.f;
+    if (MODE != 2) sx = __half2float(__ldg(scale_x + (bx ? r : row)));
+    float sy[8];
+    if (MODE != 1) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(scale_y + (by ? 0 : (int64_t)b * m) + col));
+        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            sy[2 * i] = f.x;
+            sy[2 * i + 1] = f.y;
+        }
+    }
+    const int4 a0 = __ldcs(reinterpret_cast<const int4 *>(mat + g * 8));
+    const int4 a1 = __ldcs(reinterpret_cast<const int4 *>(mat + g * 8) + 1);
+    const int acc[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    __align__(16) __half o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float v;
+        if (MODE == 0) v = __fmul_rn(__fmul_rn((float)acc[i], sx), sy[i]);
+        else if (MODE == 1) v = __fmul_rn(sx, (float)acc[i]);
+        else v = __fmul_rn((float)acc[i], sy[i]);
+        o[i] = __float2half_rn(v);
+    }
+    *reinterpret_cast<uint4 *>(out + g * 8) = *reinterpret_cast<const uint4 *>(o);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kBlock) dequant_generic_kernel(int64_t total, int32_t n, int32_t m, const int32_t *__restrict__ mat,
+                                                                 const __half *__restrict__ scale_x, const __half *__restrict__ scale_y,
+                                                                 __half *__restrict__ out, int bx, int by) {
+    const int64_t g = (int64_t)blockIdx.x * kBlock + threadIdx.x;
+    if (g >= total) return;
+    const int64_t row = g / m;
+    const int c = (int)(g - row * m);
+    const int b = (int)(row / n);
+    const int r = (int)(row - (int64_t)b * n);
+    float v = (float)mat[g];
+    if (MODE == 0) v = __fmul_rn(__fmul_rn(v, __half2float(scale_x[bx ? r : row])), __half2float(scale_y[(by ? 0 : (int64_t)b * m) + c]));
+    else if (MODE == 1) v = __fmul_rn(__half2float(scale_x[row]), v);
+    else v = __fmul_rn(v, __half2float(scale_y[(int64_t)b * m + c]));
+    out[g] = __float2half_rn(v);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Backward helpers (cuda/gemm.cu:103-172): the operand is mat * scale, its absmax scale stays in
+// fp32 for the division, so the division-free rule (which relies on fp16 operands) does not apply.
+// One block per row / one thread per column, reference expressions.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kBlock) backward_round_scale_kernel(int32_t batch, int32_t n, int32_t m, const __half *__restrict__ mat,
+                                                                      const __half *__restrict__ scale_y, int8_t *__restrict__ out,
+                                                                      __half *__restrict__ scale_x, int by) {
+    __shared__ float warp_max[kBlock / 32];
+    __shared__ float row_scale;
+    const int64_t rows = (int64_t)batch * n;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int b = (int)(row / n);
+        const __half *src = mat + row * (int64_t)m;
+        const __half *sy = scale_y + (by ? 0 : (int64_t)b * m);
+        float amax = 0.f;
+        for (int i = threadIdx.x; i < m; i += kBlock)
+            amax = fmaxf(fabsf(__fmul_rn(__half2float(src[i]), __half2float(__ldg(sy + i)))), amax);
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < kBlock / 32; ++w) amax = fmaxf(amax, warp_max[w]);
+            const float s = __fdiv_rn(amax, 127.0f);
+            row_scale = s;
+            scale_x[row] = __float2half_rn(s);
+        }
+        __syncthreads();
+        const float s = row_scale;
+        for (int i = threadIdx.x; i < m; i += kBlock)
+            out[row * (int64_t)m + i] = (int8_t)nearbyintf(__fdiv_rn(__fmul_rn(__half2float(src[i]), __half2float(__ldg(sy + i))), s));
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(kBlock) backward_scale_round_kernel(int32_t batch, int32_t n, int32_t m, const __half *__restrict__ mat,
+                                                                      const __half *__restrict__ scale_x, int8_t *__restrict__ out,
+                                                                      __half *__restrict__ scale_y, int bx) {
+    const int64_t idx = (int64_t)blockIdx.x * kBlock + threadIdx.x;
+    if (idx >= (int64_t)batch * m) return;
+    const int b = (int)(idx / m), c = (int)(idx % m);
+    const __half *base = mat + (int64_t)b * n * m + c;
+    const __half *sx = scale_x + (bx ? 0 : (int64_t)b * n);
+    float amax = 0.f;
+    for (int r = 0; r < n; ++r) amax = fmaxf(fabsf(__fmul_rn(__half2float(base[(int64_t)r * m]), __half2float(__ldg(sx + r)))), amax);
+    const float s = __fdiv_rn(amax, 127.0f);
+    scale_y[idx] = __float2half_rn(s);
+    for (int r = 0; r < n; ++r)
+        out[(int64_t)b * n * m + (int64_t)r * m + c] =
+            (int8_t)nearbyintf(__fdiv_rn(__fmul_rn(__half2float(base[(int64_t)r * m]), __half2float(__ldg(sx + r))), s));
+}
+
+// ------------------------------------------------------------------------------------------------
+// host-side dispatch
+// ------------------------------------------------------------------------------------------------
+int32_t check_shape(int32_t batch, int32_t n, int32_t m) {
+    CPMK_REQUIRE(batch >= 0 && n >= 0 && m >= 0, "negative size: batch=%d n=%d m=%d", batch, n, m);
+    CPMK_REQUIRE((int64_t)batch * n * m < (int64_t(1) << 40), "tensor too large: batch=%d n=%d m=%d", batch, n, m);
+    return CPMK_OK;
+}
+
+template <int MODE>
+int32_t launch_quant_rows(int32_t batch, int32_t n, int32_t m, const void *mat, void *scale, void *out, cudaStream_t stream) {
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    rc = check_shape(batch, n, m);
+    if (rc) return rc;
+    const int64_t rows = (int64_t)batch * n;
+    if (rows == 0 || m == 0) {
+        if (MODE != 2 && rows > 0) CPMK_CUDA_TRY(cudaMemsetAsync(scale, 0, rows * sizeof(__half), stream));
+        return CPMK_OK;
+    }
+    CPMK_REQUIRE(mat && (MODE == 1 || out) && scale, "null tensor pointer");
+    const __half *src = static_cast<const __half *>(mat);
+    __half *sc = static_cast<__half *>(scale);
+    int8_t *dst = static_cast<int8_t *>(out);
+    const bool vec_ok = (m % 8 == 0) && aligned16(mat) && (MODE == 1 || (reinterpret_cast<uintptr_t>(out) & 7u) == 0) && m <= 256 * 8 * 8;
+    if (!vec_ok) {
+        const int grid = (int)(rows < 148 * 16 ? rows : 148 * 16);
+        quant_rows_generic_kernel<MODE><<<grid, kBlock, 0, stream>>>(rows, m, src, sc, dst);
+        CPMK_LAUNCH_CHECK();
+        return CPMK_OK;
+    }
+    const int nvec = m / 8;
+    int group = 8;
+    while (group < 256 && group * 4 < nvec) group <<= 1;       // aim at <= 4 vectors per thread
+    const int nv = (nvec + group - 1) / group;                  // 1..8
+    const int rows_per_block = kBlock / group;
+    const int64_t blocks = ceil_div64(rows, rows_per_block);
+    CPMK_REQUIRE(blocks < (int64_t(1) << 31), "too many rows: %lld", (long long)rows);
+    const dim3 grid((unsigned)blocks);
+    if (nv <= 1) quant_rows_kernel<1, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
+    else if (nv <= 2) quant_rows_kernel<2, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
+    else if (nv <= 4) quant_rows_kernel<4, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
+    else quant_rows_kernel<8, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
+    CPMK_LAUNCH_CHECK();
+    return CPMK_OK;
+}
+
+struct ColPlan {
+    int strips, splits, rows_per_split;
+};
+
+ColPlan plan_cols(int32_t batch, int32_t n, int32_t m, int sm_count, size_t partial_elem_bytes, size_t scratch_bytes) {
+    ColPlan p;
+    p.strips = (m + kStripCols - 1) / kStripCols;
+    const int64_t target = (int64_t)sm_count * 8;
+    int64_t splits = target / ((int64_t)p.strips * batch);
+    const int64_t max_by_rows = (n + kStripRows - 1) / kStripRows;
+    if (splits > max_by_rows) splits = max_by_rows;
+    if (splits > 64) splits = 64;
+    const int64_t max_by_scratch = (int64_t)(scratch_bytes / (partial_elem_bytes * (size_t)batch * (size_t)m));
+    if (splits > max_by_scratch) splits = max_by_scratch;
+    if (splits < 1) splits = 1;
+    int rps = (int)((n + splits - 1) / splits);
+    rps = (rps + kStripRows - 1) / kStripRows * kStripRows;
+    p.rows_per_split = rps;
+    p.splits = (n + rps - 1) / rps;
+    return p;
+}
+
+// MODE 0: fused; 1: scale only; 2: round only with the caller's scale
+template <int MODE>
+int32_t launch_quant_cols(int32_t batch, int32_t n, int32_t m, const void *mat, void *scale, void *out, cudaStream_t stream) {
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    rc = check_shape(batch, n, m);
+    if (rc) return rc;
+    if (batch == 0 || m == 0) return CPMK_OK;
+    if (n == 0) {
+        if (MODE != 2) CPMK_CUDA_TRY(cudaMemsetAsync(scale, 0, (size_t)batch * m * sizeof(__half), stream));
+        return CPMK_OK;
+    }
+    CPMK_REQUIRE(mat && (MODE == 1 || out) && scale, "null tensor pointer");
+    const __half *src = static_cast<const __half *>(mat);
+    __half *sc = static_cast<__half *>(scale);
+    int8_t *dst = static_cast<int8_t *>(out);
+    const bool vec_ok = (m % 8 == 0) && aligned16(mat) && aligned16(scale) && (MODE == 1 || (reinterpret_cast<uintptr_t>(out) & 7u) == 0) &&
+                        batch <= 65535 && (size_t)batch * m * sizeof(__half) <= Workspace::kScratchBytes;
+    if (!vec_ok) {
+        const int64_t blocks = ceil_div64((int64_t)batch * m, kBlock);
+        quant_cols_generic_kernel<MODE><<<(unsigned)blocks, kBlock, 0, stream>>>(batch, n, m, src, sc, dst);
+        CPMK_LAUNCH_CHECK();
+        return CPMK_OK;
+    }
+    const ColPlan p = plan_cols(batch, n, m, info.sm_count, sizeof(__half), Workspace::kScratchBytes);
+    const dim3 grid(p.strips, p.splits, batch);
+    if (MODE == 2) {
+        quant_cols_round_kernel<1><<<grid, kBlock, 0, stream>>>(n, m, p.rows_per_split, p.splits, src, nullptr, sc, dst);
+        CPMK_LAUNCH_CHECK();
+        return CPMK_OK;
+    }
+    Workspace ws;
+    rc = get_workspace(stream, &ws);
+    if (rc) return rc;
+    __half *partial = reinterpret_cast<__half *>(ws.scratch());
+    colmax_partial_kernel<<<grid, kBlock, 0, stream>>>(n, m, p.rows_per_split, src, partial);
+    CPMK_LAUNCH_CHECK();
+    if (MODE == 1) {
+        const int64_t blocks = ceil_div64((int64_t)batch * m, kBlock);
+        colmax_finish_kernel<<<(unsigned)blocks, kBlock, 0, stream>>>(batch, m, p.splits, partial, sc);
+    } else {
+        quant_cols_round_kernel<0><<<grid, kBlock, 0, stream>>>(n, m, p.rows_per_split, p.splits, src, partial, sc, dst);
+    }
+    CPMK_LAUNCH_CHECK();
+    return CPMK_OK;
+}
+
+template <int MODE>
+int32_t launch_dequant(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale_x, const void *scale_y, void *out,
+                       int bx, int by, cudaStream_t stream) {
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    rc = check_shape(batch, n, m);
+    if (rc) return rc;
+    const int64_t total = (int64_t)batch * n * m;
+    if (total == 0) return CPMK_OK;
+    CPMK_REQUIRE(mat && out && (MODE == 2 || scale_x) && (MODE == 1 || scale_y), "null tensor pointer");
+    const int32_t *acc = static_cast<const int32_t *>(mat);
+    const __half *sx = static_cast<const __half *>(scale_x);
+    const __half *sy = static_cast<const __half *>(scale_y);
+    __half *dst = static_cast<__half *>(out);
+    const bool vec_ok = (m % 8 == 0) && aligned16(mat) && aligned16(out) && (MODE == 1 || aligned16(scale_y));
+    if (vec_ok) {
+        const int64_t total_vec = total / 8;
+        const int64_t blocks = ceil_div64(total_vec, kBlock);
+        CPMK_REQUIRE(blocks < (int64_t(1) << 31), "tensor too large");
+        dequant_kernel<MODE><<<(unsigned)blocks, kBlock, 0, stream>>>(total_vec, n, m, acc, sx, sy, dst, bx, by);
+    } else {
+        const int64_t blocks = ceil_div64(total, kBlock);
+        CPMK_REQUIRE(blocks < (int64_t(1) << 31), "tensor too large");
+        dequant_generic_kernel<MODE><<<(unsigned)blocks, kBlock, 0, stream>>>(total, n, m, acc, sx, sy, dst, bx, by);
+    }
+    CPMK_LAUNCH_CHECK();
+    return CPMK_OK;
+}
+
+}  // namespace
+}  // namespace cpmk
+
+using namespace cpmk;
+
+extern "C" {
+
+int32_t cpmk_gemm_calc_scale(int32_t batch, int32_t n, int32_t m, const void *mat, void *out, cpmk_stream_t stream) {
+    return launch_quant_rows<1>(batch, n, m, mat, out, nullptr, as_stream(stream));
+}
+
+int32_t cpmk_gemm_round(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale, void *out, cpmk_stream_t stream) {
+    return launch_quant_rows<2>(batch, n, m, mat, const_cast<void *>(scale), out, as_stream(stream));
+}
+
+int32_t cpmk_quantize_rows(int32_t batch, int32_t n, int32_t m, const void *mat, void *scale_out, void *q_out, cpmk_stream_t stream) {
+    return launch_quant_rows<0>(batch, n, m, mat, scale_out, q_out, as_stream(stream));
+}
+
+int32_t cpmk_gemm_calc_scale_transpose(int32_t batch, int32_t n, int32_t m, const void *inp, void *out, cpmk_stream_t stream) {
+    return launch_quant_cols<1>(batch, n, m, inp, out, nullptr, as_stream(stream));
+}
+
+int32_t cpmk_gemm_round_transpose(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale, void *out, cpmk_stream_t stream) {
+    return launch_quant_cols<2>(batch, n, m, mat, const_cast<void *>(scale), out, as_stream(stream));
+}
+
+int32_t cpmk_quantize_cols(int32_t batch, int32_t n, int32_t m, const void *mat, void *scale_out, void *q_out, cpmk_stream_t stream) {
+    return launch_quant_cols<0>(batch, n, m, mat, scale_out, q_out, as_stream(stream));
+}
+
+int32_t cpmk_gemm_scale(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale_x, const void *scale_y, void *out,
+                        int32_t broad_cast_x, int32_t broad_cast_y, cpmk_stream_t stream) {
+    return launch_dequant<0>(batch, n, m, mat, scale_x, scale_y, out, broad_cast_x != 0, broad_cast_y != 0, as_stream(stream));
+}
+
+int32_t cpmk_gemm_scale_x(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale_x, void *out, cpmk_stream_t stream) {
+    return launch_dequant<1>(batch, n, m, mat, scale_x, nullptr, out, 0, 0, as_stream(stream));
+}
+
+int32_t cpmk_gemm_scale_y(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale_y, void *out, cpmk_stream_t stream) {
+    return launch_dequant<2>(batch, n, m, mat, nullptr, scale_y, out, 0, 0, as_stream(stream));
+}
+
+int32_t cpmk_gemm_backward_round_scale(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale_y, void *out, void *scale_x,
+                                       int32_t broad_cast_y, cpmk_stream_t stream) {
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    rc = check_shape(batch, n, m);
+    if (rc) return rc;
+    const int64_t rows = (int64_t)batch * n;
+    if (rows == 0) return CPMK_OK;
+    CPMK_REQUIRE(mat && scale_y && out && scale_x, "null tensor pointer");
+    const int grid = (int)(rows < (int64_t)info.sm_count * 16 ? rows : (int64_t)info.sm_count * 16);
+    backward_round_scale_kernel<<<grid, kBlock, 0, as_stream(stream)>>>(batch, n, m, static_cast<const __half *>(mat),
+                                                                         static_cast<const __half *>(scale_y), static_cast<int8_t *>(out),
+                                                                         static_cast<__half *>(scale_x), broad_cast_y != 0);
+    CPMK_LAUNCH_CHECK();
+    return CPMK_OK;
+}
+
+int32_t cpmk_gemm_backward_scale_round(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale_x, void *out, void *scale_y,
+                                       int32_t broad_cast_x, cpmk_stream_t stream) {
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    rc = check_shape(batch, n, m);
+    if (rc) return rc;
+    if ((int64_t)batch * m == 0) return CPMK_OK;
+    CPMK_REQUIRE(mat && scale_x && out && scale_y, "null tensor pointer");
+    const int64_t blocks = ceil_div64((int64_t)batch * m, kBlock);
+    backward_scale_round_kernel<<<(unsigned)blocks, kBlock, 0, as_stream(stream)>>>(batch, n, m, static_cast<const __half *>(mat),
+                                                                                    static_cast<const __half *>(scale_x), static_cast<int8_t *>(out),
+                                                                                    static_cast<__half *>(scale_y), broad_cast_x != 0);
+    CPMK_LAUNCH_CHECK();
+    return CPMK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,144 @@
+"""Launchers of the quantisation passes and the int8 GEMM, with the signatures of
+cpm_kernels/kernels/gemm.py (positional order, meaning and preconditions unchanged).
+
+All pointers are raw device addresses (``DevicePointer = int``), sizes are Python ints and ``stream``
+is a ``cudaStream_t`` value.  Work is enqueued on ``stream``; nothing synchronises.  Shape
+preconditions raise ``AssertionError`` as in the reference; CUDA failures raise ``RuntimeError``.
+"""
+from ..library import cpmk
+from .base import DevicePointer, CUDAStream, stream_arg
+
+
+def gemm_round(batch: int, n: int, m: int,
+               mat: DevicePointer,      # (b, n, m) fp16
+               scale: DevicePointer,    # (b, n)    fp16
+               out: DevicePointer,      # (b, n, m) int8
+               stream: CUDAStream):
+    """kernels/gemm.py:21-41.  out = (int8) nearbyintf(mat / scale[b, row])."""
+    cpmk.call("cpmk_gemm_round", batch, n, m, mat, scale, out, stream_arg(stream))
+
+
+def gemm_round_transpose(batch: int, n: int, m: int,
+                         mat: DevicePointer,    # (b, n, m) fp16
+                         scale: DevicePointer,  # (b, m)    fp16
+                         out: DevicePointer,    # (b, n, m) int8
+                         stream: CUDAStream):
+    """kernels/gemm.py:43-63.  out = (int8) nearbyintf(mat / scale[b, column])."""
+    cpmk.call("cpmk_gemm_round_transpose", batch, n, m, mat, scale, out, stream_arg(stream))
+
+
+def gemm_scale(batch: int, n: int, m: int,
+               mat: DevicePointer,        # (b, n, m) int32
+               scale_x: DevicePointer,    # (b, n)    fp16
+               scale_y: DevicePointer,    # (b, m)    fp16
+               out: DevicePointer,        # (b, n, m) fp16
+               broad_cast_x: bool, broad_cast_y: bool,
+               stream: CUDAStream):
+    """kernels/gemm.py:65-89.  out = half(((float)mat * scale_x) * scale_y)."""
+    cpmk.call("cpmk_gemm_scale", batch, n, m, mat, scale_x, scale_y, out, int(bool(broad_cast_x)), int(bool(broad_cast_y)),
+              stream_arg(stream))
+
+
+def gemm_calc_scale(batch: int, n: int, m: int,
+                    mat: DevicePointer,    # (b, n, m) fp16
+                    out: DevicePointer,    # (b, n)    fp16
+                    stream: CUDAStream):
+    """kernels/gemm.py:91-107.  out = half(max_i |mat[b, r, i]| / 127)."""
+    cpmk.call("cpmk_gemm_calc_scale", batch, n, m, mat, out, stream_arg(stream))
+
+
+def gemm_calc_scale_transpose(batch: int, n: int, m: int,
+                              inp: DevicePointer,    # (b, n, m) fp16
+                              out: DevicePointer,    # (b, m)    fp16
+                              stream: CUDAStream):
+    """kernels/gemm.py:109-125.  out = half(max_r |inp[b, r, c]| / 127)."""
+    cpmk.call("cpmk_gemm_calc_scale_transpose", batch, n, m, inp, out, stream_arg(stream))
+
+
+def gemm_int8(m: int, k: int, n: int,
+              batchA: int, batchB: int,
+              aT: bool, bT: bool,
+              A: DevicePointer,    # (bA, k, m), or (bA, m, k) if aT     int8
+              B: DevicePointer,    # (bB, n, k), or (bB, k, n) if bT     int8
+              out: DevicePointer,  # (max(bA, bB), n, m)                 int32
+              stream: CUDAStream):
+    """kernels/gemm.py:127-186.  out[b, j, i] = sum_l Aop[b, l, i] * Bop[b, j, l] in int32."""
+    assert m % 4 == 0 and n % 4 == 0 and k % 4 == 0
+    assert batchA == batchB or batchA == 1 or batchB == 1
+    cpmk.call("cpmk_gemm_int8", m, k, n, batchA, batchB, int(bool(aT)), int(bool(bT)), A, B, out, stream_arg(stream))
+
+
+def gemm_backward_round_scale(batch: int, n: int, m: int,
+                              mat: DevicePointer,        # (batch, n, m) fp16
+                              scale_y: DevicePointer,    # (batch, m)    fp16
+                              out: DevicePointer,        # (batch, n, m) int8
+                              scale_x: DevicePointer,    # (batch, n)    fp16
+                              broad_cast_y: bool,
+                              stream: CUDAStream):
+    """kernels/gemm.py:261-283."""
+    cpmk.call("cpmk_gemm_backward_round_scale", batch, n, m, mat, scale_y, out, scale_x, int(bool(broad_cast_y)), stream_arg(stream))
+
+
+def gemm_backward_scale_round(batch: int, n: int, m: int,
+                              mat: DevicePointer,        # (batch, n, m) fp16
+                              scale_x: DevicePointer,    # (batch, n)    fp16
+                              out: DevicePointer,        # (batch, n, m) int8
+                              scale_y: DevicePointer,    # (batch, m)    fp16
+                              broad_cast_x: bool,
+                              stream: CUDAStream):
+    """kernels/gemm.py:285-307."""
+    cpmk.call("cpmk_gemm_backward_scale_round", batch, n, m, mat, scale_x, out, scale_y, int(bool(broad_cast_x)), stream_arg(stream))
+
+
+def gemm_scale_x(batch: int, n: int, m: int,
+                 mat: DevicePointer,        # (batch, n, m) int32
+                 scale_x: DevicePointer,    # (batch, n)    fp16
+                 out: DevicePointer,        # (batch, n, m) fp16
+                 stream: CUDAStream):
+    """kernels/gemm.py:309-327."""
+    cpmk.call("cpmk_gemm_scale_x", batch, n, m, mat, scale_x, out, stream_arg(stream))
+
+
+def gemm_scale_y(batch: int, n: int, m: int,
+                 mat: DevicePointer,        # (batch, n, m) int32
+                 scale_y: DevicePointer,    # (batch, m)    fp16
+                 out: DevicePointer,        # (batch, n, m) fp16
+                 stream: CUDAStream):
+    """kernels/gemm.py:329-347."""
+    cpmk.call("cpmk_gemm_scale_y", batch, n, m, mat, scale_y, out, stream_arg(stream))
+
+
+# ---- fused forms (no counterpart function in the reference; each equals two of the calls above) ----
+
+def gemm_quantize_rows(batch: int, n: int, m: int,
+                       mat: DevicePointer,      # (b, n, m) fp16
+                       scale: DevicePointer,    # (b, n)    fp16, written
+                       out: DevicePointer,      # (b, n, m) int8, written
+                       stream: CUDAStream):
+    """gemm_calc_scale followed by gemm_round on the same tensor (torch/gemm.py:98-102), in one pass."""
+    cpmk.call("cpmk_quantize_rows", batch, n, m, mat, scale, out, stream_arg(stream))
+
+
+def gemm_quantize_cols(batch: int, n: int, m: int,
+                       mat: DevicePointer,      # (b, n, m) fp16
+                       scale: DevicePointer,    # (b, m)    fp16, written
+                       out: DevicePointer,      # (b, n, m) int8, written
+                       stream: CUDAStream):
+    """gemm_calc_scale_transpose followed by gemm_round_transpose on the same tensor."""
+    cpmk.call("cpmk_quantize_cols", batch, n, m, mat, scale, out, stream_arg(stream))
+
+
+def gemm_int8_scale(m: int, k: int, n: int,
+                    batchA: int, batchB: int,
+                    aT: bool, bT: bool,
+                    A: DevicePointer, B: DevicePointer,
+                    scale_x: DevicePointer,    # (broad_cast_x ? 1 : batch, n) fp16
+                    scale_y: DevicePointer,    # (broad_cast_y ? 1 : batch, m) fp16
+                    broad_cast_x: bool, broad_cast_y: bool,
+                    out: DevicePointer,        # (max(bA, bB), n, m) fp16
+                    stream: CUDAStream):
+    """gemm_int8 followed by gemm_scale (torch/gemm.py:45-64) without the int32 tensor in between."""
+    assert m % 4 == 0 and n % 4 == 0 and k % 4 == 0
+    assert batchA == batchB or batchA == 1 or batchB == 1
+    cpmk.call("cpmk_gemm_int8_dequant", m, k, n, batchA, batchB, int(bool(aT)), int(bool(bT)), A, B, scale_x, scale_y,
+              int(bool(broad_cast_x)), int(bool(broad_cast_y)), out, stream_arg(stream))

@@ -1,0 +1,185 @@
+"""``bmm`` and its autograd functions, as cpm_kernels/torch/gemm.py.
+
+PyTorch is used for what the reference uses it for: allocating the outputs, ``data_ptr()``, the current
+stream and autograd bookkeeping.  All arithmetic of the int8 path runs in this package's CUDA kernels.
+
+The forward pass issues three kernels where the reference issues six (torch/gemm.py:98-104): each operand
+is quantised by one fused scale+round pass, and the int8 GEMM writes dequantised fp16 directly, so neither
+the fp16 operands are read twice nor does an int32 tensor travel through HBM.  The tensors saved for
+backward and every value returned are bit-identical to what the six separate passes produce.
+"""
+from typing import Optional
+
+import torch
+
+from ..kernels import (gemm_calc_scale, gemm_calc_scale_transpose, gemm_round, gemm_round_transpose, gemm_scale, gemm_int8,
+                       gemm_backward_round_scale, gemm_backward_scale_round, gemm_scale_x, gemm_scale_y,
+                       gemm_quantize_rows, gemm_quantize_cols, gemm_int8_scale)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def calc_scale(mat: torch.Tensor, transpose: bool) -> torch.Tensor:
+    """torch/gemm.py:5-19.  (b, n, m) -> (b, m) if transpose else (b, n)."""
+    assert mat.is_contiguous() and mat.is_cuda
+    with torch.cuda.device(mat.device):
+        if transpose:
+            out = torch.empty((mat.size(0), mat.size(2)), dtype=torch.half, device=mat.device)
+            gemm_calc_scale_transpose(mat.size(0), mat.size(1), mat.size(2), mat.data_ptr(), out.data_ptr(), _stream())
+        else:
+            out = torch.empty((mat.size(0), mat.size(1)), dtype=torch.half, device=mat.device)
+            gemm_calc_scale(mat.size(0), mat.size(1), mat.size(2), mat.data_ptr(), out.data_ptr(), _stream())
+    return out
+
+
+def round_i8(mat: torch.Tensor, scale: torch.Tensor, transpose: bool) -> torch.Tensor:
+    """torch/gemm.py:21-38."""
+    assert mat.is_contiguous() and mat.is_cuda
+    assert scale.is_contiguous() and scale.is_cuda
+    out = torch.empty(mat.size(), dtype=torch.int8, device=mat.device)
+    with torch.cuda.device(mat.device):
+        if transpose:
+            gemm_round_transpose(mat.size(0), mat.size(1), mat.size(2), mat.data_ptr(), scale.data_ptr(), out.data_ptr(), _stream())
+        else:
+            gemm_round(mat.size(0), mat.size(1), mat.size(2), mat.data_ptr(), scale.data_ptr(), out.data_ptr(), _stream())
+    return out
+
+
+def quantize(mat: torch.Tensor, transpose: bool):
+    """calc_scale + round_i8 in one pass over ``mat``.  Returns (scale fp16, codes int8)."""
+    assert mat.is_contiguous() and mat.is_cuda and mat.dtype == torch.half and mat.ndim == 3
+    b, n, m = mat.shape
+    codes = torch.empty(mat.size(), dtype=torch.int8, device=mat.device)
+    with torch.cuda.device(mat.device):
+        if transpose:
+            scale = torch.empty((b, m), dtype=torch.half, device=mat.device)
+            gemm_quantize_cols(b, n, m, mat.data_ptr(), scale.data_ptr(), codes.data_ptr(), _stream())
+        else:
+            scale = torch.empty((b, n), dtype=torch.half, device=mat.device)
+            gemm_quantize_rows(b, n, m, mat.data_ptr(), scale.data_ptr(), codes.data_ptr(), _stream())
+    return scale, codes
+
+
+def gemm_and_scale(quantA: torch.Tensor, scaleA: Optional[torch.Tensor], quantB: torch.Tensor, scaleB: Optional[torch.Tensor],
+                   aT: bool, bT: bool) -> torch.Tensor:
+    """torch/gemm.py:40-82.  quantA (bA, M, K) [(bA, K, M) if aT], quantB (bB, K, N) [(bB, N, K) if bT] -> fp16 (b, M, N).
+    The operands are passed swapped (torch/gemm.py:45-52) so that the kernel-level (n, m) = (M, N) output is row-major C."""
+    M = quantA.size(2) if aT else quantA.size(1)
+    K = quantA.size(1) if aT else quantA.size(2)
+    N = quantB.size(1) if bT else quantB.size(2)
+    batch = max(quantA.size(0), quantB.size(0))
+    result_fp = torch.empty((batch, M, N), dtype=torch.float16, device=quantA.device)
+    with torch.cuda.device(quantA.device):
+        if scaleA is not None and scaleB is not None:
+            gemm_int8_scale(N, K, M, quantB.size(0), quantA.size(0), bT, aT, quantB.data_ptr(), quantA.data_ptr(),
+                            scaleA.data_ptr(), scaleB.data_ptr(), quantA.size(0) == 1, quantB.size(0) == 1,
+                            result_fp.data_ptr(), _stream())
+            return result_fp
+        result_i32 = torch.empty((batch, M, N), dtype=torch.int32, device=quantA.device)
+        gemm_int8(N, K, M, quantB.size(0), quantA.size(0), bT, aT, quantB.data_ptr(), quantA.data_ptr(), result_i32.data_ptr(), _stream())
+        if scaleA is not None:
+            gemm_scale_x(batch, M, N, result_i32.data_ptr(), scaleA.data_ptr(), result_fp.data_ptr(), _stream())
+        else:
+            assert scaleB is not None
+            gemm_scale_y(batch, M, N, result_i32.data_ptr(), scaleB.data_ptr(), result_fp.data_ptr(), _stream())
+    return result_fp
+
+
+class GEMMInt8(torch.autograd.Function):
+    """torch/gemm.py:84-179."""
+
+    @staticmethod
+    def forward(ctx, A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool):
+        """A (batchA, M, K) [(batchA, K, M) if aT], B (batchB, K, N) [(batchB, N, K) if bT] -> (batch, M, N)."""
+        assert A.is_cuda and B.is_cuda and A.device == B.device
+        assert A.is_contiguous() and B.is_contiguous()
+        assert A.dtype == torch.half and B.dtype == torch.half
+
+        scale_A, quantized_A = quantize(A, aT)
+        scale_B, quantized_B = quantize(B, not bT)
+        result = gemm_and_scale(quantized_A, scale_A, quantized_B, scale_B, aT, bT)
+
+        ctx.save_for_backward(scale_A, quantized_A, scale_B, quantized_B)
+        ctx.aT = aT
+        ctx.bT = bT
+        return result
+
+    @staticmethod
+    def backward(ctx, grad_f: torch.Tensor):
+        assert grad_f.is_contiguous() and grad_f.is_cuda and grad_f.dtype == torch.float16
+        scale_A, quantized_A, scale_B, quantized_B = ctx.saved_tensors
+        aT, bT = ctx.aT, ctx.bT
+        batch, m, n = grad_f.size()
+
+        with torch.cuda.device(grad_f.device):
+            scale_G_a = torch.empty((batch, m), dtype=torch.half, device=grad_f.device)
+            quant_G_a = torch.empty((batch, m, n), dtype=torch.int8, device=grad_f.device)
+            gemm_backward_round_scale(batch, m, n, grad_f.data_ptr(), scale_B.data_ptr(), quant_G_a.data_ptr(), scale_G_a.data_ptr(),
+                                      scale_B.size(0) == 1, _stream())
+        if aT:
+            grad_A = gemm_and_scale(quantized_B, None, quant_G_a, scale_G_a, bT, True)
+        else:
+            grad_A = gemm_and_scale(quant_G_a, scale_G_a, quantized_B, None, False, not bT)
+        del scale_G_a, quant_G_a
+
+        with torch.cuda.device(grad_f.device):
+            scale_G_b = torch.empty((batch, n), dtype=torch.half, device=grad_f.device)
+            quant_G_b = torch.empty((batch, m, n), dtype=torch.int8, device=grad_f.device)
+            gemm_backward_scale_round(batch, m, n, grad_f.data_ptr(), scale_A.data_ptr(), quant_G_b.data_ptr(), scale_G_b.data_ptr(),
+                                      scale_A.size(0) == 1, _stream())
+        if bT:
+            grad_B = gemm_and_scale(quant_G_b, scale_G_b, quantized_A, None, True, aT)
+        else:
+            grad_B = gemm_and_scale(quantized_A, None, quant_G_b, scale_G_b, not aT, False)
+
+        if scale_A.size(0) == 1 and grad_A.size(0) > 1:
+            grad_A = grad_A.sum(dim=0, keepdim=True)
+        if scale_B.size(0) == 1 and grad_B.size(0) > 1:
+            grad_B = grad_B.sum(dim=0, keepdim=True)
+        return grad_A, None, grad_B, None
+
+
+def _matmul_fp16(A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool) -> torch.Tensor:
+    a = A.transpose(-1, -2) if aT else A
+    b = B.transpose(-1, -2) if bT else B
+    return torch.matmul(a, b)
+
+
+class GEMMFloat(torch.autograd.Function):
+    """torch/gemm.py:197-231: the ``int8=False`` branch of ``bmm``.  The reference hands this fp16 GEMM to
+    cublasLt (kernels/gemm.py:188-256); it is outside the quantised path, and is likewise handed to the
+    vendor library here, through ``torch.matmul``."""
+
+    @staticmethod
+    def forward(ctx, A: torch.Tensor, aT, B: torch.Tensor, bT):
+        assert A.is_cuda and A.is_contiguous() and A.dtype == torch.half
+        assert B.is_cuda and B.is_contiguous() and B.dtype == torch.half
+        assert A.device == B.device
+        ctx.save_for_backward(A, B)
+        ctx.aT = aT
+        ctx.bT = bT
+        return _matmul_fp16(A, aT, B, bT)
+
+    @staticmethod
+    def backward(ctx, grad_f):
+        assert grad_f.is_cuda and grad_f.is_contiguous() and grad_f.dtype == torch.float16
+        aT, bT = ctx.aT, ctx.bT
+        A, B = ctx.saved_tensors
+        grad_A = _matmul_fp16(B, bT, grad_f, True) if aT else _matmul_fp16(grad_f, False, B, not bT)
+        grad_B = _matmul_fp16(grad_f, True, A, aT) if bT else _matmul_fp16(A, not aT, grad_f, False)
+        if A.size(0) == 1 and grad_A.size(0) > 1:
+            grad_A = grad_A.sum(dim=0, keepdim=True)
+        if B.size(0) == 1 and grad_B.size(0) > 1:
+            grad_B = grad_B.sum(dim=0, keepdim=True)
+        return grad_A, None, grad_B, None
+
+
+def bmm(A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool, int8: bool = False) -> torch.Tensor:
+    """torch/gemm.py:233-239."""
+    assert A.ndim == 3
+    assert B.ndim == 3
+    if int8:
+        return GEMMInt8.apply(A, aT, B, bT)
+    return GEMMFloat.apply(A, aT, B, bT)

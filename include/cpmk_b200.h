@@ -1,0 +1,143 @@
+/*
+ * cpmk_b200 -- C ABI of the B200 (sm_100a) implementation of cpm_kernels' int8-quantised linear
+ * layer and fp16 decode GEMV.
+ *
+ * Conventions (they mirror cpm_kernels/kernels/*.py, whose functions these replace one for one):
+ *   - every tensor argument is a raw device address; the caller owns all tensors;
+ *   - sizes are int32; `stream` is a cudaStream_t (CUstream) value, 0 = the legacy default stream;
+ *   - all work is enqueued on `stream` and the call returns without synchronising;
+ *   - the return value is 0 on success, a CPMK_E* code otherwise; cpmk_last_error() returns a
+ *     thread-local description of the last failure.  Nothing throws, traps or calls exit();
+ *   - tensors are row-major and contiguous; fp16 = IEEE binary16.
+ *
+ * File:line citations name the interface of the reference (OpenBMB/cpm_kernels v1.0.11) that each
+ * entry point replaces.
+ */
+#ifndef CPMK_B200_H_
+#define CPMK_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CPMK_ABI_VERSION 1
+
+enum {
+    CPMK_OK = 0,
+    CPMK_EINVAL = 1,       /* bad size / null pointer / misaligned pointer                       */
+    CPMK_EARCH = 2,        /* the current device is not compute capability 10.x                  */
+    CPMK_ECUDA = 3,        /* a CUDA runtime / driver call failed (text in cpmk_last_error)      */
+    CPMK_EDEVICE = 4,      /* a kernel reported a bounded-wait timeout through the status word   */
+    CPMK_ENOMEM = 5        /* the library's own workspace could not be allocated or is too small */
+};
+
+typedef void *cpmk_stream_t;
+
+int32_t cpmk_abi_version(void);
+const char *cpmk_last_error(void);
+
+/* Compute capability (major*10+minor) of the current device; CPMK_EARCH unless it is 10.x.
+ * Replaces the architecture gate of cpm_kernels/device/__init__.py:143-145. */
+int32_t cpmk_check_device(int32_t *arch_out);
+
+/* Reads (and clears) the per-device status word that kernels with bounded waits set when a wait
+ * runs out: 0 = no error.  Synchronises the device.  No counterpart in the reference (its cublasLt
+ * GEMM has no user-visible waits). */
+int32_t cpmk_read_status(uint32_t *status_out);
+
+/* ------------------------------------------------------------------------------------------
+ * Quantisation passes (cuda/gemm.cu)
+ * ------------------------------------------------------------------------------------------ */
+
+/* kernels/gemm.py:91-107 gemm_calc_scale -> cuda/gemm.cu:60-76.
+ * mat (batch, n, m) fp16; out (batch, n) fp16 = half(max_i |mat[b,r,i]| / 127). */
+int32_t cpmk_gemm_calc_scale(int32_t batch, int32_t n, int32_t m, const void *mat, void *out, cpmk_stream_t stream);
+
+/* kernels/gemm.py:109-125 gemm_calc_scale_transpose -> cuda/gemm.cu:79-98.
+ * inp (batch, n, m) fp16; out (batch, m) fp16 = half(max_r |inp[b,r,c]| / 127). */
+int32_t cpmk_gemm_calc_scale_transpose(int32_t batch, int32_t n, int32_t m, const void *inp, void *out, cpmk_stream_t stream);
+
+/* kernels/gemm.py:21-41 gemm_round -> cuda/gemm.cu:6-18.
+ * out[b,r,i] = (int8) nearbyintf((float)mat[b,r,i] / (float)scale[b,r]). */
+int32_t cpmk_gemm_round(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale, void *out, cpmk_stream_t stream);
+
+/* kernels/gemm.py:43-63 gemm_round_transpose -> cuda/gemm.cu:22-33.  scale is (batch, m). */
+int32_t cpmk_gemm_round_transpose(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale, void *out, cpmk_stream_t stream);
+
+/* Fused gemm_calc_scale + gemm_round (cpm_kernels/torch/gemm.py:98-102 calls them back to back on
+ * the same tensor): one read of `mat`, writes both scale_out (batch, n) and q_out (batch, n, m). */
+int32_t cpmk_quantize_rows(int32_t batch, int32_t n, int32_t m, const void *mat, void *scale_out, void *q_out, cpmk_stream_t stream);
+
+/* Fused gemm_calc_scale_transpose + gemm_round_transpose (same call sites, transposed operand):
+ * writes scale_out (batch, m) and q_out (batch, n, m).  Uses the library workspace. */
+int32_t cpmk_quantize_cols(int32_t batch, int32_t n, int32_t m, const void *mat, void *scale_out, void *q_out, cpmk_stream_t stream);
+
+/* kernels/gemm.py:65-89 gemm_scale -> cuda/gemm.cu:37-57.
+ * mat int32 (batch, n, m); scale_x (batch or 1, n); scale_y (batch or 1, m); out fp16 (batch, n, m)
+ * out = half(((float)mat * sx) * sy). */
+int32_t cpmk_gemm_scale(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale_x, const void *scale_y,
+                        void *out, int32_t broad_cast_x, int32_t broad_cast_y, cpmk_stream_t stream);
+
+/* kernels/gemm.py:309-347 gemm_scale_x / gemm_scale_y -> cuda/gemm.cu:176-205. */
+int32_t cpmk_gemm_scale_x(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale_x, void *out, cpmk_stream_t stream);
+int32_t cpmk_gemm_scale_y(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale_y, void *out, cpmk_stream_t stream);
+
+/* kernels/gemm.py:261-283 gemm_backward_round_scale -> cuda/gemm.cu:103-134. */
+int32_t cpmk_gemm_backward_round_scale(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale_y, void *out,
+                                       void *scale_x, int32_t broad_cast_y, cpmk_stream_t stream);
+/* kernels/gemm.py:285-307 gemm_backward_scale_round -> cuda/gemm.cu:137-172. */
+int32_t cpmk_gemm_backward_scale_round(int32_t batch, int32_t n, int32_t m, const void *mat, const void *scale_x, void *out,
+                                       void *scale_y, int32_t broad_cast_x, cpmk_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * int8 GEMM (replaces the cublasLt call)
+ * ------------------------------------------------------------------------------------------ */
+
+/* kernels/gemm.py:127-186 gemm_int8 -> library/cublaslt.py:126-150 cublasLtMatmul.
+ * A int8 (batchA, k, m), or (batchA, m, k) when aT;  B int8 (batchB, n, k), or (batchB, k, n) when bT;
+ * out int32 (max(batchA,batchB), n, m):  out[b,j,i] = sum_l Aop[b,l,i] * Bop[b,j,l].
+ * batchA, batchB equal or 1 (broadcast).  m, n, k multiples of 4 (the reference's assert). */
+int32_t cpmk_gemm_int8(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT,
+                       const void *A, const void *B, void *out, cpmk_stream_t stream);
+
+/* gemm_int8 with gemm_scale fused into its epilogue (cpm_kernels/torch/gemm.py:40-64 runs them back
+ * to back through an int32 tensor in HBM).  scale_x is (broad_cast_x ? 1 : batch, n) and multiplies
+ * first, scale_y is (broad_cast_y ? 1 : batch, m); out is fp16 (batch, n, m). */
+int32_t cpmk_gemm_int8_dequant(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT,
+                               const void *A, const void *B, const void *scale_x, const void *scale_y,
+                               int32_t broad_cast_x, int32_t broad_cast_y, void *out, cpmk_stream_t stream);
+
+/* Which GEMM kernel the last cpmk_gemm_int8* call on this thread selected:
+ * 1 = tcgen05 tensor-core kernel, 2 = generic SIMT kernel.  For tests and the benchmark. */
+int32_t cpmk_last_gemm_path(void);
+
+/* ------------------------------------------------------------------------------------------
+ * fp16 decode GEMV (cuda/gemv.cu)
+ * ------------------------------------------------------------------------------------------ */
+
+/* kernels/gemv.py:82-148 gemv_fp16 / gemv_fp16_light -> cuda/gemv.cu:79-106.
+ * mat (batch, dim_out, dim_in), vec (batch, dim_in), out (batch, dim_out); dim_in even. */
+int32_t cpmk_gemv_fp16(int32_t batch, int32_t dim_out, int32_t dim_in, const void *mat, const void *vec, void *out, cpmk_stream_t stream);
+
+/* kernels/gemv.py:151-216 gemv_fp16_transpose / _light -> cuda/gemv.cu:109-135.
+ * mat (batch, dim_in, dim_out).  Uses the library workspace for split partial sums. */
+int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in, const void *mat, const void *vec, void *out, cpmk_stream_t stream);
+
+/* kernels/gemv.py:218-283 gemv_broadcast_mat_fp16 / _light -> cuda/gemv.cu:138-164.
+ * mat (dim_out, dim_in) shared by all `batch` vectors. */
+int32_t cpmk_gemv_broadcast_mat_fp16(int32_t batch, int32_t dim_out, int32_t dim_in, const void *mat, const void *vec, void *out, cpmk_stream_t stream);
+
+/* kernels/gemv.py:18-33 gemv_calc_scale -> cuda/gemv.cu:26-40.  vec (batch, n) -> out (batch,). */
+int32_t cpmk_gemv_calc_scale(int32_t batch, int32_t n, const void *vec, void *out, cpmk_stream_t stream);
+/* kernels/gemv.py:35-53 gemv_round -> cuda/gemv.cu:43-54. */
+int32_t cpmk_gemv_round(int32_t batch, int32_t n, const void *vec, const void *scale, void *out, cpmk_stream_t stream);
+/* kernels/gemv.py:56-79 gemv_broadcast_mat_int8 -> cuda/gemv.cu:57-76.  dim_in multiple of 4. */
+int32_t cpmk_gemv_broadcast_mat_int8(int32_t batch, int32_t dim_out, int32_t dim_in, const void *scale_mat, const void *mat,
+                                     const void *scale_vec, const void *vec, void *out, cpmk_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CPMK_B200_H_ */

@@ -1,0 +1,312 @@
+"""TEST INFRASTRUCTURE ONLY -- numpy restatement of the cpm_kernels quantised-linear hot path.
+
+This module is the checker the CUDA kernels are compared against.  The shipped package never
+imports it; only ``tests/``, the smoke check and the CPU-baseline leg of the benchmark do.
+
+Two restatements live side by side and are tested against each other:
+
+* the functions below (vectorised numpy, usable at the benchmark's full sizes), and
+* ``oracle/quant_linear.c`` (scalar C that follows the reference's device code operation by
+  operation; reached through :class:`COracle`).
+
+Parity pin: the reference holds no golden vectors for this path.  The pin is the reference's
+own device code (``cuda/gemm.cu``, ``cuda/gemv.cu``), compiled unmodified for sm_100 by
+``oracle/Makefile`` (target ``ref``) and run on a B200 by ``tests/golden/make_golden.py``; its
+outputs on seeded inputs are committed under ``tests/golden/`` and ``tests/test_oracle_golden.py``
+holds both restatements to them bit for bit.
+
+All fp16 tensors are ``np.float16`` arrays; int8 codes ``np.int8``; accumulators ``np.int32``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+# --------------------------------------------------------------------------------------------
+# numpy restatement
+# --------------------------------------------------------------------------------------------
+def _scale_from_amax(amax_f32: np.ndarray) -> np.ndarray:
+    """``__float2half(local_max / 127.0)``: double division, narrowed to float, then to half
+    (cuda/gemm.cu:74, :96)."""
+    return (amax_f32.astype(np.float64) / 127.0).astype(np.float32).astype(np.float16)
+
+
+def _absmax(x_f32: np.ndarray, axis: int) -> np.ndarray:
+    """``fmaxf(fabsf(x), running)`` starting from 0: NaN elements are dropped (fmaxf returns the
+    non-NaN operand), as in cuda/gemm.cu:67-69."""
+    a = np.abs(x_f32)
+    a = np.where(np.isnan(a), np.float32(0), a)
+    return a.max(axis=axis, initial=np.float32(0)).astype(np.float32)
+
+
+def cast_i8(v_f32: np.ndarray) -> np.ndarray:
+    """float -> int8 as the reference's sm_100 build performs it: saturating round-toward-zero
+    conversion to a 16-bit integer (NaN -> 0), low byte kept.  Equal to the C cast wherever that
+    is defined (|v| <= 127)."""
+    v = np.asarray(v_f32, dtype=np.float32)
+    t = np.trunc(np.where(np.isnan(v), np.float32(0), v))
+    w = np.clip(t, -32768.0, 32767.0).astype(np.int32)
+    return (w & 0xFF).astype(np.uint8).view(np.int8)
+
+
+def gemm_calc_scale(mat: np.ndarray) -> np.ndarray:
+    """cuda/gemm.cu:60-76.  mat (batch, n, m) fp16 -> (batch, n) fp16."""
+    assert mat.dtype == np.float16 and mat.ndim == 3
+    return _scale_from_amax(_absmax(mat.astype(np.float32), axis=2))
+
+
+def gemm_calc_scale_transpose(mat: np.ndarray) -> np.ndarray:
+    """cuda/gemm.cu:79-98.  mat (batch, n, m) fp16 -> (batch, m) fp16 (reduction over n)."""
+    assert mat.dtype == np.float16 and mat.ndim == 3
+    return _scale_from_amax(_absmax(mat.astype(np.float32), axis=1))
+
+
+def _round_div(x_f32: np.ndarray, s_f32: np.ndarray) -> np.ndarray:
+    with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
+        q = x_f32 / s_f32                      # IEEE binary32 division, round to nearest even
+        return cast_i8(np.rint(q))             # nearbyintf: round half to even
+
+
+def gemm_round(mat: np.ndarray, scale: np.ndarray) -> np.ndarray:
+    """cuda/gemm.cu:6-18.  mat (batch, n, m), scale (batch, n) -> int8 (batch, n, m)."""
+    assert mat.dtype == np.float16 and scale.dtype == np.float16
+    return _round_div(mat.astype(np.float32), scale.astype(np.float32)[:, :, None])
+
+
+def gemm_round_transpose(mat: np.ndarray, scale: np.ndarray) -> np.ndarray:
+    """cuda/gemm.cu:22-33.  mat (batch, n, m), scale (batch, m) -> int8 (batch, n, m)."""
+    assert mat.dtype == np.float16 and scale.dtype == np.float16
+    return _round_div(mat.astype(np.float32), scale.astype(np.float32)[:, None, :])
+
+
+def gemm_int8(m: int, k: int, n: int, aT: bool, bT: bool, A: np.ndarray, B: np.ndarray) -> np.ndarray:
+    """cpm_kernels/kernels/gemm.py:127-186.  A (bA, k, m) or (bA, m, k) if aT; B (bB, n, k) or
+    (bB, k, n) if bT; returns int32 (max(bA, bB), n, m) with out[b,j,i] = sum_l Aop[b,l,i]*Bop[b,j,l].
+    Computed in float64 (exact: |sum| <= 128*128*k < 2**53)."""
+    assert A.dtype == np.int8 and B.dtype == np.int8
+    a_km = A.transpose(0, 2, 1) if aT else A                  # (bA, k, m)
+    b_nk = B.transpose(0, 2, 1) if bT else B                  # (bB, n, k)
+    assert a_km.shape[1:] == (k, m) and b_nk.shape[1:] == (n, k)
+    assert A.shape[0] == B.shape[0] or A.shape[0] == 1 or B.shape[0] == 1
+    out = np.matmul(b_nk.astype(np.float64), a_km.astype(np.float64))
+    return np.rint(out).astype(np.int32)
+
+
+def gemm_scale(mat: np.ndarray, scale_x: np.ndarray, scale_y: np.ndarray,
+               broad_cast_x: bool, broad_cast_y: bool) -> np.ndarray:
+    """cuda/gemm.cu:37-57.  mat int32 (batch, n, m); scale_x (batch or 1, n); scale_y (batch or 1, m).
+    out = half(((float)mat * sx) * sy), the two multiplies in binary32, left to right."""
+    assert mat.dtype == np.int32
+    sx = scale_x.astype(np.float32).reshape(-1, mat.shape[1])
+    sy = scale_y.astype(np.float32).reshape(-1, mat.shape[2])
+    sx = sx[0:1] if broad_cast_x else sx
+    sy = sy[0:1] if broad_cast_y else sy
+    with np.errstate(over="ignore", invalid="ignore"):
+        v = mat.astype(np.float32) * sx[:, :, None]
+        v = v * sy[:, None, :]
+        return v.astype(np.float16)
+
+
+def gemm_scale_x(mat: np.ndarray, scale_x: np.ndarray) -> np.ndarray:
+    """cuda/gemm.cu:176-189."""
+    with np.errstate(over="ignore"):
+        return (scale_x.astype(np.float32)[:, :, None] * mat.astype(np.float32)).astype(np.float16)
+
+
+def gemm_scale_y(mat: np.ndarray, scale_y: np.ndarray) -> np.ndarray:
+    """cuda/gemm.cu:192-205."""
+    with np.errstate(over="ignore"):
+        return (mat.astype(np.float32) * scale_y.astype(np.float32)[:, None, :]).astype(np.float16)
+
+
+def gemm_backward_round_scale(mat: np.ndarray, scale_y: np.ndarray, broad_cast_y: bool):
+    """cuda/gemm.cu:103-134.  Returns (codes int8 (b,n,m), scale_x fp16 (b,n)).  The divisor of the
+    rounding step is the float scale *before* it is narrowed to fp16."""
+    sy = scale_y.astype(np.float32).reshape(-1, mat.shape[2])
+    sy = sy[0:1] if broad_cast_y else sy
+    v = mat.astype(np.float32) * sy[:, None, :]
+    s = (_absmax(v, axis=2).astype(np.float64) / 127.0).astype(np.float32)
+    return _round_div(v, s[:, :, None]), s.astype(np.float16)
+
+
+def gemm_backward_scale_round(mat: np.ndarray, scale_x: np.ndarray, broad_cast_x: bool):
+    """cuda/gemm.cu:137-172.  Returns (codes int8 (b,n,m), scale_y fp16 (b,m))."""
+    sx = scale_x.astype(np.float32).reshape(-1, mat.shape[1])
+    sx = sx[0:1] if broad_cast_x else sx
+    v = mat.astype(np.float32) * sx[:, :, None]
+    s = (_absmax(v, axis=1).astype(np.float64) / 127.0).astype(np.float32)
+    return _round_div(v, s[:, None, :]), s.astype(np.float16)
+
+
+def gemv_fp16(mat: np.ndarray, vec: np.ndarray) -> np.ndarray:
+    """cuda/gemv.cu:79-106 / kernels/gemv.py:82-127.  mat (batch, dim_out, dim_in), vec (batch, dim_in);
+    returns the exact sums in float64 (batch, dim_out).  The reference's own two implementations differ
+    in accumulation order and precision; its tests pin them to 1e-3 (tests/test_gemv.py:81)."""
+    return np.einsum("boi,bi->bo", mat.astype(np.float64), vec.astype(np.float64))
+
+
+def gemv_fp16_transpose(mat: np.ndarray, vec: np.ndarray) -> np.ndarray:
+    """cuda/gemv.cu:109-135.  mat (batch, dim_in, dim_out), vec (batch, dim_in) -> float64 (batch, dim_out)."""
+    return np.einsum("bio,bi->bo", mat.astype(np.float64), vec.astype(np.float64))
+
+
+def gemv_broadcast_mat_fp16(mat: np.ndarray, vec: np.ndarray) -> np.ndarray:
+    """cuda/gemv.cu:138-164.  mat (dim_out, dim_in) shared, vec (batch, dim_in) -> float64 (batch, dim_out)."""
+    return vec.astype(np.float64) @ mat.astype(np.float64).T
+
+
+def gemv_broadcast_mat_int8(scale_mat, mat, scale_vec, vec) -> np.ndarray:
+    """cuda/gemv.cu:57-76.  out[b,o] = half(((float)dot * scale_vec[b]) * scale_mat[o])."""
+    acc = np.rint(vec.astype(np.float64) @ mat.astype(np.float64).T).astype(np.int32)
+    with np.errstate(over="ignore"):
+        v = acc.astype(np.float32) * scale_vec.astype(np.float32)[:, None]
+        v = v * scale_mat.astype(np.float32)[None, :]
+        return v.astype(np.float16)
+
+
+def bmm_int8(A: np.ndarray, aT: bool, B: np.ndarray, bT: bool):
+    """cpm_kernels/torch/gemm.py:86-113 GEMMInt8.forward, restated with the functions above.
+    A (bA, M, K) [or (bA, K, M) if aT], B (bB, K, N) [or (bB, N, K) if bT], fp16.
+    Returns dict with scale_A, quant_A, scale_B, quant_B, acc (int32), out (fp16 (b, M, N))."""
+    scale_A = gemm_calc_scale_transpose(A) if aT else gemm_calc_scale(A)
+    scale_B = gemm_calc_scale(B) if bT else gemm_calc_scale_transpose(B)
+    qA = gemm_round_transpose(A, scale_A) if aT else gemm_round(A, scale_A)
+    qB = gemm_round(B, scale_B) if bT else gemm_round_transpose(B, scale_B)
+    M = A.shape[2] if aT else A.shape[1]
+    K = A.shape[1] if aT else A.shape[2]
+    N = B.shape[1] if bT else B.shape[2]
+    # torch/gemm.py:45-52: operands swapped so that the (n, m) = (M, N) result is row-major C
+    acc = gemm_int8(N, K, M, bT, aT, qB, qA)
+    out = gemm_scale(acc, scale_A, scale_B, A.shape[0] == 1, B.shape[0] == 1)
+    return dict(scale_A=scale_A, quant_A=qA, scale_B=scale_B, quant_B=qB, acc=acc, out=out)
+
+
+# --------------------------------------------------------------------------------------------
+# C restatement (oracle/quant_linear.c) through ctypes
+# --------------------------------------------------------------------------------------------
+def build_c_oracle() -> str:
+    """Compile oracle/quant_linear.c (and, where a reference checkout is present, the reference's
+    own device code into oracle/_ref/) with oracle/Makefile; return the path of the C library."""
+    subprocess.run(["make", "-s", "-C", _HERE, "all"], check=True, stdout=subprocess.DEVNULL)
+    return os.path.join(_HERE, "_build", "libquant_linear_oracle.so")
+
+
+class COracle:
+    """ctypes view of oracle/quant_linear.c.  Arrays are numpy, C-contiguous."""
+
+    def __init__(self, path: str | None = None):
+        path = path or os.path.join(_HERE, "_build", "libquant_linear_oracle.so")
+        if not os.path.exists(path):
+            path = build_c_oracle()
+        self.lib = ctypes.CDLL(path)
+
+    @staticmethod
+    def _p(a: np.ndarray):
+        assert a.flags["C_CONTIGUOUS"]
+        return a.ctypes.data_as(ctypes.c_void_p)
+
+    def gemm_calc_scale(self, mat):
+        b, n, m = mat.shape
+        out = np.empty((b, n), np.float16)
+        self.lib.orc_gemm_calc_scale(b, n, m, self._p(mat), self._p(out))
+        return out
+
+    def gemm_calc_scale_transpose(self, mat):
+        b, n, m = mat.shape
+        out = np.empty((b, m), np.float16)
+        self.lib.orc_gemm_calc_scale_transpose(b, n, m, self._p(mat), self._p(out))
+        return out
+
+    def gemm_round(self, mat, scale):
+        b, n, m = mat.shape
+        out = np.empty((b, n, m), np.int8)
+        self.lib.orc_gemm_round(b, n, m, self._p(mat), self._p(scale), self._p(out))
+        return out
+
+    def gemm_round_transpose(self, mat, scale):
+        b, n, m = mat.shape
+        out = np.empty((b, n, m), np.int8)
+        self.lib.orc_gemm_round_transpose(b, n, m, self._p(mat), self._p(scale), self._p(out))
+        return out
+
+    def gemm_int8(self, m, k, n, aT, bT, A, B, threads: int | None = None):
+        bA, bB = A.shape[0], B.shape[0]
+        out = np.empty((max(bA, bB), n, m), np.int32)
+        threads = threads or min(os.cpu_count() or 1, max(1, n))
+        bounds = np.linspace(0, n, threads + 1).astype(int)
+
+        def run(t):
+            self.lib.orc_gemm_int8_rows(m, k, n, bA, bB, int(aT), int(bT), self._p(A), self._p(B),
+                                        self._p(out), int(bounds[t]), int(bounds[t + 1]))
+        with ThreadPoolExecutor(threads) as ex:
+            list(ex.map(run, range(threads)))
+        return out
+
+    def gemm_scale(self, mat, scale_x, scale_y, bx, by):
+        b, n, m = mat.shape
+        out = np.empty((b, n, m), np.float16)
+        self.lib.orc_gemm_scale(b, n, m, self._p(mat), self._p(scale_x), self._p(scale_y), self._p(out), int(bx), int(by))
+        return out
+
+    def gemm_scale_x(self, mat, scale_x):
+        b, n, m = mat.shape
+        out = np.empty((b, n, m), np.float16)
+        self.lib.orc_gemm_scale_x(b, n, m, self._p(mat), self._p(scale_x), self._p(out))
+        return out
+
+    def gemm_scale_y(self, mat, scale_y):
+        b, n, m = mat.shape
+        out = np.empty((b, n, m), np.float16)
+        self.lib.orc_gemm_scale_y(b, n, m, self._p(mat), self._p(scale_y), self._p(out))
+        return out
+
+    def gemm_backward_round_scale(self, mat, scale_y, by):
+        b, n, m = mat.shape
+        out = np.empty((b, n, m), np.int8)
+        sx = np.empty((b, n), np.float16)
+        self.lib.orc_gemm_backward_round_scale(b, n, m, self._p(mat), self._p(scale_y), self._p(out), self._p(sx), int(by))
+        return out, sx
+
+    def gemm_backward_scale_round(self, mat, scale_x, bx):
+        b, n, m = mat.shape
+        out = np.empty((b, n, m), np.int8)
+        sy = np.empty((b, m), np.float16)
+        self.lib.orc_gemm_backward_scale_round(b, n, m, self._p(mat), self._p(scale_x), self._p(out), self._p(sy), int(bx))
+        return out, sy
+
+    def gemv_fp16(self, mat, vec):
+        b, o, i = mat.shape
+        out = np.empty((b, o), np.float64)
+        self.lib.orc_gemv_fp16(b, o, i, self._p(mat), self._p(vec), self._p(out))
+        return out
+
+    def gemv_fp16_transpose(self, mat, vec):
+        b, i, o = mat.shape
+        out = np.empty((b, o), np.float64)
+        self.lib.orc_gemv_fp16_transpose(b, o, i, self._p(mat), self._p(vec), self._p(out))
+        return out
+
+    def gemv_broadcast_mat_fp16(self, mat, vec):
+        o, i = mat.shape
+        b = vec.shape[0]
+        out = np.empty((b, o), np.float64)
+        self.lib.orc_gemv_broadcast_mat_fp16(b, o, i, self._p(mat), self._p(vec), self._p(out))
+        return out
+
+    def gemv_broadcast_mat_int8(self, scale_mat, mat, scale_vec, vec):
+        o, i = mat.shape
+        b = vec.shape[0]
+        out = np.empty((b, o), np.float16)
+        self.lib.orc_gemv_broadcast_mat_int8(b, o, i, self._p(scale_mat), self._p(mat), self._p(scale_vec), self._p(vec), self._p(out))
+        return out
+
+    def round_one(self, x_bits: int, s_bits: int) -> int:
+        self.lib.orc_round_one.restype = ctypes.c_int8
+        return int(self.lib.orc_round_one(ctypes.c_uint16(x_bits), ctypes.c_uint16(s_bits)))
