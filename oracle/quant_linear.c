@@ -18,7 +18,7 @@
  * Out-of-domain casts.  `(int8_t)nearbyintf(x / s)` is undefined in C when the quotient is NaN,
  * infinite or outside [-128, 127] (an all-zero row gives 0/0; a scale that underflows to a
  * subnormal or zero gives huge quotients).  orc_cast_i8() restates what the reference's sm_100
- * build was observed to produce for those inputs (recorded in tests/golden/edge_cases.npz).
+ * build was observed to produce for those inputs (tests/golden/reference_sm100.npz, arrays c_*).
  */
 #include <math.h>
 #include <stdint.h>
@@ -41,17 +41,18 @@ static inline uint16_t f2h(float v) { /* round to nearest even, as __float2half 
 }
 
 /*
- * float -> int8 as the reference's compiled device code performs it: the float is converted to a
- * 16-bit integer with round-toward-zero and saturation (NaN -> 0) and the low byte is kept.
- * In the normal domain (|v| <= 127 after nearbyintf) this is the plain C cast.
+ * float -> int8 as the reference's compiled device code performs it (observed on its sm_100 build, recorded in
+ * tests/golden/reference_sm100.npz, arrays c_*): the float is converted to a 32-bit integer with
+ * round-toward-zero and saturation (NaN -> 0, +inf and anything >= 2^31 -> INT32_MAX, -inf -> INT32_MIN) and the
+ * low byte is kept.  In the normal domain (|v| <= 127 after nearbyintf) this is the plain C cast.
  */
 static inline int8_t orc_cast_i8(float v) {
     if (v != v) return 0;
-    float t = truncf(v);
-    int32_t w;
-    if (t >= 32767.0f) w = 32767;
-    else if (t <= -32768.0f) w = -32768;
-    else w = (int32_t)t;
+    double t = trunc((double)v);
+    int64_t w;
+    if (t >= 2147483647.0) w = 2147483647LL;
+    else if (t <= -2147483648.0) w = -2147483648LL;
+    else w = (int64_t)t;
     return (int8_t)(uint8_t)(w & 0xff);
 }
 

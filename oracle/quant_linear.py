@@ -47,12 +47,12 @@ def _absmax(x_f32: np.ndarray, axis: int) -> np.ndarray:
 
 
 def cast_i8(v_f32: np.ndarray) -> np.ndarray:
-    """float -> int8 as the reference's sm_100 build performs it: saturating round-toward-zero
-    conversion to a 16-bit integer (NaN -> 0), low byte kept.  Equal to the C cast wherever that
-    is defined (|v| <= 127)."""
-    v = np.asarray(v_f32, dtype=np.float32)
-    t = np.trunc(np.where(np.isnan(v), np.float32(0), v))
-    w = np.clip(t, -32768.0, 32767.0).astype(np.int32)
+    """float -> int8 as the reference's sm_100 build performs it (observed; tests/golden/reference_sm100.npz,
+    arrays c_*): saturating round-toward-zero conversion to a 32-bit integer (NaN -> 0), low byte kept.  Equal to
+    the C cast wherever that is defined (|v| <= 127)."""
+    v = np.asarray(v_f32, dtype=np.float32).astype(np.float64)
+    t = np.trunc(np.where(np.isnan(v), 0.0, v))
+    w = np.clip(t, -2147483648.0, 2147483647.0).astype(np.int64)
     return (w & 0xFF).astype(np.uint8).view(np.int8)
 
 

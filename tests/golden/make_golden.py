@@ -53,6 +53,17 @@ def main():
         out[key + "_codes_rows"] = qr.cpu().numpy()
         out[key + "_codes_cols"] = qc.cpu().numpy()
 
+    # out-of-range quotients: what (int8_t)nearbyintf(x / s) yields beyond [-128, 127], for inf and for NaN
+    cx = np.array([0.0, -0.0, 1.0, -1.0, 0.5, 1.5, 2.5, 127.0, 128.0, 129.0, 200.0, 255.0, 256.0, 300.0, 1000.0, -1000.0, 32768.0,
+                   40000.0, 65504.0, -65504.0, 3.0, 7.0, 100.0, -100.0, 1e-3, 6e-8, -6e-8, np.inf, -np.inf, np.nan, 12345.0, -12345.0],
+                  dtype=np.float16)
+    cs = np.array([1.0, 0.5, 0.25, 2.0 ** -8, 2.0 ** -10, 2.0 ** -14, 2.0 ** -16, 2.0 ** -20, 2.0 ** -24, 0.0, np.inf, np.nan, 3.0, 1e-3,
+                   65504.0, 7e-5], dtype=np.float16)
+    cxm = torch.from_numpy(np.tile(cx[None, None, :], (1, len(cs), 1)).copy())
+    csm = torch.from_numpy(cs[None, :].copy())
+    out["c_x"], out["c_s"] = u16(cxm), u16(csm)
+    out["c_codes"] = ref.gemm_round(cxm.cuda(), csm.cuda()).cpu().numpy()
+
     # dequantisation, both broadcast settings (cuda/gemm.cu:37-57)
     g = torch.Generator(device="cpu").manual_seed(104)
     acc = torch.randint(-2_000_000, 2_000_000, (2, 24, 40), generator=g, dtype=torch.int32)

@@ -33,12 +33,13 @@ def test_gemv_fp16(G, batch, dim_out, dim_in):
     mat = randn_fp16((batch, dim_out, dim_in), 1, 1.0 / ssk)
     vec = randn_fp16((batch, dim_in), 2, 1.0 / ssk)
     out = torch.full((batch, dim_out), 9.0, dtype=torch.half, device="cuda")
-    ck.gemv_fp16(batch, dim_out, dim_in, mat.cuda().data_ptr(), vec.cuda().data_ptr(), out.data_ptr(), G.stream())
+    md, vd = mat.cuda(), vec.cuda()
+    ck.gemv_fp16(batch, dim_out, dim_in, md.data_ptr(), vd.data_ptr(), out.data_ptr(), G.stream())
     want = ql.gemv_fp16(np16(mat), np16(vec))
     assert close(G.host(out), want)
     if dim_in % 2 == 0:
         out2 = torch.empty_like(out)
-        ck.gemv_fp16_light(batch, dim_out, dim_in, mat.cuda().data_ptr(), vec.cuda().data_ptr(), out2.data_ptr(), G.stream())
+        ck.gemv_fp16_light(batch, dim_out, dim_in, md.data_ptr(), vd.data_ptr(), out2.data_ptr(), G.stream())
         assert torch.equal(out, out2)
 
 
@@ -68,7 +69,8 @@ def test_gemv_broadcast_mat_fp16(G, batch, dim_out, dim_in):
     mat = randn_fp16((dim_out, dim_in), 5, 1.0 / ssk)
     vec = randn_fp16((batch, dim_in), 6, 1.0 / ssk)
     out = torch.full((batch, dim_out), 9.0, dtype=torch.half, device="cuda")
-    ck.gemv_broadcast_mat_fp16(batch, dim_out, dim_in, mat.cuda().data_ptr(), vec.cuda().data_ptr(), out.data_ptr(), G.stream())
+    md, vd = mat.cuda(), vec.cuda()
+    ck.gemv_broadcast_mat_fp16(batch, dim_out, dim_in, md.data_ptr(), vd.data_ptr(), out.data_ptr(), G.stream())
     assert close(G.host(out), ql.gemv_broadcast_mat_fp16(np16(mat), np16(vec)))
 
 

@@ -148,9 +148,10 @@ def test_dequant_single_scale_forms(G):
     sx = randn_fp16((2, 20), 4, 0.01).abs()
     sy = randn_fp16((2, 48), 5, 0.01).abs()
     accd, out = acc.cuda(), torch.empty((2, 20, 48), dtype=torch.half, device="cuda")
-    ck.gemm_scale_x(2, 20, 48, accd.data_ptr(), sx.cuda().data_ptr(), out.data_ptr(), G.stream())
+    sxd, syd = sx.cuda(), sy.cuda()
+    ck.gemm_scale_x(2, 20, 48, accd.data_ptr(), sxd.data_ptr(), out.data_ptr(), G.stream())
     assert G.same_bits(out, ql.gemm_scale_x(acc.numpy(), np16(sx)))
-    ck.gemm_scale_y(2, 20, 48, accd.data_ptr(), sy.cuda().data_ptr(), out.data_ptr(), G.stream())
+    ck.gemm_scale_y(2, 20, 48, accd.data_ptr(), syd.data_ptr(), out.data_ptr(), G.stream())
     assert G.same_bits(out, ql.gemm_scale_y(acc.numpy(), np16(sy)))
 
 
@@ -161,11 +162,12 @@ def test_backward_helpers_match_oracle(G):
     sx = randn_fp16((1, 20), 109, 0.01).abs() + 1e-3
     q = torch.empty((2, 20, 32), dtype=torch.int8, device="cuda")
     s = torch.empty((2, 20), dtype=torch.half, device="cuda")
-    ck.gemm_backward_round_scale(2, 20, 32, gr.cuda().data_ptr(), sy.cuda().data_ptr(), q.data_ptr(), s.data_ptr(), False, G.stream())
+    grd, syd, sxd = gr.cuda(), sy.cuda(), sx.cuda()
+    ck.gemm_backward_round_scale(2, 20, 32, grd.data_ptr(), syd.data_ptr(), q.data_ptr(), s.data_ptr(), False, G.stream())
     wq, ws = ql.gemm_backward_round_scale(np16(gr), np16(sy), False)
     assert (G.host(q) == wq).all() and G.same_bits(s, ws)
     s2 = torch.empty((2, 32), dtype=torch.half, device="cuda")
-    ck.gemm_backward_scale_round(2, 20, 32, gr.cuda().data_ptr(), sx.cuda().data_ptr(), q.data_ptr(), s2.data_ptr(), True, G.stream())
+    ck.gemm_backward_scale_round(2, 20, 32, grd.data_ptr(), sxd.data_ptr(), q.data_ptr(), s2.data_ptr(), True, G.stream())
     wq, ws = ql.gemm_backward_scale_round(np16(gr), np16(sx), True)
     assert (G.host(q) == wq).all() and G.same_bits(s2, ws)
 
