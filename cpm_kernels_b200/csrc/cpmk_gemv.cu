@@ -4,6 +4,8 @@
 // Replaces cuda/gemv.cu:57-164 of the reference (one block per output element with half2 accumulation;
 // 32x32 blocks reading 64-byte row segments for the transposed form) and the cublasLt n=1 GEMMs of
 // cpm_kernels/kernels/gemv.py:82-262.
+#include <mutex>
+
 #include "cpmk_common.cuh"
 
 namespace cpmk {
@@ -297,6 +299,35 @@ int32_t launch_gemv_rows(int32_t batch, int32_t dim_out, int32_t dim_in, const v
     return CPMK_OK;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of the transposed GEMV: its split partial sums and tickets live in a
+// file-scope device array instead of the library's cudaMalloc'ed workspace.
+// ------------------------------------------------------------------------------------------------
+constexpr size_t kStaticTicketBytes = 16 * 1024;
+constexpr size_t kStaticPartialBytes = 4u << 20;
+constexpr size_t kStaticScratchBytes = kStaticTicketBytes + kStaticPartialBytes;
+
+// [0, kStaticTicketBytes): tickets; [kStaticTicketBytes, end): fp32 partial sums.  One copy per GPU that loads
+// the library, held until the process exits.  In host code this name is only a handle for
+// cudaGetSymbolAddress; the device address it stands for is looked up once per device below.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+std::mutex g_static_mutex;
+unsigned char *g_static_ptr[64] = {nullptr};
+
+// Device address of g_static_scratch on the current device (looked up on the first call per device).
+int32_t static_scratch_address(int device, unsigned char **out) {
+    CPMK_REQUIRE(device >= 0 && device < 64, "device index %d out of range", device);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_ptr[device]) {
+        void *p = nullptr;
+        CPMK_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+        g_static_ptr[device] = static_cast<unsigned char *>(p);
+    }
+    *out = g_static_ptr[device];
+    return CPMK_OK;
+}
+
 }  // namespace
 }  // namespace cpmk
 
@@ -401,6 +432,52 @@ int32_t cpmk_gemv_broadcast_mat_int8(int32_t batch, int32_t dim_out, int32_t dim
         else { gemv_int8_kernel<1><<<blocks, kBlock, 0, st>>>(dim_out, dim_in, b, sm, w, sv, x, y, vec16); b += 1; }
         CPMK_LAUNCH_CHECK();
     }
+    return CPMK_OK;
+}
+
+int32_t cpmk_gemv_fp16_transpose_noalloc(int32_t batch, int32_t dim_out, int32_t dim_in, const void *mat, const void *vec, void *out,
+                                         cpmk_stream_t stream) {
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    rc = check_gemv(batch, dim_out, dim_in);
+    if (rc) return rc;
+    if ((int64_t)batch * dim_out == 0) return CPMK_OK;
+    CPMK_REQUIRE(mat && vec && out, "null tensor pointer");
+    CPMK_REQUIRE(dim_in > 0, "dim_in must be positive");
+    CPMK_REQUIRE(dim_out % 8 == 0 && aligned16(mat), "the allocation-free GEMV needs dim_out %% 8 == 0 and a 16-byte aligned matrix");
+    CPMK_REQUIRE(batch <= 65535, "batch %d exceeds 65535", batch);
+    const int strips = (dim_out + kTStripCols - 1) / kTStripCols;
+    // the fixed scratch must hold at least two row chunks of partial sums and one ticket per (batch, strip)
+    if ((size_t)batch * strips * sizeof(uint32_t) > kStaticTicketBytes ||
+        2 * sizeof(float) * (size_t)batch * (size_t)dim_out > kStaticPartialBytes) {
+        set_error("cpmk_gemv_fp16_transpose_noalloc: batch * dim_out = %lld exceeds the fixed scratch (limit: batch * dim_out <= %zu "
+                  "and batch * ceil(dim_out / 256) <= %zu); use cpmk_gemv_fp16_transpose",
+                  (long long)batch * dim_out, kStaticPartialBytes / (2 * sizeof(float)), kStaticTicketBytes / sizeof(uint32_t));
+        return CPMK_ENOMEM;
+    }
+    unsigned char *scratch = nullptr;
+    rc = static_scratch_address(info.device, &scratch);
+    if (rc) return rc;
+    cudaStream_t st = as_stream(stream);
+    int64_t splits = ((int64_t)info.sm_count * 6) / ((int64_t)strips * batch);
+    const int64_t max_by_rows = (dim_in + 63) / 64;
+    if (splits > max_by_rows) splits = max_by_rows;
+    const int64_t max_by_scratch = (int64_t)(kStaticPartialBytes / (sizeof(float) * (size_t)batch * (size_t)dim_out));
+    if (splits > max_by_scratch) splits = max_by_scratch;
+    if (splits > 65535) splits = 65535;
+    if (splits < 1) splits = 1;
+    int rps = (int)((dim_in + splits - 1) / splits);
+    rps = (rps + kWarps - 1) / kWarps * kWarps;
+    const int nsplit = (dim_in + rps - 1) / rps;
+    uint32_t *tickets = reinterpret_cast<uint32_t *>(scratch);
+    float *partial = reinterpret_cast<float *>(scratch + kStaticTicketBytes);
+    // the array keeps whatever the previous call left: the tickets this call counts on must start at zero
+    if (nsplit > 1) CPMK_CUDA_TRY(cudaMemsetAsync(tickets, 0, (size_t)batch * strips * sizeof(uint32_t), st));
+    const dim3 grid(strips, nsplit, batch);
+    gemv_transpose_kernel<<<grid, kBlock, 0, st>>>(dim_out, dim_in, rps, nsplit, static_cast<const __half *>(mat),
+                                                   static_cast<const __half *>(vec), static_cast<__half *>(out), partial, tickets);
+    CPMK_LAUNCH_CHECK();
     return CPMK_OK;
 }
 

@@ -41,6 +41,7 @@ SIGNATURES = {
     "cpmk_gemm_int8_dequant": [_i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p, _p],
     "cpmk_gemv_fp16": [_i, _i, _i, _p, _p, _p, _p],
     "cpmk_gemv_fp16_transpose": [_i, _i, _i, _p, _p, _p, _p],
+    "cpmk_gemv_fp16_transpose_noalloc": [_i, _i, _i, _p, _p, _p, _p],
     "cpmk_gemv_broadcast_mat_fp16": [_i, _i, _i, _p, _p, _p, _p],
     "cpmk_gemv_calc_scale": [_i, _i, _p, _p, _p],
     "cpmk_gemv_round": [_i, _i, _p, _p, _p, _p],

@@ -125,6 +125,19 @@ int32_t cpmk_gemv_fp16(int32_t batch, int32_t dim_out, int32_t dim_in, const voi
  * mat (batch, dim_in, dim_out).  Uses the library workspace for split partial sums. */
 int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in, const void *mat, const void *vec, void *out, cpmk_stream_t stream);
 
+/* No counterpart in the reference.  Same result as cpmk_gemv_fp16_transpose, for callers that must not trigger a
+ * device allocation: serving processes that hand the whole GPU to their own memory pool at start-up (a later
+ * cudaMalloc would fail or stall them), code that runs where allocation calls are forbidden by the host
+ * application, and latency-critical loops that cannot afford the device-wide synchronisation an allocation implies.  The split partial sums and the
+ * tickets that combine them live in a fixed 4 MiB + 16 KiB array inside the library's device image instead of the
+ * library workspace; nothing is allocated or freed, by this call or by anything it uses.
+ *   Limits: dim_out % 8 == 0, mat 16-byte aligned, batch * dim_out <= 524288 and batch * ceil(dim_out / 256) <= 4096;
+ *   beyond them the call returns CPMK_ENOMEM with a message and does nothing.
+ *   The first call on each device looks up the array's device address; make that call before any stream capture.
+ *   All calls on a device share the one array: two calls that overlap on the GPU (different streams) race. */
+int32_t cpmk_gemv_fp16_transpose_noalloc(int32_t batch, int32_t dim_out, int32_t dim_in, const void *mat, const void *vec, void *out,
+                                         cpmk_stream_t stream);
+
 /* kernels/gemv.py:218-283 gemv_broadcast_mat_fp16 / _light -> cuda/gemv.cu:138-164.
  * mat (dim_out, dim_in) shared by all `batch` vectors. */
 int32_t cpmk_gemv_broadcast_mat_fp16(int32_t batch, int32_t dim_out, int32_t dim_in, const void *mat, const void *vec, void *out, cpmk_stream_t stream);
