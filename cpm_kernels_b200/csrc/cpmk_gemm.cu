@@ -15,6 +15,7 @@
 // raises its abort flag, lets copies in flight land, frees its tensor memory and returns.
 #include <cuda.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include <mutex>
 
@@ -179,6 +180,71 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
+// One epilogue warp's share of a finished accumulator: TMEM lanes [32*quarter, 32*quarter+32) = output rows
+// row_base + 32*quarter + lane, all kBN columns from col_base, 32 columns per tcgen05.ld.
+template <bool DEQUANT>
+__device__ __forceinline__ void epilogue_rows(const GemmParams &prm, uint32_t tmem_base, uint32_t acc, int quarter, int lane, int b,
+                                              int row_base, int col_base) {
+    const int row = row_base + quarter * 32 + lane;
+    const bool row_ok = row < prm.R;
+    const int64_t out_row = ((int64_t)b * prm.R + (row_ok ? row : 0)) * prm.C;
+    float sr = 0.f;
+    if (DEQUANT && row_ok) sr = __half2float(__ldg(prm.scale_r + (prm.bcast_r ? 0 : (int64_t)b * prm.R) + row));
+    const __half *sc = DEQUANT ? prm.scale_c + (prm.bcast_c ? 0 : (int64_t)b * prm.C) : nullptr;
+#pragma unroll 1
+    for (int chunk = 0; chunk < kBN / 32; ++chunk) {
+        const int col0 = col_base + chunk * 32;
+        if (col0 >= prm.C) break;                    // uniform across the warp
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN + chunk * 32, v);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        if (DEQUANT) {
+            __half *dst = static_cast<__half *>(prm.out) + out_row + col0;
+            if ((prm.C & 7) == 0) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    if (col0 + g * 8 < prm.C) {
+                        const uint4 s8 = __ldg(reinterpret_cast<const uint4 *>(sc + col0 + g * 8));
+                        const __half2 *sh = reinterpret_cast<const __half2 *>(&s8);
+                        uint4 o;
+                        uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 s2 = __half22float2(sh[e]);
+                            const float a0 = __fmul_rn(__fmul_rn((float)(int32_t)v[g * 8 + 2 * e], sr), s2.x);
+                            const float a1 = __fmul_rn(__fmul_rn((float)(int32_t)v[g * 8 + 2 * e + 1], sr), s2.y);
+                            ow[e] = pack_half2(a0, a1);
+                        }
+                        *reinterpret_cast<uint4 *>(dst + g * 8) = o;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    if (col0 + e < prm.C) {
+                        const float a = __fmul_rn(__fmul_rn((float)(int32_t)v[e], sr), __half2float(__ldg(sc + col0 + e)));
+                        dst[e] = __float2half_rn(a);
+                    }
+                }
+            }
+        } else {
+            int32_t *dst = static_cast<int32_t *>(prm.out) + out_row + col0;
+            if ((prm.C & 3) == 0) {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    if (col0 + g * 4 < prm.C)
+                        *reinterpret_cast<uint4 *>(dst + g * 4) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e)
+                    if (col0 + e < prm.C) dst[e] = (int32_t)v[e];
+            }
+        }
+    }
+}
+
 template <bool DEQUANT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, const GemmParams prm) {
@@ -275,64 +341,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_const
             const int c_blk = rem / prm.tiles_r, r_blk = rem - c_blk * prm.tiles_r;
             if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, prm.status, kErrEpilogueWait)) break;
             tcgen05_fence_after();
-            const int row = r_blk * kBM + quarter * 32 + lane;
-            const bool row_ok = row < prm.R;
-            const int64_t out_row = ((int64_t)b * prm.R + (row_ok ? row : 0)) * prm.C;
-            float sr = 0.f;
-            if (DEQUANT && row_ok) sr = __half2float(__ldg(prm.scale_r + (prm.bcast_r ? 0 : (int64_t)b * prm.R) + row));
-            const __half *sc = DEQUANT ? prm.scale_c + (prm.bcast_c ? 0 : (int64_t)b * prm.C) : nullptr;
-#pragma unroll 1
-            for (int chunk = 0; chunk < kBN / 32; ++chunk) {
-                const int col0 = c_blk * kBN + chunk * 32;
-                if (col0 >= prm.C) break;                    // uniform across the warp
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN + chunk * 32, v);
-                tmem_ld_wait();
-                if (!row_ok) continue;
-                if (DEQUANT) {
-                    __half *dst = static_cast<__half *>(prm.out) + out_row + col0;
-                    if ((prm.C & 7) == 0) {
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            if (col0 + g * 8 < prm.C) {
-                                const uint4 s8 = __ldg(reinterpret_cast<const uint4 *>(sc + col0 + g * 8));
-                                const __half2 *sh = reinterpret_cast<const __half2 *>(&s8);
-                                uint4 o;
-                                uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const float2 s2 = __half22float2(sh[e]);
-                                    const float a0 = __fmul_rn(__fmul_rn((float)(int32_t)v[g * 8 + 2 * e], sr), s2.x);
-                                    const float a1 = __fmul_rn(__fmul_rn((float)(int32_t)v[g * 8 + 2 * e + 1], sr), s2.y);
-                                    ow[e] = pack_half2(a0, a1);
-                                }
-                                *reinterpret_cast<uint4 *>(dst + g * 8) = o;
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            if (col0 + e < prm.C) {
-                                const float a = __fmul_rn(__fmul_rn((float)(int32_t)v[e], sr), __half2float(__ldg(sc + col0 + e)));
-                                dst[e] = __float2half_rn(a);
-                            }
-                        }
-                    }
-                } else {
-                    int32_t *dst = static_cast<int32_t *>(prm.out) + out_row + col0;
-                    if ((prm.C & 3) == 0) {
-#pragma unroll
-                        for (int g = 0; g < 8; ++g) {
-                            if (col0 + g * 4 < prm.C)
-                                *reinterpret_cast<uint4 *>(dst + g * 4) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-                        }
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 32; ++e)
-                            if (col0 + e < prm.C) dst[e] = (int32_t)v[e];
-                    }
-                }
-            }
+            epilogue_rows<DEQUANT>(prm, tmem_base, acc, quarter, lane, b, r_blk * kBM, c_blk * kBN);
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty_bar + 8 * acc);
@@ -353,6 +362,191 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_const
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Two-CTA form: a cluster of two CTAs on neighbouring SMs computes a 256 x 256 output tile with
+// tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of the row operand and 128 of the 256 rows of
+// the column operand (the tensor cores of the pair read both halves), so per MMA a CTA's shared memory serves
+// 8 KiB instead of 12 KiB and receives 8 KiB instead of 12 KiB from TMA: the shared-memory port stops being
+// the limiter.  Stages shrink to 32 KiB, so the ring holds 6 of them.
+//   - both CTAs run a producer warp; every load signals the full barrier of CTA 0 (the leader), whose producer
+//     posts the expected byte count of both CTAs;
+//   - only the leader issues MMAs; its commits arrive on the empty / accumulator-full barriers of both CTAs;
+//   - the epilogue warps of both CTAs arrive on the leader's accumulator-empty barrier.
+// ------------------------------------------------------------------------------------------------
+constexpr int kStages2 = 6;
+constexpr int kHalfBN = kBN / 2;                       // rows of the column operand staged per CTA
+constexpr int kQBytes2 = kHalfBN * kBK;                // 16 KiB
+constexpr int kStageBytes2 = kPBytes + kQBytes2;       // 32 KiB
+constexpr int kTc2SmemBytes = kStages2 * kStageBytes2 + 1024 + kBarrierBytes;
+constexpr uint32_t kInstrDesc2 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)((2 * kBM) >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load issued by one CTA of a pair; the completion bytes go to `bar`, a shared::cluster barrier address
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int32_t c0, int32_t c1, int32_t c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives on the barrier at offset `bar` in every CTA of `cta_mask` once the MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(cta_mask) : "memory");
+}
+
+template <bool DEQUANT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
+gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, const GemmParams prm) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars_base = tiles_base + kStages2 * kStageBytes2;
+    const uint32_t full_bar = bars_base;                          // used in the leader only
+    const uint32_t empty_bar = bars_base + 8 * kStages2;
+    const uint32_t tmem_full_bar = bars_base + 16 * kStages2;
+    const uint32_t tmem_empty_bar = tmem_full_bar + 16;           // used in the leader only
+    uint8_t *bars_generic = smem_raw + (bars_base - smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars_generic + 16 * kStages2 + 32);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages2; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tmem_full_bar + 8 * a, 1);
+            mbar_init(tmem_empty_bar + 8 * a, 8);      // four epilogue warps in each of the two CTAs
+        }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc_pair(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
+    tcgen05_fence_before();
+    cluster_sync_all();                                // barriers of both CTAs are initialised before anyone signals them
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int tiles_per_batch = prm.tiles_r * prm.tiles_c;   // in 256 x 256 pair tiles
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool alive = true;
+            for (int tile = pair; alive && tile < prm.total_tiles; tile += num_pairs) {
+                const int b = tile / tiles_per_batch;
+                const int rem = tile - b * tiles_per_batch;
+                const int c_blk = rem / prm.tiles_r, r_blk = rem - c_blk * prm.tiles_r;
+                const int row0 = r_blk * (2 * kBM) + (int)rank * kBM;
+                const int col0 = c_blk * kBN + (int)rank * kHalfBN;
+                for (int kb = 0; kb < prm.num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, prm.status, kErrProducerWait)) { alive = false; break; }
+                    const uint32_t p_dst = tiles_base + stage * kStageBytes2;
+                    if (leader) mbar_expect_tx(full_bar + 8 * stage, 2 * kStageBytes2);
+                    const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
+                    tma_load_3d_pair(p_dst, &tmap_p, kb * kBK, row0, prm.p_batched ? b : 0, leader_full);
+                    tma_load_3d_pair(p_dst + kPBytes, &tmap_q, kb * kBK, col0, prm.q_batched ? b : 0, leader_full);
+                    if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (leader && lane == 0) {
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool alive = true;
+            for (int tile = pair; alive && tile < prm.total_tiles; tile += num_pairs) {
+                if (!mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, prm.status, kErrMmaWaitTmem)) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * kBN;
+                for (int kb = 0; kb < prm.num_kb; ++kb) {
+                    if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, prm.status, kErrMmaWaitFull)) { alive = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t p_src = tiles_base + stage * kStageBytes2;
+                    const uint64_t p_desc = make_kmajor_sw128_desc(p_src);
+                    const uint64_t q_desc = make_kmajor_sw128_desc(p_src + kPBytes);
+#pragma unroll
+                    for (int j = 0; j < kBK / kUmmaK; ++j)
+                        umma_i8_pair(d_tmem, p_desc + (uint64_t)(2 * j), q_desc + (uint64_t)(2 * j), kInstrDesc2, (kb | j) != 0 ? 1u : 0u);
+                    umma_commit_pair(empty_bar + 8 * stage, 3);
+                    if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+                }
+                if (!alive) break;
+                umma_commit_pair(tmem_full_bar + 8 * acc, 3);
+                acc ^= 1u;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ---------------- epilogue (both CTAs; each owns 128 of the tile's 256 rows) ----------------
+        const int quarter = warp & 3;
+        uint32_t acc = 0, acc_phase = 0;
+        for (int tile = pair; tile < prm.total_tiles; tile += num_pairs) {
+            const int b = tile / tiles_per_batch;
+            const int rem = tile - b * tiles_per_batch;
+            const int c_blk = rem / prm.tiles_r, r_blk = rem - c_blk * prm.tiles_r;
+            if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, prm.status, kErrEpilogueWait)) break;
+            tcgen05_fence_after();
+            epilogue_rows<DEQUANT>(prm, tmem_base, acc, quarter, lane, b, r_blk * (2 * kBM) + (int)rank * kBM, c_blk * kBN);
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(tmem_empty_bar + 8 * acc, 0));
+            acc ^= 1u;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    // ---------------- teardown: neither CTA may leave while its partner can still touch its memory ----------------
+    __syncwarp();
+    tcgen05_fence_before();
+    cluster_sync_all();
+    if (*abort_flag) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc_pair(tmem_base, kTmemCols);
     }
 }
 
@@ -484,14 +678,64 @@ bool encode_operand(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, 
 }
 
 thread_local int32_t g_last_path = 0;
+thread_local int32_t g_last_variant = 0;
 
-bool force_generic() {
-    static int cached = -1;
-    if (cached < 0) {
-        const char *e = getenv("CPMK_FORCE_GENERIC_GEMM");
-        cached = (e && e[0] && e[0] != '0') ? 1 : 0;
+// CPMK_GEMM_VARIANT = auto (default) | 1cta | 2cta | generic; CPMK_FORCE_GENERIC_GEMM=1 is the same as "generic"
+enum { kVariantAuto = 0, kVariantOneCta = 1, kVariantTwoCta = 2, kVariantGeneric = 3 };
+int gemm_variant() {
+    const char *e = getenv("CPMK_GEMM_VARIANT");
+    if (e) {
+        if (!strcmp(e, "1cta")) return kVariantOneCta;
+        if (!strcmp(e, "2cta")) return kVariantTwoCta;
+        if (!strcmp(e, "generic")) return kVariantGeneric;
     }
-    return cached == 1;
+    const char *f = getenv("CPMK_FORCE_GENERIC_GEMM");
+    if (f && f[0] && f[0] != '0') return kVariantGeneric;
+    return kVariantAuto;
+}
+
+// Opt-in shared memory for the tensor-core kernels and the number of CTA pairs that can be resident at once
+// (a persistent grid must not exceed it); once per device.
+int g_max_pairs[64] = {0};
+std::once_flag g_prepare_once[64];
+cudaError_t g_prepare_err[64];
+
+int32_t prepare_tc_kernels(int device) {
+    const int dev = device & 63;
+    std::call_once(g_prepare_once[dev], [dev] {
+        cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_i8_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_i8_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTc2SmemBytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_i8_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTc2SmemBytes);
+        g_prepare_err[dev] = e;
+        if (e != cudaSuccess) return;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2, 1, 1);
+        cfg.blockDim = dim3(kTcThreads, 1, 1);
+        cfg.dynamicSmemBytes = kTc2SmemBytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_i8_tc2_kernel<true>, &cfg) == cudaSuccess && clusters > 0) {
+            g_max_pairs[dev] = clusters;
+        } else {
+            // the query is advisory: a pair that is not resident at launch simply starts when a pair retires
+            int sms = 0;
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            g_max_pairs[dev] = sms / 2;
+        }
+        (void)cudaGetLastError();
+    });
+    if (g_prepare_err[dev] != cudaSuccess) {
+        set_error("cudaFuncSetAttribute(max dynamic shared memory) failed: %s", cudaGetErrorString(g_prepare_err[dev]));
+        return CPMK_ECUDA;
+    }
+    return CPMK_OK;
 }
 
 template <bool DEQUANT>
@@ -517,46 +761,53 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
     CPMK_REQUIRE((reinterpret_cast<uintptr_t>(A) & 3u) == 0 && (reinterpret_cast<uintptr_t>(B) & 3u) == 0, "operands must be 4-byte aligned");
     if (DEQUANT) CPMK_REQUIRE(scale_x && scale_y, "null scale pointer");
 
-    // tensor-core path: both operands contiguous along k, TMA-compatible strides and addresses
-    const int64_t tiles_r = (n + kBM - 1) / kBM, tiles_c = (m + kBN - 1) / kBN;
-    const int64_t total_tiles = tiles_r * tiles_c * batch;
-    bool tc = aT && !bT && !force_generic() && k % 16 == 0 && aligned16(A) && aligned16(B) && aligned16(out) &&
-              total_tiles < (int64_t(1) << 31) && (!DEQUANT || aligned16(scale_y)) && info.max_smem_optin >= kTcSmemBytes;
-    CUtensorMap tmap_p, tmap_q;
-    if (tc) {
-        // rows of the output come from B (n x k), columns from A (m x k)
-        tc = encode_operand(&tmap_p, B, n, k, batchB, kBM) && encode_operand(&tmap_q, A, m, k, batchA, kBN);
-    }
-    if (tc) {
-        static std::once_flag attr_once[64];
-        static cudaError_t attr_err[64];
-        const int dev = info.device & 63;
-        std::call_once(attr_once[dev], [dev] {
-            cudaError_t e1 = cudaFuncSetAttribute(gemm_i8_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
-            cudaError_t e2 = cudaFuncSetAttribute(gemm_i8_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
-            attr_err[dev] = e1 != cudaSuccess ? e1 : e2;
-        });
-        if (attr_err[dev] != cudaSuccess) {
-            set_error("cudaFuncSetAttribute(max dynamic shared memory) failed: %s", cudaGetErrorString(attr_err[dev]));
-            return CPMK_ECUDA;
-        }
+    // tensor-core paths: both operands contiguous along k, TMA-compatible strides and addresses
+    const int variant = gemm_variant();
+    const bool tc_ok = aT && !bT && variant != kVariantGeneric && k % 16 == 0 && aligned16(A) && aligned16(B) && aligned16(out) &&
+                       (!DEQUANT || aligned16(scale_y)) && info.max_smem_optin >= kTcSmemBytes;
+    if (tc_ok) {
         Workspace ws;
         rc = get_workspace(stream, &ws);
         if (rc) return rc;
         GemmParams prm;
         prm.R = n; prm.C = m; prm.K = k; prm.batch = batch;
         prm.p_batched = batchB > 1; prm.q_batched = batchA > 1;
-        prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.num_kb = (k + kBK - 1) / kBK;
-        prm.total_tiles = (int32_t)total_tiles;
+        prm.num_kb = (k + kBK - 1) / kBK;
         prm.out = out;
         prm.scale_r = static_cast<const __half *>(scale_x); prm.scale_c = static_cast<const __half *>(scale_y);
         prm.bcast_r = bx; prm.bcast_c = by;
         prm.status = ws.status();
-        const int grid = (int)(total_tiles < info.sm_count ? total_tiles : info.sm_count);
-        gemm_i8_tc_kernel<DEQUANT><<<grid, kTcThreads, kTcSmemBytes, stream>>>(tmap_p, tmap_q, prm);
-        CPMK_LAUNCH_CHECK();
-        g_last_path = 1;
-        return CPMK_OK;
+        rc = prepare_tc_kernels(info.device);
+        if (rc) return rc;
+        CUtensorMap tmap_p, tmap_q;
+        // ---- two-CTA form: 256 x 256 tiles per CTA pair; worth it once there is more than one 128-row block ----
+        const int max_pairs = g_max_pairs[info.device & 63];
+        if (variant != kVariantOneCta && max_pairs > 0 && (n > kBM || variant == kVariantTwoCta)) {
+            const int64_t tiles_r = (n + 2 * kBM - 1) / (2 * kBM), tiles_c = (m + kBN - 1) / kBN;
+            const int64_t total = tiles_r * tiles_c * batch;
+            // rows of the output come from B (n x k), columns from A (m x k); each CTA stages 128 rows of either
+            if (total < (int64_t(1) << 31) && encode_operand(&tmap_p, B, n, k, batchB, kBM) && encode_operand(&tmap_q, A, m, k, batchA, kHalfBN)) {
+                prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.total_tiles = (int32_t)total;
+                const int pairs = (int)(total < max_pairs ? total : max_pairs);
+                gemm_i8_tc2_kernel<DEQUANT><<<2 * pairs, kTcThreads, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, prm);
+                CPMK_LAUNCH_CHECK();
+                g_last_path = 1;
+                g_last_variant = 2;
+                return CPMK_OK;
+            }
+        }
+        const int64_t tiles_r = (n + kBM - 1) / kBM, tiles_c = (m + kBN - 1) / kBN;
+        const int64_t total_tiles = tiles_r * tiles_c * batch;
+        if (variant != kVariantTwoCta && total_tiles < (int64_t(1) << 31) && encode_operand(&tmap_p, B, n, k, batchB, kBM) &&
+            encode_operand(&tmap_q, A, m, k, batchA, kBN)) {
+            prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.total_tiles = (int32_t)total_tiles;
+            const int grid = (int)(total_tiles < info.sm_count ? total_tiles : info.sm_count);
+            gemm_i8_tc_kernel<DEQUANT><<<grid, kTcThreads, kTcSmemBytes, stream>>>(tmap_p, tmap_q, prm);
+            CPMK_LAUNCH_CHECK();
+            g_last_path = 1;
+            g_last_variant = 1;
+            return CPMK_OK;
+        }
     }
     const dim3 grid((m + kSimtTile - 1) / kSimtTile, (n + kSimtTile - 1) / kSimtTile, batch);
     CPMK_REQUIRE(grid.y <= 65535, "n = %d is too large for the generic kernel", n);
@@ -565,6 +816,7 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
                                                           static_cast<const __half *>(scale_y), bx, by);
     CPMK_LAUNCH_CHECK();
     g_last_path = 2;
+    g_last_variant = 0;
     return CPMK_OK;
 }
 
@@ -588,5 +840,7 @@ int32_t cpmk_gemm_int8_dequant(int32_t m, int32_t k, int32_t n, int32_t batchA, 
 }
 
 int32_t cpmk_last_gemm_path(void) { return g_last_path; }
+
+int32_t cpmk_last_gemm_variant(void) { return g_last_path == 1 ? g_last_variant : 0; }
 
 }  // extern "C"

@@ -34,21 +34,32 @@ __device__ __forceinline__ __half2 absmax8(const uint4 &v, __half2 m) {
 }
 
 // Rounds the 8 halves of `v` with one scale.  r_up is NaN when the scale is outside the rule's
-// domain, which sends every element to the reference expression.
+// domain, which sends every element to the reference expression.  The two roundings of each pair of
+// elements are one packed fp32 FMA each (fma.rn.f32x2).
 __device__ __forceinline__ uint2 round8_one_scale(const uint4 &v, float s, float r_up, float r_dn) {
     const __half2 *h = reinterpret_cast<const __half2 *>(&v);
-    uint32_t b[8];
-    int ok = 1;
+    const float2 ru = make_float2(r_up, r_up), rd = make_float2(r_dn, r_dn);
+    const float2 magic = make_float2(CPMK_ROUND_MAGIC, CPMK_ROUND_MAGIC);
+    float2 dn[4];
+    bool ok = true;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        float2 f = __half22float2(h[i]);
-        ok &= cpmk_round_pair(f.x, r_up, r_dn, &b[2 * i]);
-        ok &= cpmk_round_pair(f.y, r_up, r_dn, &b[2 * i + 1]);
+        const float2 f = __half22float2(h[i]);
+        const float2 up = __ffma2_rn(f, ru, magic);
+        dn[i] = __ffma2_rn(f, rd, magic);
+        ok = ok && (up.x == dn[i].x);
+        ok = ok && (up.y == dn[i].y);
+    }
+    uint32_t b[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        b[2 * i] = __float_as_uint(dn[i].x);
+        b[2 * i + 1] = __float_as_uint(dn[i].y);
     }
     if (!ok) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            float2 f = __half22float2(h[i]);
+            const float2 f = __half22float2(h[i]);
             b[2 * i] = (uint8_t)round_reference(f.x, s);
             b[2 * i + 1] = (uint8_t)round_reference(f.y, s);
         }
@@ -66,7 +77,7 @@ __device__ __forceinline__ uint2 round8_one_scale(const uint4 &v, float s, float
 // ------------------------------------------------------------------------------------------------
 template <int NV, int MODE>
 __global__ void __launch_bounds__(kBlock) quant_rows_kernel(int64_t rows, int32_t m, int group, const __half *__restrict__ mat,
-                                                            __half *__restrict__ scale, int8_t *__restrict__ out) {
+                                                                 __half *__restrict__ scale, int8_t *__restrict__ out) {
     __shared__ float warp_max[kBlock / 32];
     const int tid = threadIdx.x;
     const int rows_per_block = kBlock / group;
@@ -82,7 +93,6 @@ __global__ void __launch_bounds__(kBlock) quant_rows_kernel(int64_t rows, int32_
         const int idx = lane_in_row + j * group;
         v[j] = (row_ok && idx < nvec) ? __ldcs(src + idx) : make_uint4(0, 0, 0, 0);
     }
-
     __half2 m2 = __float2half2_rn(0.f);
 #pragma unroll
     for (int j = 0; j < NV; ++j) m2 = absmax8(v[j], m2);
@@ -107,11 +117,9 @@ __global__ void __launch_bounds__(kBlock) quant_rows_kernel(int64_t rows, int32_
         s = __half2float(sh);
     }
     if (MODE == 1) return;
-
     float r_up, r_dn;
     cpmk_round_prepare(s, &r_up, &r_dn);
     if (!(cpmk_scale_in_domain(s) && cpmk_round_domain_ok(local_max, r_up))) r_up = __int_as_float(0x7fc00000);
-
     uint2 *dst = reinterpret_cast<uint2 *>(out + (row_ok ? row : 0) * (int64_t)m);
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
@@ -268,19 +276,24 @@ __global__ void __launch_bounds__(kBlock) quant_cols_round_kernel(int32_t n, int
         const uint4 v = __ldcs(reinterpret_cast<const uint4 *>(base + (int64_t)r * m + col));
         const __half2 *h = reinterpret_cast<const __half2 *>(&v);
         uint32_t bits[8];
-        int ok = 1;
+        bool ok = true;
         uint32_t range = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float2 f = __half22float2(h[j]);
-            ok &= cpmk_round_pair(f.x, r_up[2 * j], r_dn[2 * j], &bits[2 * j]);
-            ok &= cpmk_round_pair(f.y, r_up[2 * j + 1], r_dn[2 * j + 1], &bits[2 * j + 1]);
+            const float2 magic = make_float2(CPMK_ROUND_MAGIC, CPMK_ROUND_MAGIC);
+            const float2 up = __ffma2_rn(f, make_float2(r_up[2 * j], r_up[2 * j + 1]), magic);
+            const float2 dn = __ffma2_rn(f, make_float2(r_dn[2 * j], r_dn[2 * j + 1]), magic);
+            ok = ok && (up.x == dn.x);
+            ok = ok && (up.y == dn.y);
+            bits[2 * j] = __float_as_uint(dn.x);
+            bits[2 * j + 1] = __float_as_uint(dn.y);
             if (SRC == 1) {
                 // a code is valid iff its pattern is 0x4B400000 + q with -128 <= q <= 127
                 range |= ((bits[2 * j] + 0x80u) ^ 0x4B400000u) | ((bits[2 * j + 1] + 0x80u) ^ 0x4B400000u);
             }
         }
-        if (SRC == 1) ok &= (range < 0x100u);
+        if (SRC == 1) ok = ok && (range < 0x100u);
         if (!ok) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -463,8 +476,10 @@ int32_t launch_quant_rows(int32_t batch, int32_t n, int32_t m, const void *mat, 
         return CPMK_OK;
     }
     const int nvec = m / 8;
+    // four vectors (32 elements) per thread where the row is long enough: measured best on B200 (fewer threads
+    // per row means fewer shuffle / barrier steps per byte, and more bytes in flight per thread)
     int group = 8;
-    while (group < 256 && group * 4 < nvec) group <<= 1;       // aim at <= 4 vectors per thread
+    while (group < 256 && group * 4 < nvec) group <<= 1;
     const int nv = (nvec + group - 1) / group;                  // 1..8
     const int rows_per_block = kBlock / group;
     const int64_t blocks = ceil_div64(rows, rows_per_block);
@@ -473,6 +488,7 @@ int32_t launch_quant_rows(int32_t batch, int32_t n, int32_t m, const void *mat, 
     if (nv <= 1) quant_rows_kernel<1, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
     else if (nv <= 2) quant_rows_kernel<2, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
     else if (nv <= 4) quant_rows_kernel<4, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
+    else if (nv <= 6) quant_rows_kernel<6, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
     else quant_rows_kernel<8, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
     CPMK_LAUNCH_CHECK();
     return CPMK_OK;

@@ -53,6 +53,7 @@ for _name, _args in SIGNATURES.items():
 lib.bind("cpmk_abi_version", [], c_int32)
 lib.bind("cpmk_last_error", [], c_char_p)
 lib.bind("cpmk_last_gemm_path", [], c_int32)
+lib.bind("cpmk_last_gemm_variant", [], c_int32)
 
 if lib.cpmk_abi_version() != ABI_VERSION:
     raise RuntimeError("%s has ABI version %d, this package expects %d" % (lib.path, lib.cpmk_abi_version(), ABI_VERSION))
@@ -86,6 +87,11 @@ def read_status() -> int:
     word = c_uint32(0)
     check_status(lib.cpmk_read_status(ctypes.byref(word)), "cpmk_read_status")
     return word.value
+
+
+def last_gemm_variant() -> int:
+    """1 = one-CTA tiles, 2 = CTA-pair tiles (cta_group::2), 0 = the generic kernel, for the last int8 GEMM of this thread."""
+    return lib.cpmk_last_gemm_variant()
 
 
 def last_gemm_path() -> int:

@@ -113,6 +113,11 @@ int32_t cpmk_gemm_int8_dequant(int32_t m, int32_t k, int32_t n, int32_t batchA, 
  * 1 = tcgen05 tensor-core kernel, 2 = generic SIMT kernel.  For tests and the benchmark. */
 int32_t cpmk_last_gemm_path(void);
 
+/* Which form of the tensor-core kernel that call used: 1 = one CTA per 128 x 256 tile, 2 = CTA pairs on 256 x 256
+ * tiles (tcgen05 cta_group::2), 0 = none (generic kernel).  The environment variable CPMK_GEMM_VARIANT
+ * (auto | 1cta | 2cta | generic) overrides the choice.  For tests and the benchmark. */
+int32_t cpmk_last_gemm_variant(void);
+
 /* ------------------------------------------------------------------------------------------
  * fp16 decode GEMV (cuda/gemv.cu)
  * ------------------------------------------------------------------------------------------ */

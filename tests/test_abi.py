@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol(built_library):
 
 def test_python_binding_covers_every_declared_symbol(built_library):
     from cpm_kernels_b200.library import cpmk
-    bound = set(cpmk.SIGNATURES) | {"cpmk_abi_version", "cpmk_last_error", "cpmk_last_gemm_path"}
+    bound = set(cpmk.SIGNATURES) | {"cpmk_abi_version", "cpmk_last_error", "cpmk_last_gemm_path", "cpmk_last_gemm_variant"}
     assert sorted(bound) == declared_symbols()
 
 

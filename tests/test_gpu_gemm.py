@@ -57,13 +57,21 @@ TC_SHAPES = [
 ]
 
 
+@pytest.fixture
+def variant(request, monkeypatch):
+    """Forces one form of the tensor-core kernel (one-CTA tiles / CTA-pair tiles) for the duration of a test."""
+    monkeypatch.setenv("CPMK_GEMM_VARIANT", request.param)
+    return {"1cta": 1, "2cta": 2}[request.param]
+
+
+@pytest.mark.parametrize("variant", ["1cta", "2cta"], indirect=True)
 @pytest.mark.parametrize("m,k,n,bA,bB", TC_SHAPES)
-def test_tensor_core_kernel_exact(G, m, k, n, bA, bB):
+def test_tensor_core_kernel_exact(G, variant, m, k, n, bA, bB):
     A, B = operands(m, k, n, bA, bB, True, False, seed=m + n)
     want = ql.gemm_int8(m, k, n, True, False, A.numpy(), B.numpy())
     Ad, Bd = A.cuda(), B.cuda()
     got = G.gemm_int8(m, k, n, True, False, Ad, Bd)
-    assert cpmk.last_gemm_path() == 1
+    assert cpmk.last_gemm_path() == 1 and cpmk.last_gemm_variant() == variant
     assert (G.host(got) == want).all()
     # extreme codes: every product +-127*127 (or 128*128), accumulators at their largest magnitude
     Ae = torch.full_like(A, -128).cuda()
@@ -75,9 +83,11 @@ def test_tensor_core_kernel_exact(G, m, k, n, bA, bB):
 
 @pytest.mark.parametrize("m,k,n,bA,bB", [(256, 128, 128, 1, 1), (260, 144, 132, 2, 2), (1000, 2064, 500, 1, 1), (516, 256, 200, 3, 1),
                                          (512, 128, 512, 1, 4), (2560, 4096, 384, 1, 1)])
-@pytest.mark.parametrize("path", ["tc", "generic"])
-def test_fused_dequant_epilogue(G, m, k, n, bA, bB, path):
-    aT, bT = (True, False) if path == "tc" else (False, True)
+@pytest.mark.parametrize("path", ["tc", "tc2", "generic"])
+def test_fused_dequant_epilogue(G, m, k, n, bA, bB, path, monkeypatch):
+    if path != "generic":
+        monkeypatch.setenv("CPMK_GEMM_VARIANT", "1cta" if path == "tc" else "2cta")
+    aT, bT = (True, False) if path != "generic" else (False, True)
     A, B = operands(m, k, n, bA, bB, aT, bT, seed=m * 3 + n)
     batch = max(bA, bB)
     bx, by = bB == 1, bA == 1                       # scale_x pairs with the n axis (operand B), scale_y with m (operand A)
@@ -86,7 +96,8 @@ def test_fused_dequant_epilogue(G, m, k, n, bA, bB, path):
     acc = ql.gemm_int8(m, k, n, aT, bT, A.numpy(), B.numpy())
     want = ql.gemm_scale(acc, np16(sx), np16(sy), bx, by)
     got = G.gemm_int8_scale(m, k, n, aT, bT, A.cuda(), B.cuda(), sx.cuda(), sy.cuda(), bx, by)
-    assert cpmk.last_gemm_path() == (1 if path == "tc" else 2)
+    assert cpmk.last_gemm_path() == (2 if path == "generic" else 1)
+    assert cpmk.last_gemm_variant() == {"tc": 1, "tc2": 2, "generic": 0}[path]
     assert G.same_bits(got, want)
     G.assert_no_device_error()
 
@@ -103,7 +114,7 @@ def test_full_size_shapes_by_checksum_and_library(G, m, k, n):
     A = torch.randint(-127, 128, (1, m, k), generator=g, device="cuda", dtype=torch.int8)
     B = torch.randint(-127, 128, (1, n, k), generator=g, device="cuda", dtype=torch.int8)
     out = G.gemm_int8(m, k, n, True, False, A, B)
-    assert cpmk.last_gemm_path() == 1
+    assert cpmk.last_gemm_path() == 1 and cpmk.last_gemm_variant() == 2
     colsum_A = A[0].to(torch.int64).sum(dim=0)                                      # (k,)
     want_rowsum = (B[0].to(torch.float64) @ colsum_A.to(torch.float64)).to(torch.int64)   # exact: < 2**53
     assert torch.equal(out[0].to(torch.int64).sum(dim=1), want_rowsum)
