@@ -337,34 +337,39 @@ def run_ours(args) -> None:
     gemv = None
     if rank == 0 and not args.kernels_only:
         gemv = {}
-        nbuf = 4                                         # 4 x 84 MB of weights rotate: larger than L2
-        mats = [(torch.randn((1, 10240, 4096), generator=gen, device=dev) * 0.02).half() for _ in range(nbuf)]
-        vec_in = torch.randn((1, 4096), generator=gen, device=dev).half()
-        y_rows = torch.empty((1, 10240), dtype=torch.half, device=dev)
         gs = torch.cuda.Stream()                         # capture stream; warmed up first so that the library's
         s = gs.cuda_stream                               # per-stream workspace exists before capture begins
-        for name, fn in (("gemv_fp16", lambda j: ck.gemv_fp16(1, 10240, 4096, mats[j].data_ptr(), vec_in.data_ptr(), y_rows.data_ptr(), s)),
-                         # the transposed weight [4096, 10240] = (dim_in, dim_out): the same 84 MB buffers, read with the other shape
-                         ("gemv_fp16_transpose", lambda j: ck.gemv_fp16_transpose(1, 10240, 4096, mats[j].data_ptr(), vec_in.data_ptr(), y_rows.data_ptr(), s))):
-            gs.wait_stream(stream)
-            with torch.cuda.stream(gs):
-                for j in range(nbuf):
-                    fn(j)
-            gs.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=gs):
-                for j in range(nbuf * 5):
-                    fn(j % nbuf)
-            graph.replay()
-            torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            graph.replay()
-            b.record()
-            torch.cuda.synchronize()
-            sec = a.elapsed_time(b) * 1e-3 / (nbuf * 5)
-            bytes_alg = 2 * 10240 * 4096 + 2 * (10240 + 4096)
-            gemv[name] = {"GBps": bytes_alg / sec / 1e9, "us": sec * 1e6, "frac_of_hbm_peak": bytes_alg / sec / 1e9 / peaks["hbm_gbs"]}
+        for batch in (1, 4, 16):
+            nbuf = max(1, 4 // batch)                    # at least 4 x 84 MB of weights rotate: larger than L2
+            mats = [(torch.randn((batch, 10240, 4096), generator=gen, device=dev) * 0.02).half() for _ in range(nbuf)]
+            vec_in = torch.randn((batch, 4096), generator=gen, device=dev).half()
+            y_rows = torch.empty((batch, 10240), dtype=torch.half, device=dev)
+            # the transposed weight [4096, 10240] = (dim_in, dim_out): the same buffers, read with the other shape
+            for name, fn in (("gemv_fp16", lambda j: ck.gemv_fp16(batch, 10240, 4096, mats[j].data_ptr(), vec_in.data_ptr(), y_rows.data_ptr(), s)),
+                             ("gemv_fp16_transpose", lambda j: ck.gemv_fp16_transpose(batch, 10240, 4096, mats[j].data_ptr(), vec_in.data_ptr(), y_rows.data_ptr(), s))):
+                gs.wait_stream(stream)
+                with torch.cuda.stream(gs):
+                    for j in range(nbuf):
+                        fn(j)
+                gs.synchronize()
+                reps = max(2, 20 // (nbuf * batch))
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=gs):
+                    for j in range(nbuf * reps):
+                        fn(j % nbuf)
+                graph.replay()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                graph.replay()
+                b.record()
+                torch.cuda.synchronize()
+                sec = a.elapsed_time(b) * 1e-3 / (nbuf * reps)
+                bytes_alg = batch * (2 * 10240 * 4096 + 2 * (10240 + 4096))
+                gemv["%s_batch%d" % (name, batch)] = {"GBps": bytes_alg / sec / 1e9, "us": sec * 1e6,
+                                                     "frac_of_hbm_peak": bytes_alg / sec / 1e9 / peaks["hbm_gbs"]}
+            del mats
+        mats = None
         del mats
 
     status = cpmk.read_status()

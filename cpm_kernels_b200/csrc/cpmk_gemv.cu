@@ -4,9 +4,12 @@
 // Replaces cuda/gemv.cu:57-164 of the reference (one block per output element with half2 accumulation;
 // 32x32 blocks reading 64-byte row segments for the transposed form) and the cublasLt n=1 GEMMs of
 // cpm_kernels/kernels/gemv.py:82-262.
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "cpmk_common.cuh"
+#include "cpmk_ptx.cuh"
 
 namespace cpmk {
 namespace {
@@ -82,6 +85,254 @@ __global__ void __launch_bounds__(kBlock) gemv_rows_kernel(int32_t batch, int32_
     for (int j = 0; j < NB; ++j) {
         const float v = warp_sum(acc[j]);
         if (lane == 0) out[(int64_t)(b0 + j) * dim_out + o] = __float2half_rn(v);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Streaming form of the row-major GEMV for decode-sized rows (2 KiB .. 12.5 KiB): one persistent block per SM
+// owns a contiguous range of matrix rows and pulls them through a shared-memory ring with 1-d bulk asynchronous
+// copies (one producer thread), eight rows per stage, so that 100-200 KiB per SM are in flight without costing
+// registers; eight consumer warps take one row of each stage apiece (128-bit shared loads, fp32 accumulation).
+// ------------------------------------------------------------------------------------------------
+constexpr int kStreamRows = 8;                      // rows per stage = consumer warps
+constexpr int kStreamThreads = (kStreamRows + 1) * 32;
+constexpr int kStreamRingBytes = 200 * 1024;
+constexpr uint32_t kErrGemvProducer = 0x201;
+constexpr uint32_t kErrGemvConsumer = 0x202;
+
+// Rows longer than one stage slot are streamed in chunks of `chunk` halves (<= 4096): a stage then holds the
+// same chunk of eight consecutive rows, and each warp carries its row's sum across the chunks.
+template <bool SHARED>
+__global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int64_t total_rows, int32_t dim_out, int32_t dim_in, int32_t chunk,
+                                                                             int32_t stages, const __half *__restrict__ mat,
+                                                                             const __half *__restrict__ vec, __half *__restrict__ out,
+                                                                             uint32_t *status) {
+    extern __shared__ __align__(128) uint8_t ring[];
+    __shared__ __align__(8) uint64_t bars[32];       // full[stages], empty[stages]
+    __shared__ uint32_t abort_word;
+    const uint32_t slot_bytes = (uint32_t)chunk * 2u;             // one row's chunk
+    const uint32_t stage_bytes = slot_bytes * kStreamRows;
+    const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + 16);
+    const uint32_t ring_base = smem_u32(ring);
+    volatile uint32_t *abort_flag = &abort_word;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunks = (dim_in + chunk - 1) / chunk;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, kStreamRows);
+        }
+        abort_word = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    // this block's rows: [r0, r1)
+    const int64_t r0 = total_rows * blockIdx.x / gridDim.x, r1 = total_rows * (blockIdx.x + 1) / gridDim.x;
+    const int groups = (int)((r1 - r0 + kStreamRows - 1) / kStreamRows);
+
+    if (warp == kStreamRows) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool alive = true;
+            for (int g = 0; alive && g < groups; ++g) {
+                const int64_t row = r0 + (int64_t)g * kStreamRows;
+                const int n = (int)((r1 - row) < kStreamRows ? (r1 - row) : kStreamRows);
+                for (int c = 0; c < chunks; ++c) {
+                    if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrGemvProducer)) { alive = false; break; }
+                    const int c0 = c * chunk;
+                    const uint32_t bytes = (uint32_t)((dim_in - c0) < chunk ? (dim_in - c0) : chunk) * 2u;
+                    mbar_expect_tx(full_bar + 8 * stage, (uint32_t)n * bytes);
+                    for (int i = 0; i < n; ++i)
+                        bulk_load_1d(ring_base + stage * stage_bytes + (uint32_t)i * slot_bytes, mat + (row + i) * (int64_t)dim_in + c0, bytes,
+                                     full_bar + 8 * stage);
+                    if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else {
+        uint32_t stage = 0, phase = 0;
+        bool alive = true;
+        for (int g = 0; alive && g < groups; ++g) {
+            const int64_t row = r0 + (int64_t)g * kStreamRows + warp;
+            const int b = SHARED ? 0 : (int)((row < r1 ? row : r0) / dim_out);
+            float acc0 = 0.f, acc1 = 0.f;
+            for (int c = 0; c < chunks; ++c) {
+                if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kErrGemvConsumer)) { alive = false; break; }
+                if (row < r1) {
+                    const int c0 = c * chunk;
+                    const int nvec = ((dim_in - c0) < chunk ? (dim_in - c0) : chunk) >> 3;
+                    const uint4 *w = reinterpret_cast<const uint4 *>(ring + (size_t)stage * stage_bytes + (size_t)warp * slot_bytes);
+                    const uint4 *x = reinterpret_cast<const uint4 *>(vec + (int64_t)b * dim_in + c0);
+                    int i = lane;
+                    for (; i + 32 < nvec; i += 64) {
+                        const uint4 w0 = w[i], w1 = w[i + 32];
+                        const uint4 x0 = __ldg(x + i), x1 = __ldg(x + i + 32);
+                        acc0 = dot8(w0, x0, acc0);
+                        acc1 = dot8(w1, x1, acc1);
+                    }
+                    if (i < nvec) acc0 = dot8(w[i], __ldg(x + i), acc0);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_bar + 8 * stage);
+                if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+            }
+            if (alive && row < r1) {
+                const float v = warp_sum(acc0 + acc1);
+                if (lane == 0) out[row] = __float2half_rn(v);
+            }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);     // let copies in flight land before the ring is released
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Streaming form of the transposed GEMV (mat (dim_in, dim_out) row-major, out[o] = sum_i mat[i, o] * vec[i]).
+// A block owns a strip of up to 2048 columns (4 KiB row segments) and a range of rows; the producer thread pulls
+// eight row segments per stage through a 3-stage ring (two blocks per SM keep ~190 KiB per SM in flight); each
+// of the 256 consumer threads owns eight columns and eight fp32 sums.  Row ranges are combined as in the
+// non-streaming kernel: fp32 partials in scratch, added in range order by the block that takes the last ticket.
+// ------------------------------------------------------------------------------------------------
+constexpr int kTsCols = 2048;
+constexpr int kTsStages = 3;
+constexpr int kTsStageBytes = kStreamRows * kTsCols * 2;       // 32 KiB
+constexpr int kTsRingBytes = kTsStages * kTsStageBytes;        // 96 KiB
+
+__global__ void __launch_bounds__(kStreamThreads, 2) gemv_transpose_stream_kernel(int32_t dim_out, int32_t dim_in, int32_t rows_per_split,
+                                                                                  int32_t splits, const __half *__restrict__ mat,
+                                                                                  const __half *__restrict__ vec, __half *__restrict__ out,
+                                                                                  float *__restrict__ partial, uint32_t *__restrict__ tickets,
+                                                                                  uint32_t *status) {
+    extern __shared__ __align__(128) uint8_t ring[];
+    __shared__ __align__(8) uint64_t bars[2 * kTsStages];
+    __shared__ uint32_t abort_word;
+    __shared__ uint32_t is_last;
+    const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + kTsStages);
+    const uint32_t ring_base = smem_u32(ring);
+    volatile uint32_t *abort_flag = &abort_word;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int strip = blockIdx.x, split = blockIdx.y, b = blockIdx.z, batch = gridDim.z;
+    const int c0 = strip * kTsCols;
+    const int width = (dim_out - c0) < kTsCols ? (dim_out - c0) : kTsCols;       // multiple of 8
+    const uint32_t seg_bytes = (uint32_t)width * 2u;
+    const int i0 = split * rows_per_split;
+    const int i1 = min(dim_in, i0 + rows_per_split);
+    const int groups = (i1 - i0 + kStreamRows - 1) / kStreamRows;
+    const __half *base = mat + (int64_t)b * dim_in * dim_out + c0;
+    const __half *x = vec + (int64_t)b * dim_in;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTsStages; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, kStreamRows);
+        }
+        abort_word = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+
+    if (warp == kStreamRows) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            for (int g = 0; g < groups; ++g) {
+                if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrGemvProducer)) break;
+                const int row = i0 + g * kStreamRows;
+                const int n = (i1 - row) < kStreamRows ? (i1 - row) : kStreamRows;
+                mbar_expect_tx(full_bar + 8 * stage, (uint32_t)n * seg_bytes);
+                for (int r = 0; r < n; ++r)
+                    bulk_load_1d(ring_base + stage * kTsStageBytes + (uint32_t)r * (kTsCols * 2), base + (int64_t)(row + r) * dim_out, seg_bytes,
+                                 full_bar + 8 * stage);
+                if (++stage == kTsStages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else {
+        const int t = threadIdx.x;                       // 0..255: columns c0 + 8 t .. + 7
+        const bool col_ok = t * 8 < width;
+        uint32_t stage = 0, phase = 0;
+        for (int g = 0; g < groups; ++g) {
+            const int row = i0 + g * kStreamRows;
+            const int n = (i1 - row) < kStreamRows ? (i1 - row) : kStreamRows;
+            float xv[kStreamRows];
+#pragma unroll
+            for (int r = 0; r < kStreamRows; ++r) xv[r] = r < n ? __half2float(__ldg(x + row + r)) : 0.f;
+            if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kErrGemvConsumer)) break;
+            if (col_ok) {
+                const uint8_t *src = ring + (size_t)stage * kTsStageBytes + (size_t)t * 16;
+#pragma unroll
+                for (int r = 0; r < kStreamRows; ++r) {
+                    if (r < n) {
+                        const uint4 w = *reinterpret_cast<const uint4 *>(src + (size_t)r * (kTsCols * 2));
+                        const __half2 *h = reinterpret_cast<const __half2 *>(&w);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 f = __half22float2(h[j]);
+                            acc[2 * j] = fmaf(f.x, xv[r], acc[2 * j]);
+                            acc[2 * j + 1] = fmaf(f.y, xv[r], acc[2 * j + 1]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar + 8 * stage);
+            if (++stage == kTsStages) { stage = 0; phase ^= 1u; }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+        return;
+    }
+    const int t = threadIdx.x;
+    const bool writer = t < kStreamRows * 32 && t * 8 < width;
+    const int c = c0 + t * 8;
+    if (splits == 1) {
+        if (writer) {
+            __align__(16) __half o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = __float2half_rn(acc[j]);
+            *reinterpret_cast<uint4 *>(out + (int64_t)b * dim_out + c) = *reinterpret_cast<const uint4 *>(o);
+        }
+        return;
+    }
+    if (writer) {
+        float4 *dst = reinterpret_cast<float4 *>(partial + ((int64_t)split * batch + b) * dim_out + c);
+        dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t tk = atomicAdd(&tickets[b * gridDim.x + strip], 1u);
+        is_last = (tk == (uint32_t)splits - 1u);
+        if (is_last) tickets[b * gridDim.x + strip] = 0u;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (writer) {
+        float sum[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum[j] = 0.f;
+        for (int sp = 0; sp < splits; ++sp) {
+            const float4 *src = reinterpret_cast<const float4 *>(partial + ((int64_t)sp * batch + b) * dim_out + c);
+            const float4 p0 = __ldcg(src), p1 = __ldcg(src + 1);
+            sum[0] += p0.x; sum[1] += p0.y; sum[2] += p0.z; sum[3] += p0.w;
+            sum[4] += p1.x; sum[5] += p1.y; sum[6] += p1.z; sum[7] += p1.w;
+        }
+        __align__(16) __half o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = __float2half_rn(sum[j]);
+        *reinterpret_cast<uint4 *>(out + (int64_t)b * dim_out + c) = *reinterpret_cast<const uint4 *>(o);
     }
 }
 
@@ -279,6 +530,40 @@ int32_t launch_gemv_rows(int32_t batch, int32_t dim_out, int32_t dim_in, const v
         CPMK_LAUNCH_CHECK();
         return CPMK_OK;
     }
+    // rows of at least 2 KiB in a matrix that gives every SM a few dozen rows: the streaming kernel
+    const int64_t total_rows = SHARED ? (int64_t)dim_out : (int64_t)batch * dim_out;
+    const int64_t row_bytes = (int64_t)dim_in * 2;
+    // (rows that do not fit a stage slot could be streamed in chunks -- the kernel supports it -- but measured slower
+    // than the register-staged kernel on a 4096 x 10240 matrix, so such shapes stay with that kernel)
+    if ((!SHARED || batch == 1) && row_bytes >= 2048 && row_bytes * kStreamRows * 2 <= kStreamRingBytes && total_rows >= (int64_t)info.sm_count * 16 &&
+        info.max_smem_optin >= kStreamRingBytes + 1024 && !getenv("CPMK_GEMV_NO_STREAM")) {
+        static std::once_flag attr_once[64];
+        static cudaError_t attr_err[64];
+        const int dev = info.device & 63;
+        std::call_once(attr_once[dev], [dev] {
+            cudaError_t e = cudaFuncSetAttribute(gemv_rows_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_rows_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes);
+            attr_err[dev] = e;
+        });
+        if (attr_err[dev] == cudaSuccess) {
+            Workspace ws;
+            rc = get_workspace(stream, &ws);
+            if (rc) return rc;
+            // chunk: the whole row when it fits 8 KiB, else equal parts of at most 4096 halves (multiples of 8)
+            int chunk = dim_in;
+            if (chunk > 4096) {
+                const int parts = (dim_in + 4095) / 4096;
+                chunk = ((dim_in + parts - 1) / parts + 7) / 8 * 8;
+            }
+            int stages = (int)(kStreamRingBytes / ((int64_t)chunk * 2 * kStreamRows));
+            if (stages > 16) stages = 16;
+            const size_t smem = (size_t)stages * chunk * 2 * kStreamRows;
+            gemv_rows_stream_kernel<SHARED><<<info.sm_count, kStreamThreads, smem, stream>>>(total_rows, dim_out, dim_in, chunk, stages, w, x, y,
+                                                                                            ws.status());
+            CPMK_LAUNCH_CHECK();
+            return CPMK_OK;
+        }
+    }
     if (!SHARED) {
         const int64_t blocks = ceil_div64((int64_t)batch * dim_out, kWarps);
         CPMK_REQUIRE(blocks < (int64_t(1) << 31), "too many rows");
@@ -369,6 +654,42 @@ int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in,
         gemv_transpose_generic_kernel<<<(unsigned)blocks, kBlock, 0, st>>>(batch, dim_out, dim_in, w, x, y);
         CPMK_LAUNCH_CHECK();
         return CPMK_OK;
+    }
+    // matrices of a few MB and more: the streaming kernel, two blocks per SM
+    if ((int64_t)dim_in * dim_out >= (int64_t(1) << 21) && dim_in >= 256 && aligned16(out) && info.max_smem_optin >= kTsRingBytes + 1024 &&
+        !getenv("CPMK_GEMV_NO_STREAM")) {
+        static std::once_flag attr_once[64];
+        static cudaError_t attr_err[64];
+        const int dev = info.device & 63;
+        std::call_once(attr_once[dev], [dev] {
+            attr_err[dev] = cudaFuncSetAttribute(gemv_transpose_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTsRingBytes);
+        });
+        const int ts_strips = (dim_out + kTsCols - 1) / kTsCols;
+        if (attr_err[dev] == cudaSuccess && (size_t)batch * ts_strips * sizeof(uint32_t) <= Workspace::kTicketBytes) {
+            int64_t sp = ((int64_t)info.sm_count * 2) / ((int64_t)ts_strips * batch);
+            const int64_t by_rows = (dim_in + 63) / 64;
+            if (sp > by_rows) sp = by_rows;
+            const int64_t by_scratch = (int64_t)(Workspace::kScratchBytes / (sizeof(float) * (size_t)batch * (size_t)dim_out));
+            if (sp > by_scratch) sp = by_scratch;
+            if (sp > 65535) sp = 65535;
+            if (sp < 1) sp = 1;
+            int rps = (int)((dim_in + sp - 1) / sp);
+            rps = (rps + kStreamRows - 1) / kStreamRows * kStreamRows;
+            const int nsp = (dim_in + rps - 1) / rps;
+            // the block that takes the last ticket adds nsp partials by itself: beyond several dozen that serial tail
+            // outweighs the better streaming (measured at batch 1), and the register-staged kernel below is used
+            if (nsp <= 64) {
+                Workspace ws;
+                rc = get_workspace(st, &ws);
+                if (rc) return rc;
+                const dim3 grid(ts_strips, nsp, batch);
+                gemv_transpose_stream_kernel<<<grid, kStreamThreads, kTsRingBytes, st>>>(dim_out, dim_in, rps, nsp, w, x, y,
+                                                                                         reinterpret_cast<float *>(ws.scratch()), ws.tickets(),
+                                                                                         ws.status());
+                CPMK_LAUNCH_CHECK();
+                return CPMK_OK;
+            }
+        }
     }
     // enough blocks to keep ~6 per SM streaming; at least 8 rows per warp in a chunk
     int64_t splits = ((int64_t)info.sm_count * 6) / ((int64_t)strips * batch);

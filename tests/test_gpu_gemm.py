@@ -82,7 +82,7 @@ def test_tensor_core_kernel_exact(G, variant, m, k, n, bA, bB):
 
 
 @pytest.mark.parametrize("m,k,n,bA,bB", [(256, 128, 128, 1, 1), (260, 144, 132, 2, 2), (1000, 2064, 500, 1, 1), (516, 256, 200, 3, 1),
-                                         (512, 128, 512, 1, 4), (2560, 4096, 384, 1, 1)])
+                                         (512, 128, 512, 1, 4), (2560, 4096, 384, 1, 1), (5120, 1024, 1024, 1, 1)])
 @pytest.mark.parametrize("path", ["tc", "tc2", "generic"])
 def test_fused_dequant_epilogue(G, m, k, n, bA, bB, path, monkeypatch):
     if path != "generic":
