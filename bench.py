@@ -173,6 +173,7 @@ def run_ours(args) -> None:
     import cpm_kernels_b200.torch as ct
     import cpm_kernels_b200.kernels as ck
     from cpm_kernels_b200.library import cpmk
+    from cpm_kernels_b200.sharded import shard_bounds
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -192,12 +193,15 @@ def run_ours(args) -> None:
         assert n % world == 0
         xs.append(torch.randn((1, M_TOKENS, k), generator=gen, device=dev).half())
         w_full = (torch.randn((1, n, k), generator=gen, device=dev) * 0.02).half()
-        ws.append(w_full[:, rank * (n // world):(rank + 1) * (n // world), :].contiguous())
+        lo, hi = shard_bounds(n, world, rank)
+        ws.append(w_full[:, lo:hi, :].contiguous())
         del w_full
         if world > 1:
             gathered.append(torch.empty((world, M_TOKENS, n // world), dtype=torch.half, device=dev))
     stream = torch.cuda.current_stream()
     comm_stream = torch.cuda.Stream() if world > 1 else None
+    from cpm_kernels_b200.sharded import ColumnParallelInt8Linear
+    layers = [ColumnParallelInt8Linear(w) for w in ws] if world > 1 else None
 
     gemm_events = []
 
@@ -222,7 +226,7 @@ def run_ours(args) -> None:
                 ev.record(stream)
                 with torch.cuda.stream(comm_stream):
                     comm_stream.wait_event(ev)
-                    dist.all_gather_into_tensor(gathered[i], y)
+                    layers[i].gather(y, out=gathered[i])
                 y.record_stream(comm_stream)
             results.append(y)
         if world > 1:

@@ -122,6 +122,20 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
     return d;
 }
 
+// Shared-memory matrix descriptor of an MN-major tile (the operand's rows, not k, are contiguous in memory): what
+// TMA writes for a box of 128 elements (one 128-byte swizzle row) by kBK k-rows.  Eight k-rows form a 1024-byte
+// swizzle atom (stride byte offset); a further block of 128 elements along M/N, when an MMA spans more than
+// one, lies `mn_block_bytes` away (leading byte offset).
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, uint32_t mn_block_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)((mn_block_bytes >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)(1024u >> 4) << 32;
+    d |= (uint64_t)1u << 46;
+    d |= (uint64_t)2u << 61;
+    return d;
+}
+
 // Instruction descriptor of tcgen05.mma kind::i8: int32 accumulator (bits 4-5 = 2), signed 8-bit A and B
 // (bits 7-9 = 1, 10-12 = 1), both k-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
 constexpr uint32_t kInstrDesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
@@ -379,7 +393,10 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask
                  ::"r"(bar), "h"(cta_mask) : "memory");
 }
 
-template <bool DEQUANT>
+// P_MN / Q_MN: the row / column operand is stored with its rows contiguous (k is the slow axis) instead of k:
+// the reference's bT / !aT layouts.  Their tensor maps then have (rows, k, batch) extents and 128 x kBK boxes, the
+// shared-memory tiles are MN-major, and bits 15 / 16 of the instruction descriptor say so.
+template <bool DEQUANT, bool P_MN, bool Q_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
 gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, const GemmParams prm) {
     extern __shared__ uint8_t smem_raw[];
@@ -435,8 +452,10 @@ gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     const uint32_t p_dst = tiles_base + stage * kStageBytes2;
                     if (leader) mbar_expect_tx(full_bar + 8 * stage, 2 * kStageBytes2);
                     const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
-                    tma_load_3d_pair(p_dst, &tmap_p, kb * kBK, row0, prm.p_batched ? b : 0, leader_full);
-                    tma_load_3d_pair(p_dst + kPBytes, &tmap_q, kb * kBK, col0, prm.q_batched ? b : 0, leader_full);
+                    if (P_MN) tma_load_3d_pair(p_dst, &tmap_p, row0, kb * kBK, prm.p_batched ? b : 0, leader_full);
+                    else tma_load_3d_pair(p_dst, &tmap_p, kb * kBK, row0, prm.p_batched ? b : 0, leader_full);
+                    if (Q_MN) tma_load_3d_pair(p_dst + kPBytes, &tmap_q, col0, kb * kBK, prm.q_batched ? b : 0, leader_full);
+                    else tma_load_3d_pair(p_dst + kPBytes, &tmap_q, kb * kBK, col0, prm.q_batched ? b : 0, leader_full);
                     if (++stage == kStages2) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -454,11 +473,15 @@ gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, prm.status, kErrMmaWaitFull)) { alive = false; break; }
                     tcgen05_fence_after();
                     const uint32_t p_src = tiles_base + stage * kStageBytes2;
-                    const uint64_t p_desc = make_kmajor_sw128_desc(p_src);
-                    const uint64_t q_desc = make_kmajor_sw128_desc(p_src + kPBytes);
+                    // k advances by 32 per MMA: 32 bytes inside the swizzle row of a k-major tile (+2 in the
+                    // address field), 32 rows of 128 bytes in an MN-major tile (+256)
+                    const uint64_t p_desc = P_MN ? make_mnmajor_sw128_desc(p_src, kPBytes) : make_kmajor_sw128_desc(p_src);
+                    const uint64_t q_desc = Q_MN ? make_mnmajor_sw128_desc(p_src + kPBytes, kQBytes2) : make_kmajor_sw128_desc(p_src + kPBytes);
+                    constexpr uint32_t idesc = kInstrDesc2 | (P_MN ? (1u << 15) : 0u) | (Q_MN ? (1u << 16) : 0u);
 #pragma unroll
                     for (int j = 0; j < kBK / kUmmaK; ++j)
-                        umma_i8_pair(d_tmem, p_desc + (uint64_t)(2 * j), q_desc + (uint64_t)(2 * j), kInstrDesc2, (kb | j) != 0 ? 1u : 0u);
+                        umma_i8_pair(d_tmem, p_desc + (uint64_t)((P_MN ? 256 : 2) * j), q_desc + (uint64_t)((Q_MN ? 256 : 2) * j), idesc,
+                                     (kb | j) != 0 ? 1u : 0u);
                     umma_commit_pair(empty_bar + 8 * stage, 3);
                     if (++stage == kStages2) { stage = 0; phase ^= 1u; }
                 }
@@ -628,6 +651,20 @@ bool encode_operand(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, 
     return r == CUDA_SUCCESS;
 }
 
+// int8 operand stored (batch, k, rows) with the rows contiguous, as a 3-d tensor map whose box is 128 rows x kBK of k.
+bool encode_operand_mn(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch) {
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)rows, (cuuint64_t)k, (cuuint64_t)batch};
+    const cuuint64_t strides[2] = {(cuuint64_t)rows, (cuuint64_t)rows * (cuuint64_t)k};
+    const cuuint32_t box[3] = {128u, (cuuint32_t)kBK, 1u};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 thread_local int32_t g_last_path = 0;
 thread_local int32_t g_last_variant = 0;
 
@@ -656,8 +693,11 @@ int32_t prepare_tc_kernels(int device) {
     std::call_once(g_prepare_once[dev], [dev] {
         cudaError_t e = cudaFuncSetAttribute(gemm_i8_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_i8_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_i8_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTc2SmemBytes);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_i8_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTc2SmemBytes);
+#define CPMK_SET_TC2(D, P, Q) \
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_i8_tc2_kernel<D, P, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTc2SmemBytes)
+        CPMK_SET_TC2(false, false, false); CPMK_SET_TC2(false, false, true); CPMK_SET_TC2(false, true, false); CPMK_SET_TC2(false, true, true);
+        CPMK_SET_TC2(true, false, false); CPMK_SET_TC2(true, false, true); CPMK_SET_TC2(true, true, false); CPMK_SET_TC2(true, true, true);
+#undef CPMK_SET_TC2
         g_prepare_err[dev] = e;
         if (e != cudaSuccess) return;
         cudaLaunchConfig_t cfg = {};
@@ -672,7 +712,7 @@ int32_t prepare_tc_kernels(int device) {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_i8_tc2_kernel<true>, &cfg) == cudaSuccess && clusters > 0) {
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_i8_tc2_kernel<true, false, false>, &cfg) == cudaSuccess && clusters > 0) {
             g_max_pairs[dev] = clusters;
         } else {
             // the query is advisory: a pair that is not resident at launch simply starts when a pair retires
@@ -712,9 +752,12 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
     CPMK_REQUIRE((reinterpret_cast<uintptr_t>(A) & 3u) == 0 && (reinterpret_cast<uintptr_t>(B) & 3u) == 0, "operands must be 4-byte aligned");
     if (DEQUANT) CPMK_REQUIRE(scale_x && scale_y, "null scale pointer");
 
-    // tensor-core paths: both operands contiguous along k, TMA-compatible strides and addresses
+    // tensor-core paths.  Each operand is either k-major (k contiguous: aT for A, !bT for B) or MN-major; TMA needs
+    // the contiguous extent to be a multiple of 16 bytes and 16-byte aligned base addresses.
     const int variant = gemm_variant();
-    const bool tc_ok = aT && !bT && variant != kVariantGeneric && k % 16 == 0 && aligned16(A) && aligned16(B) && aligned16(out) &&
+    const bool q_mn = !aT, p_mn = bT;                       // column operand = A, row operand = B
+    const bool strides_ok = (q_mn ? m % 16 == 0 : k % 16 == 0) && (p_mn ? n % 16 == 0 : k % 16 == 0);
+    const bool tc_ok = variant != kVariantGeneric && strides_ok && aligned16(A) && aligned16(B) && aligned16(out) &&
                        (!DEQUANT || aligned16(scale_y)) && info.max_smem_optin >= kTcSmemBytes;
     if (tc_ok) {
         Workspace ws;
@@ -733,14 +776,21 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
         CUtensorMap tmap_p, tmap_q;
         // ---- two-CTA form: 256 x 256 tiles per CTA pair; worth it once there is more than one 128-row block ----
         const int max_pairs = g_max_pairs[info.device & 63];
-        if (variant != kVariantOneCta && max_pairs > 0 && (n > kBM || variant == kVariantTwoCta)) {
+        const bool any_mn = p_mn || q_mn;                   // MN-major operands are implemented in the two-CTA kernel only
+        if (variant != kVariantOneCta && max_pairs > 0 && (n > kBM || variant == kVariantTwoCta || any_mn)) {
             const int64_t tiles_r = (n + 2 * kBM - 1) / (2 * kBM), tiles_c = (m + kBN - 1) / kBN;
             const int64_t total = tiles_r * tiles_c * batch;
             // rows of the output come from B (n x k), columns from A (m x k); each CTA stages 128 rows of either
-            if (total < (int64_t(1) << 31) && encode_operand(&tmap_p, B, n, k, batchB, kBM) && encode_operand(&tmap_q, A, m, k, batchA, kHalfBN)) {
+            const bool enc_p = p_mn ? encode_operand_mn(&tmap_p, B, n, k, batchB) : encode_operand(&tmap_p, B, n, k, batchB, kBM);
+            const bool enc_q = q_mn ? encode_operand_mn(&tmap_q, A, m, k, batchA) : encode_operand(&tmap_q, A, m, k, batchA, kHalfBN);
+            if (total < (int64_t(1) << 31) && enc_p && enc_q) {
                 prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.total_tiles = (int32_t)total;
                 const int pairs = (int)(total < max_pairs ? total : max_pairs);
-                gemm_i8_tc2_kernel<DEQUANT><<<2 * pairs, kTcThreads, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, prm);
+                const dim3 grid(2 * pairs);
+                if (!p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, false, false><<<grid, kTcThreads, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, prm);
+                else if (!p_mn && q_mn) gemm_i8_tc2_kernel<DEQUANT, false, true><<<grid, kTcThreads, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, prm);
+                else if (p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, true, false><<<grid, kTcThreads, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, prm);
+                else gemm_i8_tc2_kernel<DEQUANT, true, true><<<grid, kTcThreads, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, prm);
                 CPMK_LAUNCH_CHECK();
                 g_last_path = 1;
                 g_last_variant = 2;
@@ -749,7 +799,7 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
         }
         const int64_t tiles_r = (n + kBM - 1) / kBM, tiles_c = (m + kBN - 1) / kBN;
         const int64_t total_tiles = tiles_r * tiles_c * batch;
-        if (variant != kVariantTwoCta && total_tiles < (int64_t(1) << 31) && encode_operand(&tmap_p, B, n, k, batchB, kBM) &&
+        if (!any_mn && variant != kVariantTwoCta && total_tiles < (int64_t(1) << 31) && encode_operand(&tmap_p, B, n, k, batchB, kBM) &&
             encode_operand(&tmap_q, A, m, k, batchA, kBN)) {
             prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.total_tiles = (int32_t)total_tiles;
             const int grid = (int)(total_tiles < info.sm_count ? total_tiles : info.sm_count);

@@ -41,14 +41,16 @@ __device__ __forceinline__ uint2 round8_one_scale(const uint4 &v, float s, float
     const float2 ru = make_float2(r_up, r_up), rd = make_float2(r_dn, r_dn);
     const float2 magic = make_float2(CPMK_ROUND_MAGIC, CPMK_ROUND_MAGIC);
     float2 dn[4];
-    bool ok = true;
+    // disagreement between the two roundings is accumulated on the FMA pipe as a sum of squared differences
+    // (zero iff every pair agrees; NaN -- from a NaN element or the out-of-domain marker -- propagates)
+    float2 bad = make_float2(0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const float2 f = __half22float2(h[i]);
         const float2 up = __ffma2_rn(f, ru, magic);
         dn[i] = __ffma2_rn(f, rd, magic);
-        ok = ok && (up.x == dn[i].x);
-        ok = ok && (up.y == dn[i].y);
+        const float2 d = __fadd2_rn(up, make_float2(-dn[i].x, -dn[i].y));
+        bad = __ffma2_rn(d, d, bad);
     }
     uint32_t b[8];
 #pragma unroll
@@ -56,7 +58,7 @@ __device__ __forceinline__ uint2 round8_one_scale(const uint4 &v, float s, float
         b[2 * i] = __float_as_uint(dn[i].x);
         b[2 * i + 1] = __float_as_uint(dn[i].y);
     }
-    if (!ok) {
+    if (!(bad.x + bad.y == 0.f)) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float2 f = __half22float2(h[i]);
@@ -75,15 +77,16 @@ __device__ __forceinline__ uint2 round8_one_scale(const uint4 &v, float s, float
 // to NV 128-bit vectors of it in registers, so the row is read from HBM exactly once.
 // MODE 0: scale and codes (fused);  1: scale only;  2: codes only, scale given.
 // ------------------------------------------------------------------------------------------------
-template <int NV, int MODE>
+// FULL: every block has all its rows and every thread all NV vectors (no bounds predicates).
+template <int NV, int MODE, bool FULL>
 __global__ void __launch_bounds__(kBlock) quant_rows_kernel(int64_t rows, int32_t m, int group, const __half *__restrict__ mat,
-                                                                 __half *__restrict__ scale, int8_t *__restrict__ out) {
+                                                            __half *__restrict__ scale, int8_t *__restrict__ out) {
     __shared__ float warp_max[kBlock / 32];
     const int tid = threadIdx.x;
     const int rows_per_block = kBlock / group;
     const int lane_in_row = tid & (group - 1);
     const int64_t row = (int64_t)blockIdx.x * rows_per_block + tid / group;
-    const bool row_ok = row < rows;
+    const bool row_ok = FULL || row < rows;
     const int nvec = m >> 3;
     const uint4 *src = reinterpret_cast<const uint4 *>(mat + (row_ok ? row : 0) * (int64_t)m);
 
@@ -91,7 +94,7 @@ __global__ void __launch_bounds__(kBlock) quant_rows_kernel(int64_t rows, int32_
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
         const int idx = lane_in_row + j * group;
-        v[j] = (row_ok && idx < nvec) ? __ldcs(src + idx) : make_uint4(0, 0, 0, 0);
+        v[j] = (FULL || (row_ok && idx < nvec)) ? __ldcs(src + idx) : make_uint4(0, 0, 0, 0);
     }
     __half2 m2 = __float2half2_rn(0.f);
 #pragma unroll
@@ -124,7 +127,7 @@ __global__ void __launch_bounds__(kBlock) quant_rows_kernel(int64_t rows, int32_
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
         const int idx = lane_in_row + j * group;
-        if (row_ok && idx < nvec) dst[idx] = round8_one_scale(v[j], s, r_up, r_dn);
+        if (FULL || (row_ok && idx < nvec)) dst[idx] = round8_one_scale(v[j], s, r_up, r_dn);
     }
 }
 
@@ -171,11 +174,12 @@ __global__ void __launch_bounds__(kBlock) quant_rows_generic_kernel(int64_t rows
 constexpr int kStripCols = 64;
 constexpr int kStripRows = 32;
 
-__global__ void __launch_bounds__(kBlock) colmax_partial_kernel(int32_t n, int32_t m, int32_t rows_per_split,
+__global__ void __launch_bounds__(kBlock) colmax_partial_kernel(int32_t n, int32_t m, int32_t rows_per_split, int32_t strip0,
                                                                 const __half *__restrict__ mat, __half *__restrict__ partial) {
     __shared__ __half2 red[kStripRows][kStripCols / 2 + 1];
     const int cl = threadIdx.x & 7, rl = threadIdx.x >> 3;
-    const int col = blockIdx.x * kStripCols + cl * 8;
+    const int strip = strip0 + blockIdx.x;
+    const int col = strip * kStripCols + cl * 8;
     const int split = blockIdx.y, b = blockIdx.z, splits = gridDim.y;
     const int r_begin = split * rows_per_split;
     const int r_end = min(n, r_begin + rows_per_split);
@@ -201,7 +205,7 @@ __global__ void __launch_bounds__(kBlock) colmax_partial_kernel(int32_t n, int32
         __half2 acc = red[0][threadIdx.x];
 #pragma unroll 8
         for (int r = 1; r < kStripRows; ++r) acc = __hmax2(acc, red[r][threadIdx.x]);
-        const int c = blockIdx.x * kStripCols + threadIdx.x * 2;
+        const int c = strip * kStripCols + threadIdx.x * 2;
         if (c < m) *reinterpret_cast<__half2 *>(partial + ((int64_t)split * gridDim.z + b) * m + c) = acc;
     }
     (void)splits;
@@ -220,11 +224,11 @@ __global__ void __launch_bounds__(kBlock) colmax_finish_kernel(int32_t batch, in
 // SRC 0: fold the partial maxima, write the scale (blocks of split 0) and round.
 // SRC 1: scale given by the caller (gemm_round_transpose); validity of the rule is checked per code.
 template <int SRC>
-__global__ void __launch_bounds__(kBlock) quant_cols_round_kernel(int32_t n, int32_t m, int32_t rows_per_split, int32_t splits,
+__global__ void __launch_bounds__(kBlock) quant_cols_round_kernel(int32_t n, int32_t m, int32_t rows_per_split, int32_t splits, int32_t strip0,
                                                                   const __half *__restrict__ mat, const __half *__restrict__ partial,
                                                                   __half *__restrict__ scale, int8_t *__restrict__ out) {
     const int cl = threadIdx.x & 7, rl = threadIdx.x >> 3;
-    const int col = blockIdx.x * kStripCols + cl * 8;
+    const int col = (strip0 + blockIdx.x) * kStripCols + cl * 8;
     if (col >= m) return;
     const int split = gridDim.y - 1 - blockIdx.y, b = blockIdx.z, batch = gridDim.z;
     const int r_begin = split * rows_per_split;
@@ -485,11 +489,18 @@ int32_t launch_quant_rows(int32_t batch, int32_t n, int32_t m, const void *mat, 
     const int64_t blocks = ceil_div64(rows, rows_per_block);
     CPMK_REQUIRE(blocks < (int64_t(1) << 31), "too many rows: %lld", (long long)rows);
     const dim3 grid((unsigned)blocks);
-    if (nv <= 1) quant_rows_kernel<1, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
-    else if (nv <= 2) quant_rows_kernel<2, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
-    else if (nv <= 4) quant_rows_kernel<4, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
-    else if (nv <= 6) quant_rows_kernel<6, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
-    else quant_rows_kernel<8, MODE><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);
+    const bool full = (rows % rows_per_block == 0) && (nvec == group * nv) && (nv == 1 || nv == 2 || nv == 4 || nv == 6 || nv == 8);
+#define CPMK_LAUNCH_ROWS(NVT)                                                                                        \
+    do {                                                                                                             \
+        if (full) quant_rows_kernel<NVT, MODE, true><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);     \
+        else quant_rows_kernel<NVT, MODE, false><<<grid, kBlock, 0, stream>>>(rows, m, group, src, sc, dst);         \
+    } while (0)
+    if (nv <= 1) CPMK_LAUNCH_ROWS(1);
+    else if (nv <= 2) CPMK_LAUNCH_ROWS(2);
+    else if (nv <= 4) CPMK_LAUNCH_ROWS(4);
+    else if (nv <= 6) CPMK_LAUNCH_ROWS(6);
+    else CPMK_LAUNCH_ROWS(8);
+#undef CPMK_LAUNCH_ROWS
     CPMK_LAUNCH_CHECK();
     return CPMK_OK;
 }
@@ -541,10 +552,10 @@ int32_t launch_quant_cols(int32_t batch, int32_t n, int32_t m, const void *mat, 
         CPMK_LAUNCH_CHECK();
         return CPMK_OK;
     }
-    const ColPlan p = plan_cols(batch, n, m, info.sm_count, sizeof(__half), Workspace::kScratchBytes);
-    const dim3 grid(p.strips, p.splits, batch);
     if (MODE == 2) {
-        quant_cols_round_kernel<1><<<grid, kBlock, 0, stream>>>(n, m, p.rows_per_split, p.splits, src, nullptr, sc, dst);
+        const ColPlan p = plan_cols(batch, n, m, info.sm_count, sizeof(__half), Workspace::kScratchBytes);
+        const dim3 grid(p.strips, p.splits, batch);
+        quant_cols_round_kernel<1><<<grid, kBlock, 0, stream>>>(n, m, p.rows_per_split, p.splits, 0, src, nullptr, sc, dst);
         CPMK_LAUNCH_CHECK();
         return CPMK_OK;
     }
@@ -552,14 +563,24 @@ int32_t launch_quant_cols(int32_t batch, int32_t n, int32_t m, const void *mat, 
     rc = get_workspace(stream, &ws);
     if (rc) return rc;
     __half *partial = reinterpret_cast<__half *>(ws.scratch());
-    colmax_partial_kernel<<<grid, kBlock, 0, stream>>>(n, m, p.rows_per_split, src, partial);
-    CPMK_LAUNCH_CHECK();
     if (MODE == 1) {
+        const ColPlan p = plan_cols(batch, n, m, info.sm_count, sizeof(__half), Workspace::kScratchBytes);
+        const dim3 grid(p.strips, p.splits, batch);
+        colmax_partial_kernel<<<grid, kBlock, 0, stream>>>(n, m, p.rows_per_split, 0, src, partial);
+        CPMK_LAUNCH_CHECK();
         const int64_t blocks = ceil_div64((int64_t)batch * m, kBlock);
         colmax_finish_kernel<<<(unsigned)blocks, kBlock, 0, stream>>>(batch, m, p.splits, partial, sc);
-    } else {
-        quant_cols_round_kernel<0><<<grid, kBlock, 0, stream>>>(n, m, p.rows_per_split, p.splits, src, partial, sc, dst);
+        CPMK_LAUNCH_CHECK();
+        return CPMK_OK;
     }
+    // Fused form: absmax pass, then rounding pass over the same operand in the opposite row order.  (Walking the
+    // operand in L2-sized column panels, so that the second read never reaches HBM, was tried and measured slower:
+    // the per-panel launches are too small to fill the machine.)
+    const ColPlan p = plan_cols(batch, n, m, info.sm_count, sizeof(__half), Workspace::kScratchBytes);
+    const dim3 grid(p.strips, p.splits, batch);
+    colmax_partial_kernel<<<grid, kBlock, 0, stream>>>(n, m, p.rows_per_split, 0, src, partial);
+    CPMK_LAUNCH_CHECK();
+    quant_cols_round_kernel<0><<<grid, kBlock, 0, stream>>>(n, m, p.rows_per_split, p.splits, 0, src, partial, sc, dst);
     CPMK_LAUNCH_CHECK();
     return CPMK_OK;
 }

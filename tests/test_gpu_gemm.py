@@ -42,7 +42,8 @@ def test_all_layouts_and_broadcasts(G, m, k, n, aT, bT, bA, bB):
     want = ql.gemm_int8(m, k, n, aT, bT, A.numpy(), B.numpy())
     got = G.gemm_int8(m, k, n, aT, bT, A.cuda(), B.cuda())
     assert (G.host(got) == want).all()
-    expect_tc = aT and not bT and k % 16 == 0
+    # the tensor-core kernels need the contiguous extent of each operand to be a multiple of 16 bytes
+    expect_tc = (k % 16 == 0 if aT else m % 16 == 0) and (n % 16 == 0 if bT else k % 16 == 0)
     assert cpmk.last_gemm_path() == (1 if expect_tc else 2)
     G.assert_no_device_error()
 
@@ -85,8 +86,7 @@ def test_tensor_core_kernel_exact(G, variant, m, k, n, bA, bB):
                                          (512, 128, 512, 1, 4), (2560, 4096, 384, 1, 1), (5120, 1024, 1024, 1, 1)])
 @pytest.mark.parametrize("path", ["tc", "tc2", "generic"])
 def test_fused_dequant_epilogue(G, m, k, n, bA, bB, path, monkeypatch):
-    if path != "generic":
-        monkeypatch.setenv("CPMK_GEMM_VARIANT", "1cta" if path == "tc" else "2cta")
+    monkeypatch.setenv("CPMK_GEMM_VARIANT", {"tc": "1cta", "tc2": "2cta", "generic": "generic"}[path])
     aT, bT = (True, False) if path != "generic" else (False, True)
     A, B = operands(m, k, n, bA, bB, aT, bT, seed=m * 3 + n)
     batch = max(bA, bB)
@@ -99,6 +99,29 @@ def test_fused_dequant_epilogue(G, m, k, n, bA, bB, path, monkeypatch):
     assert cpmk.last_gemm_path() == (2 if path == "generic" else 1)
     assert cpmk.last_gemm_variant() == {"tc": 1, "tc2": 2, "generic": 0}[path]
     assert G.same_bits(got, want)
+    G.assert_no_device_error()
+
+
+@pytest.mark.parametrize("m,k,n,bA,bB", [(512, 384, 256, 1, 1), (1024, 4096, 512, 1, 1), (272, 144, 400, 2, 2), (2048, 1000, 304, 1, 3),
+                                         (4096, 2560, 768, 1, 1)])
+@pytest.mark.parametrize("aT,bT", [(False, False), (True, True), (False, True)])
+def test_tensor_core_kernel_other_storage_orders(G, m, k, n, bA, bB, aT, bT):
+    """The reference's three other storage orders (an operand whose k axis is the slow one: the transposed-weight and
+    (hidden, seq) activation layouts) on the tensor-core kernel, exact, plus the fused dequantising epilogue."""
+    if (not aT and m % 16) or (bT and n % 16) or ((aT or not bT) and k % 16):
+        pytest.skip("extent not a multiple of 16 bytes: generic kernel")
+    A, B = operands(m, k, n, bA, bB, aT, bT, seed=m + 7 * n)
+    want = ql.gemm_int8(m, k, n, aT, bT, A.numpy(), B.numpy())
+    Ad, Bd = A.cuda(), B.cuda()
+    got = G.gemm_int8(m, k, n, aT, bT, Ad, Bd)
+    assert cpmk.last_gemm_path() == 1 and cpmk.last_gemm_variant() == 2
+    assert (G.host(got) == want).all()
+    batch = max(bA, bB)
+    bx, by = bB == 1, bA == 1
+    sx = randn_fp16((1 if bx else batch, n), 7, 0.01).abs()
+    sy = randn_fp16((1 if by else batch, m), 8, 0.001).abs()
+    fused = G.gemm_int8_scale(m, k, n, aT, bT, Ad, Bd, sx.cuda(), sy.cuda(), bx, by)
+    assert G.same_bits(fused, ql.gemm_scale(want, np16(sx), np16(sy), bx, by))
     G.assert_no_device_error()
 
 
