@@ -205,7 +205,7 @@ def run_ours(args) -> None:
 
     gemm_events = []
 
-    def step(record_gemm: bool = False):
+    def step(record_gemm: bool = False, gather: bool = True):
         """The four linears through the public API.  With record_gemm, CUDA events bracket each GEMM launch."""
         results = []
         for i, (x, w) in enumerate(zip(xs, ws)):
@@ -221,7 +221,7 @@ def run_ours(args) -> None:
                 gemm_events.append((i, e0, e1))
             else:
                 y = ct.bmm(x, False, w, True, int8=True)
-            if world > 1:
+            if world > 1 and gather:
                 ev = torch.cuda.Event()
                 ev.record(stream)
                 with torch.cuda.stream(comm_stream):
@@ -229,7 +229,7 @@ def run_ours(args) -> None:
                     layers[i].gather(y, out=gathered[i])
                 y.record_stream(comm_stream)
             results.append(y)
-        if world > 1:
+        if world > 1 and gather:
             stream.wait_stream(comm_stream)
         return results
 
@@ -255,10 +255,28 @@ def run_ours(args) -> None:
     e1.record(stream)
     barrier()
     ms_total = e0.elapsed_time(e1)
-    # ---- same region again with events around each GEMM launch: per-kernel duration for the roofline ----
+    # ---- same region again with events around each GEMM launch: per-kernel duration for the roofline
+    #      (without the all-gather, whose copy kernels would otherwise share the SMs with the GEMM being timed) ----
     for _ in range(args.steps):
-        step(record_gemm=True)
+        step(record_gemm=True, gather=False)
     barrier()
+    phases = None
+    if world > 1:
+        # compute phase alone (no exchange), to separate GEMM-phase scaling from the NVLink-bound gather
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        p0.record(stream)
+        for _ in range(args.steps):
+            step(gather=False)
+        p1.record(stream)
+        barrier()
+        t = torch.tensor([p0.elapsed_time(p1) / args.steps], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_compute = float(t.item())
+        gather_bytes = sum(2 * M_TOKENS * n for _, n, _ in SHAPES) * (world - 1) // world
+        phases = {"compute_only_ms_per_step": ms_compute, "compute_only_tops": total_ops() / (ms_compute * 1e-3) / 1e12,
+                  "allgather_bytes_received_per_rank_per_step": gather_bytes,
+                  "note": "the all-gather of fp16 outputs moves (g-1)/g * 2*M*N bytes into every rank per linear and bounds the step for g >= 2"}
     clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
@@ -276,8 +294,10 @@ def run_ours(args) -> None:
     peak_tops = 2.0 * peaks["bf16_tflops"]
     roofline = {
         "bound": "tensor", "achieved": gemm_tops, "peak": peak_tops, "unit": "TOPS", "frac": gemm_tops / peak_tops,
-        "traffic": None,
-        "kernel": "gemm_i8_tc_kernel<dequant> (tcgen05 kind::i8)",
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of these four launches at N = 1
+        # (profiles/gemm_i8_tc2_kernel_cpm-bee-linears_M4096.md): 125.2 / 35.0 / 98.0 / 124.3 MB, mean of the four
+        "traffic": 95.6e6 if (world == 1 and M_TOKENS == 4096) else None,
+        "kernel": "gemm_i8_tc2_kernel<dequant> (tcgen05.mma cta_group::2 kind::i8, 256x256 tiles per CTA pair)",
         "peak_note": "2 x %s dense bf16 %s TFLOP/s (burst; no int8 figure is measured on this pool); nominal dense int8 is 4500 TOPS: frac_nominal below"
                      % (peaks["source"], peaks["bf16_tflops"]),
         "frac_nominal": gemm_tops / 4500.0,
@@ -391,7 +411,7 @@ def run_ours(args) -> None:
                    "l2": "per-step working set (fp16 weights 302 MB + activations 134 MB + outputs 252 MB) exceeds the 126 MB L2; no explicit flush",
                    "weights": "re-quantised on every call, as the reference's bmm does"},
         "roofline": roofline, "e2e": e2e, "gpu_launches": 12 * args.steps, "clocks": clocks,
-        "gemv": gemv, "device_status_word": status,
+        "gemv": gemv, "phases": phases, "device_status_word": status,
         "peaks": {k: peaks.get(k) for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained", "source")},
     }
     if base is not None:
