@@ -5,7 +5,12 @@
 //
 // Replaces cuda/gemm.cu:6-205 of the reference (one 1024-thread block per row, 2-byte loads, 1-byte
 // stores, an fp32 division per element, grid.y = n <= 65535).
+#include <stdlib.h>
+
+#include <mutex>
+
 #include "cpmk_common.cuh"
+#include "cpmk_ptx.cuh"
 #include "cpmk_round_rule.h"
 
 namespace cpmk {
@@ -313,6 +318,161 @@ __global__ void __launch_bounds__(kBlock) quant_cols_round_kernel(int32_t n, int
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Streaming form of the fused column quantisation for operands of a few MB and more.  Same two passes, but each
+// block owns a strip of up to 2048 columns (4 KiB row segments) and a range of rows, and pulls the segments through
+// a 3-stage shared-memory ring with 1-d bulk asynchronous copies (one producer thread; eight segments per stage;
+// two blocks per SM), so that ~190 KiB per SM are in flight without register staging.  Each of the 256 consumer
+// threads owns eight columns.  PASS 0 leaves per-range column maxima in scratch; PASS 1 folds them, derives the
+// scales and rounds, walking ranges and rows in the opposite order so that it starts on what L2 still holds.
+// ------------------------------------------------------------------------------------------------
+constexpr int kCsCols = 2048;
+constexpr int kCsRows = 8;
+constexpr int kCsStages = 3;
+constexpr int kCsStageBytes = kCsRows * kCsCols * 2;            // 32 KiB
+constexpr int kCsRingBytes = kCsStages * kCsStageBytes;         // 96 KiB
+constexpr int kCsThreads = (kCsRows + 1) * 32;                  // 8 consumer warps + 1 producer warp
+constexpr uint32_t kErrColqProducer = 0x301;
+constexpr uint32_t kErrColqConsumer = 0x302;
+
+template <int PASS>
+__global__ void __launch_bounds__(kCsThreads, 2) quant_cols_stream_kernel(int32_t n, int32_t m, int32_t rows_per_split, int32_t splits,
+                                                                          int32_t strip_cols, const __half *__restrict__ mat, __half *__restrict__ partial,
+                                                                          __half *__restrict__ scale, int8_t *__restrict__ out,
+                                                                          uint32_t *status) {
+    extern __shared__ __align__(128) uint8_t ring[];
+    __shared__ __align__(8) uint64_t bars[2 * kCsStages];
+    __shared__ uint32_t abort_word;
+    const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + kCsStages);
+    const uint32_t ring_base = smem_u32(ring);
+    volatile uint32_t *abort_flag = &abort_word;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int strip = blockIdx.x, b = blockIdx.z, batch = gridDim.z;
+    const int split = PASS == 0 ? (int)blockIdx.y : (int)(gridDim.y - 1 - blockIdx.y);
+    const int c0 = strip * strip_cols;                                  // strip_cols <= kCsCols, a multiple of 8
+    const int width = (m - c0) < strip_cols ? (m - c0) : strip_cols;
+    const uint32_t seg_bytes = (uint32_t)width * 2u;
+    const int i0 = split * rows_per_split;
+    const int i1 = min(n, i0 + rows_per_split);
+    const int groups = (i1 - i0 + kCsRows - 1) / kCsRows;
+    const __half *base = mat + (int64_t)b * n * m + c0;
+
+    if (threadIdx.x == 0) {
+        for (int st = 0; st < kCsStages; ++st) {
+            mbar_init(full_bar + 8 * st, 1);
+            mbar_init(empty_bar + 8 * st, kCsRows);
+        }
+        abort_word = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == kCsRows) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            for (int gi = 0; gi < groups; ++gi) {
+                const int g = PASS == 0 ? gi : groups - 1 - gi;
+                if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrColqProducer)) break;
+                const int row = i0 + g * kCsRows;
+                const int nr = (i1 - row) < kCsRows ? (i1 - row) : kCsRows;
+                mbar_expect_tx(full_bar + 8 * stage, (uint32_t)nr * seg_bytes);
+                for (int r = 0; r < nr; ++r)
+                    bulk_load_1d(ring_base + stage * kCsStageBytes + (uint32_t)r * (kCsCols * 2), base + (int64_t)(row + r) * m, seg_bytes,
+                                 full_bar + 8 * stage);
+                if (++stage == kCsStages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else {
+        const int t = threadIdx.x;                           // 0..255: columns c0 + 8 t .. + 7
+        const bool col_ok = t * 8 < width;
+        const int col = c0 + t * 8;
+        __half2 m2[4];
+        float s[8], r_up[8], r_dn[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) m2[i] = __float2half2_rn(0.f);
+        if (PASS == 1 && col_ok) {
+            for (int sp = 0; sp < splits; ++sp) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(partial + ((int64_t)sp * batch + b) * m + col));
+                const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) m2[i] = __hmax2(h[i], m2[i]);
+            }
+            __align__(16) __half sh[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 a = __half22float2(m2[i]);
+                sh[2 * i] = scale_from_amax(a.x);
+                sh[2 * i + 1] = scale_from_amax(a.y);
+                s[2 * i] = __half2float(sh[2 * i]);
+                s[2 * i + 1] = __half2float(sh[2 * i + 1]);
+                cpmk_round_prepare(s[2 * i], &r_up[2 * i], &r_dn[2 * i]);
+                cpmk_round_prepare(s[2 * i + 1], &r_up[2 * i + 1], &r_dn[2 * i + 1]);
+                if (!(cpmk_scale_in_domain(s[2 * i]) && cpmk_round_domain_ok(a.x, r_up[2 * i]))) r_up[2 * i] = __int_as_float(0x7fc00000);
+                if (!(cpmk_scale_in_domain(s[2 * i + 1]) && cpmk_round_domain_ok(a.y, r_up[2 * i + 1]))) r_up[2 * i + 1] = __int_as_float(0x7fc00000);
+            }
+            if (split == 0) *reinterpret_cast<uint4 *>(scale + (int64_t)b * m + col) = *reinterpret_cast<const uint4 *>(sh);
+        }
+        int8_t *obase = out + (int64_t)b * n * m + col;
+        uint32_t stage = 0, phase = 0;
+        for (int gi = 0; gi < groups; ++gi) {
+            const int g = PASS == 0 ? gi : groups - 1 - gi;
+            const int row = i0 + g * kCsRows;
+            const int nr = (i1 - row) < kCsRows ? (i1 - row) : kCsRows;
+            if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kErrColqConsumer)) break;
+            if (col_ok) {
+                const uint8_t *src = ring + (size_t)stage * kCsStageBytes + (size_t)t * 16;
+#pragma unroll
+                for (int r = 0; r < kCsRows; ++r) {
+                    if (r < nr) {
+                        const uint4 w = *reinterpret_cast<const uint4 *>(src + (size_t)r * (kCsCols * 2));
+                        const __half2 *h = reinterpret_cast<const __half2 *>(&w);
+                        if (PASS == 0) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) m2[j] = __hmax2(__habs2(h[j]), m2[j]);
+                        } else {
+                            uint32_t bits[8];
+                            float2 bad = make_float2(0.f, 0.f);
+                            const float2 magic = make_float2(CPMK_ROUND_MAGIC, CPMK_ROUND_MAGIC);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float2 f = __half22float2(h[j]);
+                                const float2 up = __ffma2_rn(f, make_float2(r_up[2 * j], r_up[2 * j + 1]), magic);
+                                const float2 dn = __ffma2_rn(f, make_float2(r_dn[2 * j], r_dn[2 * j + 1]), magic);
+                                const float2 d = __fadd2_rn(up, make_float2(-dn.x, -dn.y));
+                                bad = __ffma2_rn(d, d, bad);
+                                bits[2 * j] = __float_as_uint(dn.x);
+                                bits[2 * j + 1] = __float_as_uint(dn.y);
+                            }
+                            if (!(bad.x + bad.y == 0.f)) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float2 f = __half22float2(h[j]);
+                                    bits[2 * j] = (uint8_t)round_reference(f.x, s[2 * j]);
+                                    bits[2 * j + 1] = (uint8_t)round_reference(f.y, s[2 * j + 1]);
+                                }
+                            }
+                            uint2 q;
+                            q.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+                            q.y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
+                            *reinterpret_cast<uint2 *>(obase + (int64_t)(row + r) * m) = q;
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar + 8 * stage);
+            if (++stage == kCsStages) { stage = 0; phase ^= 1u; }
+        }
+        if (PASS == 0 && col_ok && !*abort_flag)
+            *reinterpret_cast<uint4 *>(partial + ((int64_t)split * batch + b) * m + col) = *reinterpret_cast<const uint4 *>(m2);
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);     // let copies in flight land before the ring is released
+    }
+}
+
 // Any shape: one thread per column, the reference expressions (m not a multiple of 8).
 template <int MODE>
 __global__ void __launch_bounds__(kBlock) quant_cols_generic_kernel(int32_t batch, int32_t n, int32_t m, const __half *__restrict__ mat,
@@ -572,6 +732,41 @@ int32_t launch_quant_cols(int32_t batch, int32_t n, int32_t m, const void *mat, 
         colmax_finish_kernel<<<(unsigned)blocks, kBlock, 0, stream>>>(batch, m, p.splits, partial, sc);
         CPMK_LAUNCH_CHECK();
         return CPMK_OK;
+    }
+    // Operands of 64 MB and more (below that the register-staged kernels measured faster): the streaming kernels
+    // (96 KiB ring, two blocks per SM).
+    if ((int64_t)batch * n * m >= (int64_t(1) << 25) && n >= 64 && m >= 1024 && info.max_smem_optin >= kCsRingBytes + 1024 && !getenv("CPMK_QUANT_NO_STREAM")) {
+        static std::once_flag attr_once[64];
+        static cudaError_t attr_err[64];
+        const int dev = info.device & 63;
+        std::call_once(attr_once[dev], [dev] {
+            cudaError_t e = cudaFuncSetAttribute(quant_cols_stream_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCsRingBytes);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(quant_cols_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCsRingBytes);
+            attr_err[dev] = e;
+        });
+        if (attr_err[dev] == cudaSuccess) {
+            // strips of equal width, at most 2048 columns (narrower strips mean bulk copies of 1 KiB and less: measured slower)
+            const int64_t by_rows = (n + 63) / 64;
+            const int64_t target = (int64_t)info.sm_count * 2;
+            int strips = (m + kCsCols - 1) / kCsCols;
+            const int strip_cols = ((m + strips - 1) / strips + 7) / 8 * 8;
+            strips = (m + strip_cols - 1) / strip_cols;
+            int64_t sp = target / ((int64_t)strips * batch);
+            if (sp > by_rows) sp = by_rows;
+            const int64_t by_scratch = (int64_t)(Workspace::kScratchBytes / (sizeof(__half) * (size_t)batch * (size_t)m));
+            if (sp > by_scratch) sp = by_scratch;
+            if (sp > 65535) sp = 65535;
+            if (sp < 1) sp = 1;
+            int rps = (int)((n + sp - 1) / sp);
+            rps = (rps + kCsRows - 1) / kCsRows * kCsRows;
+            const int nsp = (n + rps - 1) / rps;
+            const dim3 grid(strips, nsp, batch);
+            quant_cols_stream_kernel<0><<<grid, kCsThreads, kCsRingBytes, stream>>>(n, m, rps, nsp, strip_cols, src, partial, sc, dst, ws.status());
+            CPMK_LAUNCH_CHECK();
+            quant_cols_stream_kernel<1><<<grid, kCsThreads, kCsRingBytes, stream>>>(n, m, rps, nsp, strip_cols, src, partial, sc, dst, ws.status());
+            CPMK_LAUNCH_CHECK();
+            return CPMK_OK;
+        }
     }
     // Fused form: absmax pass, then rounding pass over the same operand in the opposite row order.  (Walking the
     // operand in L2-sized column panels, so that the second read never reaches HBM, was tried and measured slower:

@@ -49,6 +49,7 @@ COL_SHAPES = [
     (1, 4, 4), (3, 12, 12), (2, 33, 40),           # generic path
     (1, 7, 8), (2, 31, 64), (1, 32, 72), (1, 1000, 200),
     (1, 1024, 1536), (8, 512, 256), (1, 4096, 512), (2, 65, 4096),
+    (1, 16000, 2056), (3, 7000, 1600), (2, 16411, 1024),  # streaming kernels: ragged strips, ragged row ranges, batches
 ]
 
 
