@@ -84,7 +84,7 @@ __device__ __forceinline__ uint2 round8_one_scale(const uint4 &v, float s, float
 // ------------------------------------------------------------------------------------------------
 // FULL: every block has all its rows and every thread all NV vectors (no bounds predicates).
 template <int NV, int MODE, bool FULL>
-__global__ void __launch_bounds__(kBlock) quant_rows_kernel(int64_t rows, int32_t m, int group, const __half *__restrict__ mat,
+__global__ void __launch_bounds__(kBlock, NV <= 4 ? 6 : 4) quant_rows_kernel(int64_t rows, int32_t m, int group, const __half *__restrict__ mat,
                                                             __half *__restrict__ scale, int8_t *__restrict__ out) {
     __shared__ float warp_max[kBlock / 32];
     const int tid = threadIdx.x;
