@@ -58,6 +58,7 @@ struct GemmParams {
     const __half *scale_r;        // (bcast_r ? 1 : batch, R)   multiplies first
     const __half *scale_c;        // (bcast_c ? 1 : batch, C)
     int32_t bcast_r, bcast_c;
+    int32_t tma_store;            // the two-CTA kernel writes its output with TMA stores (needs 16-byte row pitch)
     uint32_t *status;
 };
 
@@ -149,7 +150,7 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 // row_base + 32*quarter + lane, all kBN columns from col_base, 32 columns per tcgen05.ld.
 template <bool DEQUANT>
 __device__ __forceinline__ void epilogue_rows(const GemmParams &prm, uint32_t tmem_base, uint32_t acc, int quarter, int lane, int b,
-                                              int row_base, int col_base) {
+                                              int row_base, int col_base, int chunk_begin = 0, int chunk_end = kBN / 32) {
     const int row = row_base + quarter * 32 + lane;
     const bool row_ok = row < prm.R;
     const int64_t out_row = ((int64_t)b * prm.R + (row_ok ? row : 0)) * prm.C;
@@ -157,7 +158,7 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams &prm, uint32_t tm
     if (DEQUANT && row_ok) sr = __half2float(__ldg(prm.scale_r + (prm.bcast_r ? 0 : (int64_t)b * prm.R) + row));
     const __half *sc = DEQUANT ? prm.scale_c + (prm.bcast_c ? 0 : (int64_t)b * prm.C) : nullptr;
 #pragma unroll 1
-    for (int chunk = 0; chunk < kBN / 32; ++chunk) {
+    for (int chunk = chunk_begin; chunk < chunk_end; ++chunk) {
         const int col0 = col_base + chunk * 32;
         if (col0 >= prm.C) break;                    // uniform across the warp
         uint32_t v[32];
@@ -335,17 +336,22 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_const
 // tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of the row operand and 128 of the 256 rows of
 // the column operand (the tensor cores of the pair read both halves), so per MMA a CTA's shared memory serves
 // 8 KiB instead of 12 KiB and receives 8 KiB instead of 12 KiB from TMA: the shared-memory port stops being
-// the limiter.  Stages shrink to 32 KiB, so the ring holds 6 of them.
+// the limiter.  Stages shrink to 32 KiB; the ring holds 5 of them, and 64 KiB stage the output of eight epilogue
+// warps (two per TMEM lane quarter, 128 columns each) on its way to TMA stores.
 //   - both CTAs run a producer warp; every load signals the full barrier of CTA 0 (the leader), whose producer
 //     posts the expected byte count of both CTAs;
 //   - only the leader issues MMAs; its commits arrive on the empty / accumulator-full barriers of both CTAs;
 //   - the epilogue warps of both CTAs arrive on the leader's accumulator-empty barrier.
 // ------------------------------------------------------------------------------------------------
-constexpr int kStages2 = 6;
+constexpr int kStages2 = 5;
+constexpr int kEpiWarps2 = 8;                          // two epilogue warps per TMEM lane quarter, 128 columns each
+constexpr int kTcThreads2 = (2 + kEpiWarps2) * 32;
 constexpr int kHalfBN = kBN / 2;                       // rows of the column operand staged per CTA
 constexpr int kQBytes2 = kHalfBN * kBK;                // 16 KiB
 constexpr int kStageBytes2 = kPBytes + kQBytes2;       // 32 KiB
-constexpr int kTc2SmemBytes = kStages2 * kStageBytes2 + 1024 + kBarrierBytes;
+constexpr int kOutStageBytes = 32 * 128;                // one epilogue warp's staging tile: 32 rows x 128 bytes
+constexpr int kOutStagingBytes = 8 * 2 * kOutStageBytes; // eight epilogue warps, double-buffered: 64 KiB
+constexpr int kTc2SmemBytes = kStages2 * kStageBytes2 + kOutStagingBytes + 1024 + kBarrierBytes;
 constexpr uint32_t kInstrDesc2 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)((2 * kBM) >> 4) << 24);
 
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
@@ -393,15 +399,117 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask
                  ::"r"(bar), "h"(cta_mask) : "memory");
 }
 
+// TMA store of a staged 32-row x 128-byte tile (128-byte swizzle) to the 3-d output map; out-of-range rows and
+// columns are clipped by the hardware.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int32_t c0, int32_t c1, int32_t c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// Epilogue of one warp for one finished accumulator, written through shared memory with TMA stores: the warp's
+// 32 rows x 256 columns leave as 128-byte-wide pieces (64 fp16 or 32 int32 columns): each lane converts its row,
+// writes it into a swizzled 32 x 128-byte staging tile (16-byte chunk j of row r at chunk j ^ (r & 7): no bank
+// conflicts, and what the store's 128-byte swizzle expects), and lane 0 issues the store.  Two staging tiles per
+// warp alternate, so converting piece i+1 overlaps the store of piece i; the stores are full lines and need no
+// edge predicates.
+template <bool DEQUANT>
+__device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const CUtensorMap *tmap_o, uint32_t staging, uint32_t &buf,
+                                                  uint32_t tmem_base, uint32_t acc, int quarter, int lane, int b, int row_base, int col_base,
+                                                  int half) {
+    const int row = row_base + quarter * 32 + lane;
+    const bool row_ok = row < prm.R;
+    float sr = 0.f;
+    if (DEQUANT && row_ok) sr = __half2float(__ldg(prm.scale_r + (prm.bcast_r ? 0 : (int64_t)b * prm.R) + row));
+    const __half *sc = DEQUANT ? prm.scale_c + (prm.bcast_c ? 0 : (int64_t)b * prm.C) : nullptr;
+    const int warp_col = col_base + half * (kBN / 2);                // this warp's 128 columns
+    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN + half * (kBN / 2);
+    const uint32_t sw = (uint32_t)(lane & 7);
+    constexpr int kSteps = (kBN / 2) / 32;                           // four steps of 32 columns
+    constexpr int kStepsPerPiece = DEQUANT ? 2 : 1;                  // a stored piece is 128 bytes wide: 64 fp16 / 32 int32
+
+    // Software pipeline over the steps: the tensor-memory load and the column scales of step i+1 are requested
+    // before step i is converted, so their latencies hide behind the arithmetic and the shared-memory writes.
+    uint32_t v[2][32];
+    uint4 cs[2][4];
+    auto request = [&](int st, int slot) {
+        tmem_ld_32x32b_x32(taddr + st * 32, v[slot]);
+        if (DEQUANT) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const int c = warp_col + st * 32 + g * 8;
+                cs[slot][g] = c < prm.C ? __ldg(reinterpret_cast<const uint4 *>(sc + c)) : make_uint4(0, 0, 0, 0);   // C % 8 == 0 here
+            }
+        }
+    };
+    if (warp_col >= prm.C) return;                                   // uniform across the warp
+    request(0, 0);
+#pragma unroll
+    for (int st = 0; st < kSteps; ++st) {
+        const int slot = st & 1;
+        const int col0 = warp_col + st * 32;
+        tmem_ld_wait();                                              // step st has arrived
+        if (st + 1 < kSteps) request(st + 1, slot ^ 1);
+        const bool first_of_piece = (st % kStepsPerPiece) == 0;
+        const bool last_of_piece = (st % kStepsPerPiece) == kStepsPerPiece - 1;
+        const int piece_col = col0 - (st % kStepsPerPiece) * 32;
+        if (piece_col >= prm.C) continue;                            // nothing of this piece is inside the output (uniform)
+        const uint32_t tile = staging + buf * kOutStageBytes;
+        const uint32_t my_row = tile + (uint32_t)lane * 128u;
+        if (first_of_piece) {
+            // the store issued two pieces ago read this tile: it must have finished reading
+            if (lane == 0) bulk_wait_read<1>();
+            __syncwarp();
+        }
+        if (DEQUANT) {
+            const uint32_t chunk0 = (uint32_t)(st % kStepsPerPiece) * 4u;      // 16-byte chunks 0-3 or 4-7 of the 128-byte row
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const __half2 *sh = reinterpret_cast<const __half2 *>(&cs[slot][g]);
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 s2 = __half22float2(sh[e]);
+                    const float a0 = __fmul_rn(__fmul_rn((float)(int32_t)v[slot][g * 8 + 2 * e], sr), s2.x);
+                    const float a1 = __fmul_rn(__fmul_rn((float)(int32_t)v[slot][g * 8 + 2 * e + 1], sr), s2.y);
+                    o[e] = pack_half2(a0, a1);
+                }
+                st_shared_v4(my_row + (((chunk0 + (uint32_t)g) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+            }
+        } else {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)                              // eight 16-byte chunks = 32 int32 columns
+                st_shared_v4(my_row + (((uint32_t)g ^ sw) << 4), v[slot][4 * g], v[slot][4 * g + 1], v[slot][4 * g + 2], v[slot][4 * g + 3]);
+        }
+        if (last_of_piece) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(tmap_o, tile, piece_col, row_base + quarter * 32, b);
+                bulk_commit();
+            }
+            buf ^= 1u;
+        }
+    }
+}
+
 // P_MN / Q_MN: the row / column operand is stored with its rows contiguous (k is the slow axis) instead of k:
 // the reference's bT / !aT layouts.  Their tensor maps then have (rows, k, batch) extents and 128 x kBK boxes, the
 // shared-memory tiles are MN-major, and bits 15 / 16 of the instruction descriptor say so.
 template <bool DEQUANT, bool P_MN, bool Q_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
-gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q, const GemmParams prm) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads2, 1)
+gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
+                   const __grid_constant__ CUtensorMap tmap_o, const GemmParams prm) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars_base = tiles_base + kStages2 * kStageBytes2;
+    const uint32_t staging_base = tiles_base + kStages2 * kStageBytes2;       // 1024-byte aligned: swizzle atoms
+    const uint32_t bars_base = staging_base + kOutStagingBytes;
     const uint32_t full_bar = bars_base;                          // used in the leader only
     const uint32_t empty_bar = bars_base + 8 * kStages2;
     const uint32_t tmem_full_bar = bars_base + 16 * kStages2;
@@ -421,7 +529,7 @@ gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tmem_full_bar + 8 * a, 1);
-            mbar_init(tmem_empty_bar + 8 * a, 8);      // four epilogue warps in each of the two CTAs
+            mbar_init(tmem_empty_bar + 8 * a, 2 * kEpiWarps2);   // the epilogue warps of both CTAs
         }
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -494,20 +602,26 @@ gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
     } else {
         // ---------------- epilogue (both CTAs; each owns 128 of the tile's 256 rows) ----------------
         const int quarter = warp & 3;
-        uint32_t acc = 0, acc_phase = 0;
+        uint32_t acc = 0, acc_phase = 0, out_buf = 0;
         for (int tile = pair; tile < prm.total_tiles; tile += num_pairs) {
             const int b = tile / tiles_per_batch;
             const int rem = tile - b * tiles_per_batch;
             const int c_blk = rem / prm.tiles_r, r_blk = rem - c_blk * prm.tiles_r;
             if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, prm.status, kErrEpilogueWait)) break;
             tcgen05_fence_after();
-            epilogue_rows<DEQUANT>(prm, tmem_base, acc, quarter, lane, b, r_blk * (2 * kBM) + (int)rank * kBM, c_blk * kBN);
+            const int half = (warp - 2) >> 2;            // which 128 of the tile's 256 columns this warp writes
+            if (prm.tma_store)
+                epilogue_rows_tma<DEQUANT>(prm, &tmap_o, staging_base + (uint32_t)(warp - 2) * 2u * kOutStageBytes, out_buf, tmem_base, acc, quarter,
+                                           lane, b, r_blk * (2 * kBM) + (int)rank * kBM, c_blk * kBN, half);
+            else
+                epilogue_rows<DEQUANT>(prm, tmem_base, acc, quarter, lane, b, r_blk * (2 * kBM) + (int)rank * kBM, c_blk * kBN, half * 4, half * 4 + 4);
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(tmem_empty_bar + 8 * acc, 0));
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
         }
+        if (lane == 0) bulk_wait_all();                  // this warp's output stores have completed
     }
 
     // ---------------- teardown: neither CTA may leave while its partner can still touch its memory ----------------
@@ -665,6 +779,21 @@ bool encode_operand_mn(CUtensorMap *map, const void *ptr, int32_t rows, int32_t 
     return r == CUDA_SUCCESS;
 }
 
+// Output (batch, R, C) as a 3-d tensor map whose box is 32 rows x 128 bytes, 128-byte swizzle (for TMA stores).
+bool encode_output(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int32_t batch, bool fp16) {
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return false;
+    const cuuint64_t esz = fp16 ? 2 : 4;
+    const cuuint64_t dims[3] = {(cuuint64_t)C, (cuuint64_t)R, (cuuint64_t)batch};
+    const cuuint64_t strides[2] = {(cuuint64_t)C * esz, (cuuint64_t)R * (cuuint64_t)C * esz};
+    const cuuint32_t box[3] = {(cuuint32_t)(128 / esz), 32u, 1u};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    const CUresult r = enc(map, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_INT32, 3, ptr, dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 thread_local int32_t g_last_path = 0;
 thread_local int32_t g_last_variant = 0;
 
@@ -702,7 +831,7 @@ int32_t prepare_tc_kernels(int device) {
         if (e != cudaSuccess) return;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2, 1, 1);
-        cfg.blockDim = dim3(kTcThreads, 1, 1);
+        cfg.blockDim = dim3(kTcThreads2, 1, 1);
         cfg.dynamicSmemBytes = kTc2SmemBytes;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -770,6 +899,7 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
         prm.out = out;
         prm.scale_r = static_cast<const __half *>(scale_x); prm.scale_c = static_cast<const __half *>(scale_y);
         prm.bcast_r = bx; prm.bcast_c = by;
+        prm.tma_store = 0;
         prm.status = ws.status();
         rc = prepare_tc_kernels(info.device);
         if (rc) return rc;
@@ -787,10 +917,14 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
                 prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.total_tiles = (int32_t)total;
                 const int pairs = (int)(total < max_pairs ? total : max_pairs);
                 const dim3 grid(2 * pairs);
-                if (!p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, false, false><<<grid, kTcThreads, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, prm);
-                else if (!p_mn && q_mn) gemm_i8_tc2_kernel<DEQUANT, false, true><<<grid, kTcThreads, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, prm);
-                else if (p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, true, false><<<grid, kTcThreads, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, prm);
-                else gemm_i8_tc2_kernel<DEQUANT, true, true><<<grid, kTcThreads, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, prm);
+                CUtensorMap tmap_o;
+                prm.tma_store = ((int64_t)m * (DEQUANT ? 2 : 4)) % 16 == 0 && !getenv("CPMK_GEMM_NO_TMA_STORE") &&
+                                encode_output(&tmap_o, out, n, m, batch, DEQUANT);
+                if (!prm.tma_store) memset(&tmap_o, 0, sizeof(tmap_o));
+                if (!p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, false, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+                else if (!p_mn && q_mn) gemm_i8_tc2_kernel<DEQUANT, false, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+                else if (p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, true, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+                else gemm_i8_tc2_kernel<DEQUANT, true, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
                 CPMK_LAUNCH_CHECK();
                 g_last_path = 1;
                 g_last_variant = 2;
