@@ -180,8 +180,15 @@ def run_ours(args) -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    saved_stdout = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # the collective's kernels run beside the persistent GEMM grid: leave them a few SMs
+        os.environ.setdefault("CPMK_GEMM_SM_MARGIN", "16")
+        # libraries print banners on stdout when a communicator is created: keep stdout for the one JSON line
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=dev)
     cpmk.check_device()
     peaks = measured_peaks()
@@ -295,8 +302,8 @@ def run_ours(args) -> None:
     roofline = {
         "bound": "tensor", "achieved": gemm_tops, "peak": peak_tops, "unit": "TOPS", "frac": gemm_tops / peak_tops,
         # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of these four launches at N = 1
-        # (profiles/gemm_i8_tc2_kernel_cpm-bee-linears_M4096.md): 125.2 / 35.0 / 98.0 / 124.3 MB, mean of the four
-        "traffic": 95.6e6 if (world == 1 and M_TOKENS == 4096) else None,
+        # (profiles/gemm_i8_tc2_kernel_cpm-bee-linears_M4096.md): 131.0 / 36.8 / 104.9 / 133.2 MB, mean of the four
+        "traffic": 101.5e6 if (world == 1 and M_TOKENS == 4096) else None,
         "kernel": "gemm_i8_tc2_kernel<dequant> (tcgen05.mma cta_group::2 kind::i8, 256x256 tiles per CTA pair)",
         "peak_note": "2 x %s dense bf16 %s TFLOP/s (burst; no int8 figure is measured on this pool); nominal dense int8 is 4500 TOPS: frac_nominal below"
                      % (peaks["source"], peaks["bf16_tflops"]),
@@ -416,7 +423,11 @@ def run_ours(args) -> None:
     }
     if base is not None:
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
-    print(json.dumps(line))
+    if saved_stdout is not None:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        os.close(saved_stdout)
+    print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 

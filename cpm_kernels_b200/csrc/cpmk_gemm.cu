@@ -905,7 +905,13 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
         if (rc) return rc;
         CUtensorMap tmap_p, tmap_q;
         // ---- two-CTA form: 256 x 256 tiles per CTA pair; worth it once there is more than one 128-row block ----
-        const int max_pairs = g_max_pairs[info.device & 63];
+        // CPMK_GEMM_SM_MARGIN=n leaves n SMs free of the persistent GEMM grid, so that kernels of a concurrent stream
+        // (the collective that gathers output slices across GPUs) find room to run beside it
+        int max_pairs = g_max_pairs[info.device & 63];
+        if (const char *mg = getenv("CPMK_GEMM_SM_MARGIN")) {
+            const int margin_pairs = (atoi(mg) + 1) / 2;
+            if (margin_pairs > 0 && max_pairs - margin_pairs >= 8) max_pairs -= margin_pairs;
+        }
         const bool any_mn = p_mn || q_mn;                   // MN-major operands are implemented in the two-CTA kernel only
         if (variant != kVariantOneCta && max_pairs > 0 && (n > kBM || variant == kVariantTwoCta || any_mn)) {
             const int64_t tiles_r = (n + 2 * kBM - 1) / (2 * kBM), tiles_c = (m + kBN - 1) / kBN;
