@@ -751,8 +751,59 @@ EncodeTiledFn get_encode_tiled() {
     return fn;
 }
 
-// int8 operand (batch, rows, k) with k contiguous, as a 3-d tensor map whose box is box_rows x 128 bytes.
+// Encoding a tensor map costs a microsecond or two of host time and a GEMM needs three; callers reuse the same
+// buffers call after call (weights, and whatever the framework's caching allocator hands back), so the last few
+// encodings are kept per thread, keyed by everything that went into them.
+struct MapKey {
+    const void *ptr;
+    int32_t a, b, c, kind;
+    bool operator==(const MapKey &o) const { return ptr == o.ptr && a == o.a && b == o.b && c == o.c && kind == o.kind; }
+};
+struct MapCache {
+    static constexpr int kEntries = 32;
+    MapKey keys[kEntries];
+    CUtensorMap maps[kEntries];
+    int used = 0, next = 0;
+    const CUtensorMap *find(const MapKey &k) const {
+        for (int i = 0; i < used; ++i)
+            if (keys[i] == k) return &maps[i];
+        return nullptr;
+    }
+    void put(const MapKey &k, const CUtensorMap &m) {
+        const int slot = used < kEntries ? used++ : (next++ % kEntries);
+        keys[slot] = k;
+        maps[slot] = m;
+    }
+};
+thread_local MapCache g_map_cache;
+
+bool encode_operand_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int32_t box_rows);
+bool encode_operand_mn_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch);
+bool encode_output_raw(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int32_t batch, bool fp16);
+
+template <typename F>
+bool cached_encode(CUtensorMap *map, const MapKey &key, F &&encode) {
+    if (const CUtensorMap *hit = g_map_cache.find(key)) {
+        *map = *hit;
+        return true;
+    }
+    if (!encode()) return false;
+    g_map_cache.put(key, *map);
+    return true;
+}
+
 bool encode_operand(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int32_t box_rows) {
+    return cached_encode(map, MapKey{ptr, rows, k, batch, 0x100 + box_rows}, [&] { return encode_operand_raw(map, ptr, rows, k, batch, box_rows); });
+}
+bool encode_operand_mn(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch) {
+    return cached_encode(map, MapKey{ptr, rows, k, batch, 1}, [&] { return encode_operand_mn_raw(map, ptr, rows, k, batch); });
+}
+bool encode_output(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int32_t batch, bool fp16) {
+    return cached_encode(map, MapKey{ptr, R, C, batch, fp16 ? 2 : 3}, [&] { return encode_output_raw(map, ptr, R, C, batch, fp16); });
+}
+
+// int8 operand (batch, rows, k) with k contiguous, as a 3-d tensor map whose box is box_rows x 128 bytes.
+bool encode_operand_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int32_t box_rows) {
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) return false;
     const cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)batch};
@@ -766,7 +817,7 @@ bool encode_operand(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, 
 }
 
 // int8 operand stored (batch, k, rows) with the rows contiguous, as a 3-d tensor map whose box is 128 rows x kBK of k.
-bool encode_operand_mn(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch) {
+bool encode_operand_mn_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch) {
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) return false;
     const cuuint64_t dims[3] = {(cuuint64_t)rows, (cuuint64_t)k, (cuuint64_t)batch};
@@ -780,7 +831,7 @@ bool encode_operand_mn(CUtensorMap *map, const void *ptr, int32_t rows, int32_t 
 }
 
 // Output (batch, R, C) as a 3-d tensor map whose box is 32 rows x 128 bytes, 128-byte swizzle (for TMA stores).
-bool encode_output(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int32_t batch, bool fp16) {
+bool encode_output_raw(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int32_t batch, bool fp16) {
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) return false;
     const cuuint64_t esz = fp16 ? 2 : 4;

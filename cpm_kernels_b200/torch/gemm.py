@@ -87,6 +87,32 @@ def gemm_and_scale(quantA: torch.Tensor, scaleA: Optional[torch.Tensor], quantB:
     return result_fp
 
 
+def _int8_forward(A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool):
+    """The three launches of the forward pass with one device guard and one stream lookup.
+    Returns (result, scale_A, quantized_A, scale_B, quantized_B)."""
+    dev = A.device
+    bA, bB = A.size(0), B.size(0)
+    M = A.size(2) if aT else A.size(1)
+    K = A.size(1) if aT else A.size(2)
+    N = B.size(1) if bT else B.size(2)
+    scale_A = torch.empty((bA, M), dtype=torch.half, device=dev)
+    scale_B = torch.empty((bB, N), dtype=torch.half, device=dev)
+    quantized_A = torch.empty(A.shape, dtype=torch.int8, device=dev)
+    quantized_B = torch.empty(B.shape, dtype=torch.int8, device=dev)
+    result = torch.empty((max(bA, bB), M, N), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream().cuda_stream
+        # A is quantised along K per row of the (M, K) operand: by columns of its storage when it is stored (K, M)
+        (gemm_quantize_cols if aT else gemm_quantize_rows)(bA, A.size(1), A.size(2), A.data_ptr(), scale_A.data_ptr(),
+                                                          quantized_A.data_ptr(), stream)
+        (gemm_quantize_rows if bT else gemm_quantize_cols)(bB, B.size(1), B.size(2), B.data_ptr(), scale_B.data_ptr(),
+                                                          quantized_B.data_ptr(), stream)
+        # operands swapped (torch/gemm.py:45-52) so that the kernel-level (n, m) = (M, N) output is row-major C
+        gemm_int8_scale(N, K, M, bB, bA, bT, aT, quantized_B.data_ptr(), quantized_A.data_ptr(), scale_A.data_ptr(), scale_B.data_ptr(),
+                        bA == 1, bB == 1, result.data_ptr(), stream)
+    return result, scale_A, quantized_A, scale_B, quantized_B
+
+
 class GEMMInt8(torch.autograd.Function):
     """torch/gemm.py:84-179."""
 
@@ -97,9 +123,7 @@ class GEMMInt8(torch.autograd.Function):
         assert A.is_contiguous() and B.is_contiguous()
         assert A.dtype == torch.half and B.dtype == torch.half
 
-        scale_A, quantized_A = quantize(A, aT)
-        scale_B, quantized_B = quantize(B, not bT)
-        result = gemm_and_scale(quantized_A, scale_A, quantized_B, scale_B, aT, bT)
+        result, scale_A, quantized_A, scale_B, quantized_B = _int8_forward(A, aT, B, bT)
 
         ctx.save_for_backward(scale_A, quantized_A, scale_B, quantized_B)
         ctx.aT = aT
@@ -181,5 +205,11 @@ def bmm(A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool, int8: bool = False
     assert A.ndim == 3
     assert B.ndim == 3
     if int8:
-        return GEMMInt8.apply(A, aT, B, bT)
+        if torch.is_grad_enabled() and (A.requires_grad or B.requires_grad):
+            return GEMMInt8.apply(A, aT, B, bT)
+        # nothing to differentiate: the same forward without the autograd bookkeeping
+        assert A.is_cuda and B.is_cuda and A.device == B.device
+        assert A.is_contiguous() and B.is_contiguous()
+        assert A.dtype == torch.half and B.dtype == torch.half
+        return _int8_forward(A, aT, B, bT)[0]
     return GEMMFloat.apply(A, aT, B, bT)

@@ -117,3 +117,33 @@ def test_float_branch_is_a_plain_matmul(G):
     out = ct.bmm(a.cuda(), False, b.cuda(), True, int8=False)
     ans = torch.matmul(a.float(), b.float().transpose(-1, -2))
     assert torch.isclose(out.cpu().float(), ans, rtol=1e-2, atol=1e-2).all()
+
+
+@pytest.mark.skipif(not __import__("oracle.ref_cuda", fromlist=["x"]).available(), reason="oracle/_ref fatbins not built")
+@pytest.mark.parametrize("batch,m,k,n,tp,aT,bT", [
+    (8, 512, 4096, 2048, 0, False, False), (8, 500, 4096, 7996, 2, True, False), (8, 512, 10240, 4096, 1, False, True),
+    (8, 1024, 512, 4096, 0, True, True), (1, 4096, 4096, 12288, 0, False, True), (1, 4096, 10240, 4096, 0, False, False)])
+def test_full_size_bmm_equals_the_references_own_pipeline(G, batch, m, k, n, tp, aT, bT):
+    """The largest shapes of the reference's test list (tests/test_gemm.py:54-59) and two CPM-Bee-10B linears: the result
+    of bmm(int8=True) must equal, bit for bit, what the reference's own kernels (compiled from its sources) and its
+    cublasLt call sequence produce for the same tensors on the same GPU: calc_scale, round, gemm_int8, gemm_scale
+    (cpm_kernels/torch/gemm.py:98-104)."""
+    from oracle import ref_cuda
+    g = torch.Generator(device="cuda").manual_seed(batch + m + n)
+    bA, bB = (batch, batch) if tp == 0 else ((1, batch) if tp == 1 else (batch, 1))
+    skk = float(k) ** 0.25
+    a = (torch.randn((bA, k, m) if aT else (bA, m, k), generator=g, device="cuda") / skk).half()
+    b = (torch.randn((bB, n, k) if bT else (bB, k, n), generator=g, device="cuda") / skk).half()
+    out = ct.bmm(a, aT, b, bT, int8=True)
+    ref = ref_cuda.ReferenceKernels()
+    lt = ref_cuda.ReferenceCublasLt()
+    sa = ref.gemm_calc_scale_transpose(a) if aT else ref.gemm_calc_scale(a)
+    sb = ref.gemm_calc_scale(b) if bT else ref.gemm_calc_scale_transpose(b)
+    qa = ref.gemm_round_transpose(a, sa) if aT else ref.gemm_round(a, sa)
+    qb = ref.gemm_round(b, sb) if bT else ref.gemm_round_transpose(b, sb)
+    acc = torch.empty((max(bA, bB), m, n), dtype=torch.int32, device="cuda")
+    lt.gemm_int8(n, k, m, bB, bA, bT, aT, qb, qa, acc)                      # operands swapped as torch/gemm.py:45-52
+    want = ref.gemm_scale(acc, sa, sb, bA == 1, bB == 1)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    G.assert_no_device_error()
