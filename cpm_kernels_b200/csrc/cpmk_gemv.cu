@@ -309,6 +309,7 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_transpose_stream_kerne
         dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
         dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
+    if (tickets == nullptr) return;                      // a separate kernel adds the row ranges (many of them)
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -439,6 +440,36 @@ __global__ void __launch_bounds__(kBlock) gemv_transpose_kernel(int32_t dim_out,
         float sum = 0.f;
         for (int s = 0; s < splits; ++s) sum += __ldcg(partial + ((int64_t)s * batch + b) * dim_out + c);
         out[(int64_t)b * dim_out + c] = __float2half_rn(sum);
+    }
+}
+
+// out[b, c] = half(sum over row ranges of partial[(range * batch + b) * dim_out + c]), ranges added in order within each
+// of eight interleaved groups and the groups in order: deterministic.  32 columns per block, 8 groups of ranges.
+__global__ void __launch_bounds__(kBlock) gemv_reduce_partials_kernel(int32_t dim_out, int32_t splits, const float *__restrict__ partial,
+                                                                      __half *__restrict__ out) {
+    __shared__ float red[kWarps][32];
+    const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int b = blockIdx.y, batch = gridDim.y;
+    const int c = blockIdx.x * 32 + lane;
+    float sum = 0.f;
+    if (c < dim_out) {
+        int sp = g;
+        for (; sp + 3 * kWarps < splits; sp += 4 * kWarps) {
+            const float p0 = __ldcg(partial + ((int64_t)sp * batch + b) * dim_out + c);
+            const float p1 = __ldcg(partial + ((int64_t)(sp + kWarps) * batch + b) * dim_out + c);
+            const float p2 = __ldcg(partial + ((int64_t)(sp + 2 * kWarps) * batch + b) * dim_out + c);
+            const float p3 = __ldcg(partial + ((int64_t)(sp + 3 * kWarps) * batch + b) * dim_out + c);
+            sum += p0; sum += p1; sum += p2; sum += p3;
+        }
+        for (; sp < splits; sp += kWarps) sum += __ldcg(partial + ((int64_t)sp * batch + b) * dim_out + c);
+    }
+    red[g][lane] = sum;
+    __syncthreads();
+    if (g == 0 && c < dim_out) {
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) total += red[w][lane];
+        out[(int64_t)b * dim_out + c] = __float2half_rn(total);
     }
 }
 
@@ -676,17 +707,22 @@ int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in,
             int rps = (int)((dim_in + sp - 1) / sp);
             rps = (rps + kStreamRows - 1) / kStreamRows * kStreamRows;
             const int nsp = (dim_in + rps - 1) / rps;
-            // the block that takes the last ticket adds nsp partials by itself: beyond several dozen that serial tail
-            // outweighs the better streaming (measured at batch 1), and the register-staged kernel below is used
-            if (nsp <= 64) {
+            // up to 24 row ranges: the block that takes the last ticket of a strip adds them; more than that (one
+            // matrix of a few thousand columns) and that serial tail would dominate, so a second, wide kernel adds them
+            {
                 Workspace ws;
                 rc = get_workspace(st, &ws);
                 if (rc) return rc;
                 const dim3 grid(ts_strips, nsp, batch);
-                gemv_transpose_stream_kernel<<<grid, kStreamThreads, kTsRingBytes, st>>>(dim_out, dim_in, rps, nsp, w, x, y,
-                                                                                         reinterpret_cast<float *>(ws.scratch()), ws.tickets(),
-                                                                                         ws.status());
+                float *partial = reinterpret_cast<float *>(ws.scratch());
+                const bool two_kernels = nsp > 24;
+                gemv_transpose_stream_kernel<<<grid, kStreamThreads, kTsRingBytes, st>>>(dim_out, dim_in, rps, nsp, w, x, y, partial,
+                                                                                         two_kernels ? nullptr : ws.tickets(), ws.status());
                 CPMK_LAUNCH_CHECK();
+                if (two_kernels) {
+                    gemv_reduce_partials_kernel<<<dim3((dim_out + 31) / 32, batch), kBlock, 0, st>>>(dim_out, nsp, partial, y);
+                    CPMK_LAUNCH_CHECK();
+                }
                 return CPMK_OK;
             }
         }
