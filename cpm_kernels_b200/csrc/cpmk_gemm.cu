@@ -59,6 +59,7 @@ struct GemmParams {
     const __half *scale_c;        // (bcast_c ? 1 : batch, C)
     int32_t bcast_r, bcast_c;
     int32_t tma_store;            // the two-CTA kernel writes its output with TMA stores (needs 16-byte row pitch)
+    int32_t n_dst;                // number of destinations each output tile is stored to (1, or one per GPU when scattering)
     uint32_t *status;
 };
 
@@ -399,6 +400,12 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask
                  ::"r"(bar), "h"(cta_mask) : "memory");
 }
 
+// Up to eight destinations of the output (this GPU's buffer and, when the output is scattered, its peers').
+constexpr int kMaxDst = 8;
+struct OutMaps {
+    CUtensorMap m[kMaxDst];
+};
+
 // TMA store of a staged 32-row x 128-byte tile (128-byte swizzle) to the 3-d output map; out-of-range rows and
 // columns are clipped by the hardware.
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int32_t c0, int32_t c1, int32_t c2) {
@@ -420,7 +427,7 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 // warp alternate, so converting piece i+1 overlaps the store of piece i; the stores are full lines and need no
 // edge predicates.
 template <bool DEQUANT>
-__device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const CUtensorMap *tmap_o, uint32_t staging, uint32_t &buf,
+__device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const OutMaps *tmap_o, uint32_t staging, uint32_t &buf,
                                                   uint32_t tmem_base, uint32_t acc, int quarter, int lane, int b, int row_base, int col_base,
                                                   int half) {
     const int row = row_base + quarter * 32 + lane;
@@ -491,7 +498,8 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const C
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) {
-                tma_store_3d(tmap_o, tile, piece_col, row_base + quarter * 32, b);
+                // one store per destination, all reading the same staged tile (peers' buffers are reached over NVLink)
+                for (int d = 0; d < prm.n_dst; ++d) tma_store_3d(&tmap_o->m[d], tile, piece_col, row_base + quarter * 32, b);
                 bulk_commit();
             }
             buf ^= 1u;
@@ -505,7 +513,7 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const C
 template <bool DEQUANT, bool P_MN, bool Q_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads2, 1)
 gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
-                   const __grid_constant__ CUtensorMap tmap_o, const GemmParams prm) {
+                   const __grid_constant__ OutMaps tmap_o, const GemmParams prm) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t staging_base = tiles_base + kStages2 * kStageBytes2;       // 1024-byte aligned: swizzle atoms
@@ -779,7 +787,7 @@ thread_local MapCache g_map_cache;
 
 bool encode_operand_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int32_t box_rows);
 bool encode_operand_mn_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch);
-bool encode_output_raw(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int32_t batch, bool fp16);
+bool encode_output_raw(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int64_t ld, int32_t batch, bool fp16);
 
 template <typename F>
 bool cached_encode(CUtensorMap *map, const MapKey &key, F &&encode) {
@@ -798,8 +806,9 @@ bool encode_operand(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, 
 bool encode_operand_mn(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch) {
     return cached_encode(map, MapKey{ptr, rows, k, batch, 1}, [&] { return encode_operand_mn_raw(map, ptr, rows, k, batch); });
 }
-bool encode_output(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int32_t batch, bool fp16) {
-    return cached_encode(map, MapKey{ptr, R, C, batch, fp16 ? 2 : 3}, [&] { return encode_output_raw(map, ptr, R, C, batch, fp16); });
+bool encode_output(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int64_t ld, int32_t batch, bool fp16) {
+    if (ld != C) return encode_output_raw(map, ptr, R, C, ld, batch, fp16);       // pitched views are not cached
+    return cached_encode(map, MapKey{ptr, R, C, batch, fp16 ? 2 : 3}, [&] { return encode_output_raw(map, ptr, R, C, ld, batch, fp16); });
 }
 
 // int8 operand (batch, rows, k) with k contiguous, as a 3-d tensor map whose box is box_rows x 128 bytes.
@@ -830,13 +839,14 @@ bool encode_operand_mn_raw(CUtensorMap *map, const void *ptr, int32_t rows, int3
     return r == CUDA_SUCCESS;
 }
 
-// Output (batch, R, C) as a 3-d tensor map whose box is 32 rows x 128 bytes, 128-byte swizzle (for TMA stores).
-bool encode_output_raw(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int32_t batch, bool fp16) {
+// Output (batch, R, C) with a row pitch of `ld` elements, as a 3-d tensor map whose box is 32 rows x 128 bytes,
+// 128-byte swizzle (for TMA stores).
+bool encode_output_raw(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int64_t ld, int32_t batch, bool fp16) {
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) return false;
     const cuuint64_t esz = fp16 ? 2 : 4;
     const cuuint64_t dims[3] = {(cuuint64_t)C, (cuuint64_t)R, (cuuint64_t)batch};
-    const cuuint64_t strides[2] = {(cuuint64_t)C * esz, (cuuint64_t)R * (cuuint64_t)C * esz};
+    const cuuint64_t strides[2] = {(cuuint64_t)ld * esz, (cuuint64_t)R * (cuuint64_t)ld * esz};
     const cuuint32_t box[3] = {(cuuint32_t)(128 / esz), 32u, 1u};
     const cuuint32_t estr[3] = {1u, 1u, 1u};
     const CUresult r = enc(map, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_INT32, 3, ptr, dims, strides, box, estr,
@@ -911,7 +921,12 @@ int32_t prepare_tc_kernels(int device) {
 
 template <bool DEQUANT>
 int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int aT, int bT, const void *A, const void *B,
-                    const void *scale_x, const void *scale_y, int bx, int by, void *out, cudaStream_t stream) {
+                    const void *scale_x, const void *scale_y, int bx, int by, void *out, cudaStream_t stream, int n_dst = 1,
+                    void *const *dsts = nullptr, int64_t dst_ld = 0) {
+    // n_dst > 1 or dst_ld != m: the output tiles are scattered to several (possibly pitched) destinations; this is
+    // implemented by the TMA-store epilogue of the two-CTA kernel only
+    const bool scatter = dsts != nullptr;
+    if (!scatter) dst_ld = m;
     DeviceInfo info;
     int32_t rc = current_device_info(&info);
     if (rc) return rc;
@@ -922,9 +937,16 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
     const int32_t batch = batchA > batchB ? batchA : batchB;
     CPMK_REQUIRE(batch <= 65535, "batch %d exceeds 65535", batch);
     if (m == 0 || n == 0) return CPMK_OK;
-    CPMK_REQUIRE(out, "null output pointer");
+    CPMK_REQUIRE(out || scatter, "null output pointer");
+    if (scatter) {
+        CPMK_REQUIRE(n_dst >= 1 && n_dst <= kMaxDst, "number of destinations must be 1..%d (got %d)", kMaxDst, n_dst);
+        CPMK_REQUIRE(dst_ld >= m, "destination row pitch %lld is smaller than the row length %d", (long long)dst_ld, m);
+        for (int d = 0; d < n_dst; ++d) CPMK_REQUIRE(dsts[d] && aligned16(dsts[d]), "destination %d is null or not 16-byte aligned", d);
+        out = dsts[0];
+    }
     const size_t out_elem = DEQUANT ? sizeof(__half) : sizeof(int32_t);
     if (k == 0) {
+        CPMK_REQUIRE(!scatter, "k == 0 is not supported with scattered output");
         CPMK_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)batch * n * m * out_elem, stream));
         return CPMK_OK;
     }
@@ -964,7 +986,7 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
             if (margin_pairs > 0 && max_pairs - margin_pairs >= 8) max_pairs -= margin_pairs;
         }
         const bool any_mn = p_mn || q_mn;                   // MN-major operands are implemented in the two-CTA kernel only
-        if (variant != kVariantOneCta && max_pairs > 0 && (n > kBM || variant == kVariantTwoCta || any_mn)) {
+        if ((variant != kVariantOneCta || scatter) && max_pairs > 0 && (n > kBM || variant == kVariantTwoCta || any_mn || scatter)) {
             const int64_t tiles_r = (n + 2 * kBM - 1) / (2 * kBM), tiles_c = (m + kBN - 1) / kBN;
             const int64_t total = tiles_r * tiles_c * batch;
             // rows of the output come from B (n x k), columns from A (m x k); each CTA stages 128 rows of either
@@ -974,10 +996,16 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
                 prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.total_tiles = (int32_t)total;
                 const int pairs = (int)(total < max_pairs ? total : max_pairs);
                 const dim3 grid(2 * pairs);
-                CUtensorMap tmap_o;
-                prm.tma_store = ((int64_t)m * (DEQUANT ? 2 : 4)) % 16 == 0 && !getenv("CPMK_GEMM_NO_TMA_STORE") &&
-                                encode_output(&tmap_o, out, n, m, batch, DEQUANT);
-                if (!prm.tma_store) memset(&tmap_o, 0, sizeof(tmap_o));
+                OutMaps tmap_o;
+                memset(&tmap_o, 0, sizeof(tmap_o));
+                prm.n_dst = scatter ? n_dst : 1;
+                prm.tma_store = (dst_ld * (DEQUANT ? 2 : 4)) % 16 == 0 && (scatter || !getenv("CPMK_GEMM_NO_TMA_STORE"));
+                for (int d = 0; prm.tma_store && d < prm.n_dst; ++d)
+                    prm.tma_store = encode_output(&tmap_o.m[d], scatter ? dsts[d] : out, n, m, dst_ld, batch, DEQUANT);
+                if (scatter && !prm.tma_store) {
+                    set_error("scattered output needs a row pitch that is a multiple of 16 bytes and 16-byte aligned destinations");
+                    return CPMK_EINVAL;
+                }
                 if (!p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, false, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
                 else if (!p_mn && q_mn) gemm_i8_tc2_kernel<DEQUANT, false, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
                 else if (p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, true, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
@@ -987,6 +1015,10 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
                 g_last_variant = 2;
                 return CPMK_OK;
             }
+        }
+        if (scatter) {
+            set_error("scattered output is only available on the two-CTA tensor-core kernel (shape m=%d k=%d n=%d not eligible)", m, k, n);
+            return CPMK_EINVAL;
         }
         const int64_t tiles_r = (n + kBM - 1) / kBM, tiles_c = (m + kBN - 1) / kBN;
         const int64_t total_tiles = tiles_r * tiles_c * batch;
@@ -1001,6 +1033,7 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
             return CPMK_OK;
         }
     }
+    CPMK_REQUIRE(!scatter, "scattered output needs the tensor-core kernel: extents and pointers must be multiples of 16 bytes");
     const dim3 grid((m + kSimtTile - 1) / kSimtTile, (n + kSimtTile - 1) / kSimtTile, batch);
     CPMK_REQUIRE(grid.y <= 65535, "n = %d is too large for the generic kernel", n);
     gemm_i8_simt_kernel<DEQUANT><<<grid, 256, 0, stream>>>(m, k, n, batchA, batchB, aT, bT, static_cast<const int8_t *>(A),
@@ -1029,6 +1062,17 @@ int32_t cpmk_gemm_int8_dequant(int32_t m, int32_t k, int32_t n, int32_t batchA, 
                                cpmk_stream_t stream) {
     return launch_gemm<true>(m, k, n, batchA, batchB, aT != 0, bT != 0, A, B, scale_x, scale_y, broad_cast_x != 0, broad_cast_y != 0, out,
                              as_stream(stream));
+}
+
+int32_t cpmk_gemm_int8_dequant_scatter(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT, const void *A,
+                                       const void *B, const void *scale_x, const void *scale_y, int32_t broad_cast_x, int32_t broad_cast_y,
+                                       int32_t n_dst, void *const *dst, int64_t dst_row_pitch, cpmk_stream_t stream) {
+    if (!dst) {
+        set_error("dst is null");
+        return CPMK_EINVAL;
+    }
+    return launch_gemm<true>(m, k, n, batchA, batchB, aT != 0, bT != 0, A, B, scale_x, scale_y, broad_cast_x != 0, broad_cast_y != 0, nullptr,
+                             as_stream(stream), n_dst, dst, dst_row_pitch);
 }
 
 int32_t cpmk_last_gemm_path(void) { return g_last_path; }

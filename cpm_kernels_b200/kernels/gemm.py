@@ -142,3 +142,22 @@ def gemm_int8_scale(m: int, k: int, n: int,
     assert batchA == batchB or batchA == 1 or batchB == 1
     cpmk.call("cpmk_gemm_int8_dequant", m, k, n, batchA, batchB, int(bool(aT)), int(bool(bT)), A, B, scale_x, scale_y,
               int(bool(broad_cast_x)), int(bool(broad_cast_y)), out, stream_arg(stream))
+
+
+def gemm_int8_scale_scatter(m: int, k: int, n: int,
+                            batchA: int, batchB: int,
+                            aT: bool, bT: bool,
+                            A: DevicePointer, B: DevicePointer,
+                            scale_x: DevicePointer, scale_y: DevicePointer,
+                            broad_cast_x: bool, broad_cast_y: bool,
+                            dst: list,               # device addresses of element (0, 0, 0) of each destination
+                            dst_row_pitch: int,      # elements between rows of a destination (>= m)
+                            stream: CUDAStream):
+    """gemm_int8_scale whose result goes to several pitched destinations (this GPU's and its peers' output buffers):
+    the output all-gather of a column-parallel linear, done by the GEMM's epilogue.  No counterpart in the reference."""
+    import ctypes
+    assert m % 4 == 0 and n % 4 == 0 and k % 4 == 0
+    assert batchA == batchB or batchA == 1 or batchB == 1
+    arr = (ctypes.c_void_p * len(dst))(*dst)
+    cpmk.call("cpmk_gemm_int8_dequant_scatter", m, k, n, batchA, batchB, int(bool(aT)), int(bool(bT)), A, B, scale_x, scale_y,
+              int(bool(broad_cast_x)), int(bool(broad_cast_y)), len(dst), arr, dst_row_pitch, stream_arg(stream))

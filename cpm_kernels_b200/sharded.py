@@ -71,3 +71,53 @@ class ColumnParallelInt8Linear:
         return self.to_token_major(self.gather(self.local(x)))
 
     __call__ = forward
+
+
+class FusedColumnParallelInt8Linear:
+    """The same layer with the all-gather done by the GEMM: every rank's epilogue stores its N/g output columns straight
+    into columns [r*N/g, (r+1)*N/g) of every rank's full-width, token-major y (TMA stores over NVLink into peer-mapped
+    symmetric memory), so there is no gather kernel, no second read of the slice and no re-layout pass.
+
+    ``y`` lives in symmetric memory owned by the layer (one buffer per token count, reused call after call): the caller
+    must be done reading the previous result on every rank before calling again, or pass ``sync_before=True``.
+    CUDA only (there is no host form of peer-mapped stores); NCCL process group for the rendezvous.
+    """
+
+    def __init__(self, weight_shard: torch.Tensor, group: Optional[dist.ProcessGroup] = None):
+        assert weight_shard.ndim == 3 and weight_shard.size(0) == 1 and weight_shard.is_contiguous() and weight_shard.is_cuda
+        self.weight = weight_shard
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self._buffers = {}
+
+    def _buffer(self, m_tokens: int):
+        import torch.distributed._symmetric_memory as symm_mem
+        if m_tokens not in self._buffers:
+            n_total = self.weight.size(1) * self.world
+            y = symm_mem.empty((1, m_tokens, n_total), dtype=torch.half, device=self.weight.device)
+            handle = symm_mem.rendezvous(y, self.group)
+            self._buffers[m_tokens] = (y, handle)
+        return self._buffers[m_tokens]
+
+    def forward(self, x: torch.Tensor, sync_before: bool = False) -> torch.Tensor:
+        from .torch.gemm import quantize
+        from .kernels import gemm_int8_scale_scatter
+        assert x.ndim == 3 and x.size(0) == 1 and x.is_contiguous() and x.is_cuda
+        m_tokens, k = x.size(1), x.size(2)
+        n_local = self.weight.size(1)
+        n_total = n_local * self.world
+        y, handle = self._buffer(m_tokens)
+        scale_x, q_x = quantize(x, False)
+        scale_w, q_w = quantize(self.weight, False)
+        if sync_before:
+            handle.barrier(channel=0)
+        dst = [int(handle.buffer_ptrs[p]) + 2 * self.rank * n_local for p in range(self.world)]
+        with torch.cuda.device(x.device):
+            # kernel-level (m, k, n) = (N_local, K, M): A = weights, B = activations, out rows = tokens
+            gemm_int8_scale_scatter(n_local, k, m_tokens, 1, 1, True, False, q_w.data_ptr(), q_x.data_ptr(), scale_x.data_ptr(),
+                                    scale_w.data_ptr(), True, True, dst, n_total, torch.cuda.current_stream().cuda_stream)
+        handle.barrier(channel=1)          # every rank's stores have landed before anyone reads y
+        return y
+
+    __call__ = forward

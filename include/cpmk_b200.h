@@ -109,6 +109,20 @@ int32_t cpmk_gemm_int8_dequant(int32_t m, int32_t k, int32_t n, int32_t batchA, 
                                const void *A, const void *B, const void *scale_x, const void *scale_y,
                                int32_t broad_cast_x, int32_t broad_cast_y, void *out, cpmk_stream_t stream);
 
+/* cpmk_gemm_int8_dequant whose fp16 result is stored to `n_dst` (1..8) destinations instead of one: dst[i] is the
+ * address of element (0, 0, 0) of destination i, every destination has rows `dst_row_pitch` elements apart (>= m,
+ * a multiple of 8) and batches n * dst_row_pitch apart.  With one process per GPU and the peers' output buffers mapped
+ * into this process (CUDA peer access / symmetric memory), rank r of g computes its N/g columns of y = x W^T and this
+ * call writes them straight into columns [r*N/g, (r+1)*N/g) of every rank's full-width y: the all-gather that
+ * cpm_kernels' callers would run after a column-parallel linear happens inside the GEMM's epilogue (TMA stores over
+ * NVLink), without a second pass over the slice.  No counterpart in the reference (it has no multi-GPU code).
+ * Needs the tensor-core kernel (extents and pointers multiples of 16 bytes); otherwise CPMK_EINVAL.
+ * The caller synchronises the ranks (all stores of a call are complete when the call's kernel has finished). */
+int32_t cpmk_gemm_int8_dequant_scatter(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT,
+                                       const void *A, const void *B, const void *scale_x, const void *scale_y,
+                                       int32_t broad_cast_x, int32_t broad_cast_y, int32_t n_dst, void *const *dst,
+                                       int64_t dst_row_pitch, cpmk_stream_t stream);
+
 /* Which GEMM kernel the last cpmk_gemm_int8* call on this thread selected:
  * 1 = tcgen05 tensor-core kernel, 2 = generic SIMT kernel.  For tests and the benchmark. */
 int32_t cpmk_last_gemm_path(void);

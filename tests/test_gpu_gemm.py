@@ -183,3 +183,30 @@ def test_argument_errors(G):
     out = torch.full((1, 4, 4), 5, dtype=torch.int32, device="cuda")
     ck.gemm_int8(4, 0, 4, 1, 1, True, False, A.data_ptr(), A.data_ptr(), out.data_ptr(), G.stream())
     assert int(out.abs().max()) == 0
+
+
+@pytest.mark.parametrize("m,k,n,batch", [(512, 256, 384, 1), (1536, 1024, 1000, 1), (256, 128, 300, 3)])
+def test_scattered_output_to_pitched_destinations(G, m, k, n, batch):
+    """cpmk_gemm_int8_dequant_scatter on one GPU: two destinations, each a column slice of a wider buffer (the layout a
+    column-parallel rank writes into every rank's full-width output).  Slices equal the plain call; nothing else is touched."""
+    import cpm_kernels_b200.kernels as ck
+    A, B = operands(m, k, n, batch, batch, True, False, seed=m + n)
+    sx = randn_fp16((batch, n), 7, 0.01).abs()
+    sy = randn_fp16((batch, m), 8, 0.001).abs()
+    Ad, Bd, sxd, syd = A.cuda(), B.cuda(), sx.cuda(), sy.cuda()
+    plain = G.gemm_int8_scale(m, k, n, True, False, Ad, Bd, sxd, syd, False, False)
+    pitch = 3 * m
+    bufs = [torch.full((batch, n, pitch), -7.0, dtype=torch.half, device="cuda") for _ in range(2)]
+    offs = [0, 2 * m]
+    dst = [b.data_ptr() + 2 * o for b, o in zip(bufs, offs)]
+    ck.gemm_int8_scale_scatter(m, k, n, batch, batch, True, False, Ad.data_ptr(), Bd.data_ptr(), sxd.data_ptr(), syd.data_ptr(), False, False,
+                               dst, pitch, G.stream())
+    torch.cuda.synchronize()
+    for b, o in zip(bufs, offs):
+        assert torch.equal(b[:, :, o:o + m].view(torch.int16), plain.view(torch.int16))
+        rest = torch.cat([b[:, :, :o], b[:, :, o + m:]], dim=2)
+        assert bool((rest == -7.0).all())
+    G.assert_no_device_error()
+    with pytest.raises(RuntimeError, match="pitch"):
+        ck.gemm_int8_scale_scatter(m, k, n, batch, batch, True, False, Ad.data_ptr(), Bd.data_ptr(), sxd.data_ptr(), syd.data_ptr(), False, False,
+                                   dst, m - 8, G.stream())
