@@ -183,8 +183,6 @@ def run_ours(args) -> None:
     saved_stdout = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # the collective's kernels run beside the persistent GEMM grid: leave them a few SMs
-        os.environ.setdefault("CPMK_GEMM_SM_MARGIN", "16")
         # libraries print banners on stdout when a communicator is created: keep stdout for the one JSON line
         sys.stdout.flush()
         saved_stdout = os.dup(1)
@@ -223,6 +221,9 @@ def run_ours(args) -> None:
             except Exception as e:                       # noqa: BLE001
                 sys.stderr.write("fused exchange unavailable (%s); using the NCCL all-gather\n" % (e,))
                 fused_layers = None
+        if fused_layers is None:
+            # the collective's kernels run beside the persistent GEMM grid: leave them a few SMs
+            os.environ.setdefault("CPMK_GEMM_SM_MARGIN", "16")
 
     gemm_events = []
 
