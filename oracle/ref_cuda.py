@@ -61,15 +61,20 @@ class _Driver:
 class ReferenceKernels:
     """The reference's quantisation / GEMV kernels, compiled from its sources, on the current device."""
 
-    def __init__(self):
-        if not available():
-            raise RuntimeError("oracle/_ref/*.fatbin not built (run `make -C oracle ref` where the reference checkout is)")
+    def __init__(self, fatbin_dir: str = None):
+        """``fatbin_dir``: where ``gemm.fatbin`` / ``gemv.fatbin`` are read from.  Default: the reference's own
+        device code in ``oracle/_ref``.  Tests also point it at this package's kernel modules, which export the
+        same symbols, to run them under the reference's launch shapes."""
+        if fatbin_dir is None:
+            if not available():
+                raise RuntimeError("oracle/_ref/*.fatbin not built (run `make -C oracle ref` where the reference checkout is)")
+            fatbin_dir = REF_DIR
         torch.cuda.init()
         torch.zeros(1, device="cuda")       # make the primary context current
         self.drv = _Driver()
         self._fns = {}
         for name in ("gemm", "gemv"):
-            with open(os.path.join(REF_DIR, name + ".fatbin"), "rb") as f:
+            with open(os.path.join(fatbin_dir, name + ".fatbin"), "rb") as f:
                 setattr(self, "_mod_" + name, self.drv.load(f.read()))
 
     def _fn(self, mod, name):
@@ -149,7 +154,40 @@ class ReferenceKernels:
                         [self._i(b), self._i(n), self._i(m), self._p(mat), self._p(scale_x), self._p(out), self._p(scale_y), ctypes.c_bool(bx)])
         return out, scale_y
 
+    def gemm_scale_x(self, mat: torch.Tensor, scale_x: torch.Tensor) -> torch.Tensor:
+        """kernels/gemm.py:309-326: grid (batch, n), block min(m, 1024)."""
+        b, n, m = mat.shape
+        out = torch.empty((b, n, m), dtype=torch.half, device=mat.device)
+        self.drv.launch(self._fn("gemm", "cu_gemm_scale_x"), (b, n, 1), (min(m, 1024), 1, 1), self._stream(),
+                        [self._i(b), self._i(n), self._i(m), self._p(mat), self._p(scale_x), self._p(out)])
+        return out
+
+    def gemm_scale_y(self, mat: torch.Tensor, scale_y: torch.Tensor) -> torch.Tensor:
+        """kernels/gemm.py:329-347: grid (batch, n), block min(m, 1024)."""
+        b, n, m = mat.shape
+        out = torch.empty((b, n, m), dtype=torch.half, device=mat.device)
+        self.drv.launch(self._fn("gemm", "cu_gemm_scale_y"), (b, n, 1), (min(m, 1024), 1, 1), self._stream(),
+                        [self._i(b), self._i(n), self._i(m), self._p(mat), self._p(scale_y), self._p(out)])
+        return out
+
     # ---- cpm_kernels/kernels/gemv.py -------------------------------------------------------------
+    def gemv_calc_scale(self, vec: torch.Tensor) -> torch.Tensor:
+        """kernels/gemv.py:18-35: grid (batch,), block min(1024, round_up(n, 32))."""
+        b, n = vec.shape
+        out = torch.empty((b,), dtype=torch.half, device=vec.device)
+        self.drv.launch(self._fn("gemv", "cu_gemv_calc_scale"), (b, 1, 1), (min(1024, _round_up(n, 32)), 1, 1), self._stream(),
+                        [self._i(b), self._i(n), self._p(vec), self._p(out)])
+        return out
+
+    def gemv_round(self, vec: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+        """kernels/gemv.py:37-54: threads = min(1024, round_up(n, 32)); grid (batch, round_up(n, threads) / threads)."""
+        b, n = vec.shape
+        out = torch.empty((b, n), dtype=torch.int8, device=vec.device)
+        threads = min(1024, _round_up(n, 32))
+        self.drv.launch(self._fn("gemv", "cu_gemv_round"), (b, _round_up(n, threads) // threads, 1), (threads, 1, 1), self._stream(),
+                        [self._i(b), self._i(n), self._p(vec), self._p(scale), self._p(out)])
+        return out
+
     def gemv_fp16_light(self, mat: torch.Tensor, vec: torch.Tensor) -> torch.Tensor:
         """kernels/gemv.py:129-148: grid (batch, dim_out), block min(1024, round_up(dim_in / 2, 32))."""
         b, o, i = mat.shape

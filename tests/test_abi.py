@@ -79,3 +79,23 @@ def test_kernel_level_preconditions_are_the_references(built_library):
         ck.gemm_int8(8, 8, 8, 2, 3, True, False, 0, 0, 0, 0)
     with pytest.raises(AssertionError):
         ck.gemv_broadcast_mat_int8(1, 8, 6, 0, 0, 0, 0, 0, 0)
+
+
+def test_kernel_modules_are_built_and_export_the_reference_symbols():
+    """lib/gemm.fatbin and lib/gemv.fatbin exist after a build, and their sources define every kernel name the
+    reference's loader looks up (cpm_kernels/kernels/gemm.py:6-19, kernels/gemv.py:6-16)."""
+    import os
+    import re
+    from cpm_kernels_b200 import build
+    build.build_library()
+    names = {
+        "gemm": ["cu_gemm_round", "cu_gemm_round_transpose", "cu_gemm_scale", "cu_gemm_calc_scale", "cu_gemm_calc_scale_transpose",
+                 "cu_gemm_backward_round_scale", "cu_gemm_backward_scale_round", "cu_gemm_scale_x", "cu_gemm_scale_y"],
+        "gemv": ["cu_gemv_calc_scale", "cu_gemv_round", "cu_gemv_broadcast_mat_int8", "cu_gemv_fp16", "cu_gemv_fp16_transpose",
+                 "cu_gemv_broadcast_mat_fp16"],
+    }
+    for mod, kernels in names.items():
+        assert os.path.getsize(build.module_path(mod)) > 0
+        src = open(os.path.join(build.CSRC, "modules", build.MODULES[mod])).read()
+        for k in kernels:
+            assert re.search(r'extern "C" __global__ void %s\(' % k, src), k
