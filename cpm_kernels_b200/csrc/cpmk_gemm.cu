@@ -394,6 +394,20 @@ __device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t a_desc, u
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// the same for fp16 operands with an fp32 accumulator (k = 16 per instruction)
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Instruction descriptor of kind::f16: fp32 accumulator (bits 4-5 = 1), fp16 A and B (bits 7-9 = 0, 10-12 = 0).
+constexpr uint32_t kInstrDescF16 = (1u << 4) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)((2 * kBM) >> 4) << 24);
+constexpr int kBKf16 = kBK / 2;                        // fp16 elements of k per stage (one 128-byte swizzle row)
+constexpr int kMnBlockF16 = 64 * kBKf16 * 2;           // an MN-major fp16 tile is two blocks of 64 rows x kBKf16 k-rows: 8 KiB each
+
 // arrives on the barrier at offset `bar` in every CTA of `cta_mask` once the MMAs issued so far have completed
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
@@ -426,15 +440,15 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 // conflicts, and what the store's 128-byte swizzle expects), and lane 0 issues the store.  Two staging tiles per
 // warp alternate, so converting piece i+1 overlaps the store of piece i; the stores are full lines and need no
 // edge predicates.
-template <bool DEQUANT>
+template <bool DEQUANT, bool F16 = false>
 __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const OutMaps *tmap_o, uint32_t staging, uint32_t &buf,
                                                   uint32_t tmem_base, uint32_t acc, int quarter, int lane, int b, int row_base, int col_base,
                                                   int half) {
     const int row = row_base + quarter * 32 + lane;
     const bool row_ok = row < prm.R;
     float sr = 0.f;
-    if (DEQUANT && row_ok) sr = __half2float(__ldg(prm.scale_r + (prm.bcast_r ? 0 : (int64_t)b * prm.R) + row));
-    const __half *sc = DEQUANT ? prm.scale_c + (prm.bcast_c ? 0 : (int64_t)b * prm.C) : nullptr;
+    if (DEQUANT && !F16 && row_ok) sr = __half2float(__ldg(prm.scale_r + (prm.bcast_r ? 0 : (int64_t)b * prm.R) + row));
+    const __half *sc = (DEQUANT && !F16) ? prm.scale_c + (prm.bcast_c ? 0 : (int64_t)b * prm.C) : nullptr;
     const int warp_col = col_base + half * (kBN / 2);                // this warp's 128 columns
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN + half * (kBN / 2);
     const uint32_t sw = (uint32_t)(lane & 7);
@@ -447,7 +461,7 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const O
     uint4 cs[2][4];
     auto request = [&](int st, int slot) {
         tmem_ld_32x32b_x32(taddr + st * 32, v[slot]);
-        if (DEQUANT) {
+        if (DEQUANT && !F16) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
                 const int c = warp_col + st * 32 + g * 8;
@@ -474,7 +488,18 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const O
             if (lane == 0) bulk_wait_read<1>();
             __syncwarp();
         }
-        if (DEQUANT) {
+        if (F16) {
+            // fp32 accumulators of the fp16 GEMM: one rounding to fp16, no scales
+            const uint32_t chunk0 = (uint32_t)(st % kStepsPerPiece) * 4u;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    o[e] = pack_half2(__uint_as_float(v[slot][g * 8 + 2 * e]), __uint_as_float(v[slot][g * 8 + 2 * e + 1]));
+                st_shared_v4(my_row + (((chunk0 + (uint32_t)g) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+            }
+        } else if (DEQUANT) {
             const uint32_t chunk0 = (uint32_t)(st % kStepsPerPiece) * 4u;      // 16-byte chunks 0-3 or 4-7 of the 128-byte row
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
@@ -510,10 +535,10 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const O
 // P_MN / Q_MN: the row / column operand is stored with its rows contiguous (k is the slow axis) instead of k:
 // the reference's bT / !aT layouts.  Their tensor maps then have (rows, k, batch) extents and 128 x kBK boxes, the
 // shared-memory tiles are MN-major, and bits 15 / 16 of the instruction descriptor say so.
-template <bool DEQUANT, bool P_MN, bool Q_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads2, 1)
-gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
-                   const __grid_constant__ OutMaps tmap_o, const GemmParams prm) {
+// F16: fp16 operands (kBKf16 elements of k per stage, kind::f16, fp32 accumulators) and an fp16 result with no
+// scales; everything else -- stage bytes, barriers, tile walk, epilogue staging -- is the int8 pipeline's.
+template <bool DEQUANT, bool P_MN, bool Q_MN, bool F16>
+__device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CUtensorMap &tmap_q, const OutMaps &tmap_o, const GemmParams &prm) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t staging_base = tiles_base + kStages2 * kStageBytes2;       // 1024-byte aligned: swizzle atoms
@@ -568,10 +593,18 @@ gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     const uint32_t p_dst = tiles_base + stage * kStageBytes2;
                     if (leader) mbar_expect_tx(full_bar + 8 * stage, 2 * kStageBytes2);
                     const uint32_t leader_full = map_to_cta(full_bar + 8 * stage, 0);
-                    if (P_MN) tma_load_3d_pair(p_dst, &tmap_p, row0, kb * kBK, prm.p_batched ? b : 0, leader_full);
-                    else tma_load_3d_pair(p_dst, &tmap_p, kb * kBK, row0, prm.p_batched ? b : 0, leader_full);
-                    if (Q_MN) tma_load_3d_pair(p_dst + kPBytes, &tmap_q, col0, kb * kBK, prm.q_batched ? b : 0, leader_full);
-                    else tma_load_3d_pair(p_dst + kPBytes, &tmap_q, kb * kBK, col0, prm.q_batched ? b : 0, leader_full);
+                    constexpr int kKe = F16 ? kBKf16 : kBK;          // k elements per stage
+                    if (P_MN && F16) {
+                        // two boxes of 64 rows x 64 k-rows (a 16-bit swizzle row holds 64 elements)
+                        tma_load_3d_pair(p_dst, &tmap_p, row0, kb * kKe, prm.p_batched ? b : 0, leader_full);
+                        tma_load_3d_pair(p_dst + kMnBlockF16, &tmap_p, row0 + 64, kb * kKe, prm.p_batched ? b : 0, leader_full);
+                    } else if (P_MN) tma_load_3d_pair(p_dst, &tmap_p, row0, kb * kKe, prm.p_batched ? b : 0, leader_full);
+                    else tma_load_3d_pair(p_dst, &tmap_p, kb * kKe, row0, prm.p_batched ? b : 0, leader_full);
+                    if (Q_MN && F16) {
+                        tma_load_3d_pair(p_dst + kPBytes, &tmap_q, col0, kb * kKe, prm.q_batched ? b : 0, leader_full);
+                        tma_load_3d_pair(p_dst + kPBytes + kMnBlockF16, &tmap_q, col0 + 64, kb * kKe, prm.q_batched ? b : 0, leader_full);
+                    } else if (Q_MN) tma_load_3d_pair(p_dst + kPBytes, &tmap_q, col0, kb * kKe, prm.q_batched ? b : 0, leader_full);
+                    else tma_load_3d_pair(p_dst + kPBytes, &tmap_q, kb * kKe, col0, prm.q_batched ? b : 0, leader_full);
                     if (++stage == kStages2) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -591,13 +624,18 @@ gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     const uint32_t p_src = tiles_base + stage * kStageBytes2;
                     // k advances by 32 per MMA: 32 bytes inside the swizzle row of a k-major tile (+2 in the
                     // address field), 32 rows of 128 bytes in an MN-major tile (+256)
-                    const uint64_t p_desc = P_MN ? make_mnmajor_sw128_desc(p_src, kPBytes) : make_kmajor_sw128_desc(p_src);
-                    const uint64_t q_desc = Q_MN ? make_mnmajor_sw128_desc(p_src + kPBytes, kQBytes2) : make_kmajor_sw128_desc(p_src + kPBytes);
-                    constexpr uint32_t idesc = kInstrDesc2 | (P_MN ? (1u << 15) : 0u) | (Q_MN ? (1u << 16) : 0u);
+                    // (fp16: k advances by 16 per MMA -- still 32 bytes of a k-major row, 16 rows = +128 MN-major)
+                    const uint64_t p_desc = P_MN ? make_mnmajor_sw128_desc(p_src, F16 ? kMnBlockF16 : kPBytes) : make_kmajor_sw128_desc(p_src);
+                    const uint64_t q_desc = Q_MN ? make_mnmajor_sw128_desc(p_src + kPBytes, F16 ? kMnBlockF16 : kQBytes2)
+                                                 : make_kmajor_sw128_desc(p_src + kPBytes);
+                    constexpr uint32_t idesc = (F16 ? kInstrDescF16 : kInstrDesc2) | (P_MN ? (1u << 15) : 0u) | (Q_MN ? (1u << 16) : 0u);
+                    constexpr int kMnStep = F16 ? 128 : 256;
 #pragma unroll
-                    for (int j = 0; j < kBK / kUmmaK; ++j)
-                        umma_i8_pair(d_tmem, p_desc + (uint64_t)((P_MN ? 256 : 2) * j), q_desc + (uint64_t)((Q_MN ? 256 : 2) * j), idesc,
-                                     (kb | j) != 0 ? 1u : 0u);
+                    for (int j = 0; j < kBK / kUmmaK; ++j) {
+                        const uint64_t pd = p_desc + (uint64_t)((P_MN ? kMnStep : 2) * j), qd = q_desc + (uint64_t)((Q_MN ? kMnStep : 2) * j);
+                        if (F16) umma_f16_pair(d_tmem, pd, qd, idesc, (kb | j) != 0 ? 1u : 0u);
+                        else umma_i8_pair(d_tmem, pd, qd, idesc, (kb | j) != 0 ? 1u : 0u);
+                    }
                     umma_commit_pair(empty_bar + 8 * stage, 3);
                     if (++stage == kStages2) { stage = 0; phase ^= 1u; }
                 }
@@ -618,8 +656,8 @@ gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, prm.status, kErrEpilogueWait)) break;
             tcgen05_fence_after();
             const int half = (warp - 2) >> 2;            // which 128 of the tile's 256 columns this warp writes
-            if (prm.tma_store)
-                epilogue_rows_tma<DEQUANT>(prm, &tmap_o, staging_base + (uint32_t)(warp - 2) * 2u * kOutStageBytes, out_buf, tmem_base, acc, quarter,
+            if (F16 || prm.tma_store)                    // (the fp16 GEMM is only launched with TMA stores)
+                epilogue_rows_tma<DEQUANT, F16>(prm, &tmap_o, staging_base + (uint32_t)(warp - 2) * 2u * kOutStageBytes, out_buf, tmem_base, acc, quarter,
                                            lane, b, r_blk * (2 * kBM) + (int)rank * kBM, c_blk * kBN, half);
             else
                 epilogue_rows<DEQUANT>(prm, tmem_base, acc, quarter, lane, b, r_blk * (2 * kBM) + (int)rank * kBM, c_blk * kBN, half * 4, half * 4 + 4);
@@ -644,6 +682,21 @@ gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         tcgen05_fence_after();
         tmem_dealloc_pair(tmem_base, kTmemCols);
     }
+}
+
+template <bool DEQUANT, bool P_MN, bool Q_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads2, 1)
+gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
+                   const __grid_constant__ OutMaps tmap_o, const GemmParams prm) {
+    tc2_pipeline<DEQUANT, P_MN, Q_MN, false>(tmap_p, tmap_q, tmap_o, prm);
+}
+
+// fp16 x fp16 -> fp16 with fp32 accumulation on the same pipeline (the reference's gemm_fp16, kernels/gemm.py:188-256)
+template <bool P_MN, bool Q_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads2, 1)
+gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
+                    const __grid_constant__ OutMaps tmap_o, const GemmParams prm) {
+    tc2_pipeline<true, P_MN, Q_MN, true>(tmap_p, tmap_q, tmap_o, prm);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -785,8 +838,8 @@ struct MapCache {
 };
 thread_local MapCache g_map_cache;
 
-bool encode_operand_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int32_t box_rows);
-bool encode_operand_mn_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch);
+bool encode_operand_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int32_t box_rows, int esz);
+bool encode_operand_mn_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int esz);
 bool encode_output_raw(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int64_t ld, int32_t batch, bool fp16);
 
 template <typename F>
@@ -800,40 +853,43 @@ bool cached_encode(CUtensorMap *map, const MapKey &key, F &&encode) {
     return true;
 }
 
-bool encode_operand(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int32_t box_rows) {
-    return cached_encode(map, MapKey{ptr, rows, k, batch, 0x100 + box_rows}, [&] { return encode_operand_raw(map, ptr, rows, k, batch, box_rows); });
+// esz: bytes per operand element (1: int8, 2: fp16)
+bool encode_operand(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int32_t box_rows, int esz = 1) {
+    return cached_encode(map, MapKey{ptr, rows, k, batch, 0x100 + box_rows + 0x1000 * esz},
+                         [&] { return encode_operand_raw(map, ptr, rows, k, batch, box_rows, esz); });
 }
-bool encode_operand_mn(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch) {
-    return cached_encode(map, MapKey{ptr, rows, k, batch, 1}, [&] { return encode_operand_mn_raw(map, ptr, rows, k, batch); });
+bool encode_operand_mn(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int esz = 1) {
+    return cached_encode(map, MapKey{ptr, rows, k, batch, 1 + 0x1000 * esz}, [&] { return encode_operand_mn_raw(map, ptr, rows, k, batch, esz); });
 }
 bool encode_output(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int64_t ld, int32_t batch, bool fp16) {
     if (ld != C) return encode_output_raw(map, ptr, R, C, ld, batch, fp16);       // pitched views are not cached
     return cached_encode(map, MapKey{ptr, R, C, batch, fp16 ? 2 : 3}, [&] { return encode_output_raw(map, ptr, R, C, ld, batch, fp16); });
 }
 
-// int8 operand (batch, rows, k) with k contiguous, as a 3-d tensor map whose box is box_rows x 128 bytes.
-bool encode_operand_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int32_t box_rows) {
+// Operand (batch, rows, k) with k contiguous, as a 3-d tensor map whose box is box_rows x 128 bytes.
+bool encode_operand_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int32_t box_rows, int esz) {
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) return false;
     const cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)batch};
-    const cuuint64_t strides[2] = {(cuuint64_t)k, (cuuint64_t)rows * (cuuint64_t)k};
-    const cuuint32_t box[3] = {(cuuint32_t)kBK, (cuuint32_t)box_rows, 1u};
+    const cuuint64_t strides[2] = {(cuuint64_t)k * esz, (cuuint64_t)rows * (cuuint64_t)k * esz};
+    const cuuint32_t box[3] = {(cuuint32_t)(kBK / esz), (cuuint32_t)box_rows, 1u};
     const cuuint32_t estr[3] = {1u, 1u, 1u};
-    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+    const CUresult r = enc(map, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(ptr), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 
-// int8 operand stored (batch, k, rows) with the rows contiguous, as a 3-d tensor map whose box is 128 rows x kBK of k.
-bool encode_operand_mn_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch) {
+// Operand stored (batch, k, rows) with the rows contiguous, as a 3-d tensor map whose box is one 128-byte swizzle row
+// of rows (128 int8 / 64 fp16) by one stage of k (128 int8 / 64 fp16).
+bool encode_operand_mn_raw(CUtensorMap *map, const void *ptr, int32_t rows, int32_t k, int32_t batch, int esz) {
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) return false;
     const cuuint64_t dims[3] = {(cuuint64_t)rows, (cuuint64_t)k, (cuuint64_t)batch};
-    const cuuint64_t strides[2] = {(cuuint64_t)rows, (cuuint64_t)rows * (cuuint64_t)k};
-    const cuuint32_t box[3] = {128u, (cuuint32_t)kBK, 1u};
+    const cuuint64_t strides[2] = {(cuuint64_t)rows * esz, (cuuint64_t)rows * (cuuint64_t)k * esz};
+    const cuuint32_t box[3] = {(cuuint32_t)(128 / esz), (cuuint32_t)(kBK / esz), 1u};
     const cuuint32_t estr[3] = {1u, 1u, 1u};
-    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+    const CUresult r = enc(map, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(ptr), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
@@ -888,6 +944,10 @@ int32_t prepare_tc_kernels(int device) {
         CPMK_SET_TC2(false, false, false); CPMK_SET_TC2(false, false, true); CPMK_SET_TC2(false, true, false); CPMK_SET_TC2(false, true, true);
         CPMK_SET_TC2(true, false, false); CPMK_SET_TC2(true, false, true); CPMK_SET_TC2(true, true, false); CPMK_SET_TC2(true, true, true);
 #undef CPMK_SET_TC2
+#define CPMK_SET_F16(P, Q) \
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_f16_tc2_kernel<P, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTc2SmemBytes)
+        CPMK_SET_F16(false, false); CPMK_SET_F16(false, true); CPMK_SET_F16(true, false); CPMK_SET_F16(true, true);
+#undef CPMK_SET_F16
         g_prepare_err[dev] = e;
         if (e != cudaSuccess) return;
         cudaLaunchConfig_t cfg = {};
@@ -1045,6 +1105,133 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
     return CPMK_OK;
 }
 
+// ------------------------------------------------------------------------------------------------
+// fp16 GEMM (the int8=False branch of bmm).  Generic kernel for shapes the tensor-core path does not take:
+// 64 x 64 output tile per 256-thread block, 4 x 4 outputs per thread, k in chunks of 16, fp32 accumulation.
+// ------------------------------------------------------------------------------------------------
+constexpr int kF16SimtK = 16;
+
+__global__ void __launch_bounds__(256) gemm_f16_simt_kernel(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int aT, int bT,
+                                                            const __half *__restrict__ A, const __half *__restrict__ B, __half *__restrict__ out) {
+    __shared__ float sa[kF16SimtK][kSimtTile + 1];    // [l][i]: columns of the output (from A)
+    __shared__ float sb[kF16SimtK][kSimtTile + 1];    // [l][j]: rows of the output (from B)
+    const int b = blockIdx.z;
+    const int i0 = blockIdx.x * kSimtTile, j0 = blockIdx.y * kSimtTile;
+    const __half *Ab = A + (batchA > 1 ? (int64_t)b * m * k : 0);
+    const __half *Bb = B + (batchB > 1 ? (int64_t)b * n * k : 0);
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4] = {};
+    for (int l0 = 0; l0 < k; l0 += kF16SimtK) {
+        for (int e = threadIdx.x; e < kF16SimtK * kSimtTile; e += 256) {
+            // A is (k, m) row-major, or (m, k) if aT: walk the contiguous axis with the fastest thread index
+            const int l = aT ? e % kF16SimtK : e / kSimtTile, i = aT ? e / kF16SimtK : e % kSimtTile;
+            const int gl = l0 + l, gi = i0 + i;
+            sa[l][i] = (gl < k && gi < m) ? __half2float(aT ? Ab[(int64_t)gi * k + gl] : Ab[(int64_t)gl * m + gi]) : 0.f;
+            // B is (n, k) row-major, or (k, n) if bT
+            const int lb = bT ? e / kSimtTile : e % kF16SimtK, j = bT ? e % kSimtTile : e / kF16SimtK;
+            const int glb = l0 + lb, gj = j0 + j;
+            sb[lb][j] = (glb < k && gj < n) ? __half2float(bT ? Bb[(int64_t)glb * n + gj] : Bb[(int64_t)gj * k + glb]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int l = 0; l < kF16SimtK; ++l) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) av[x] = sa[l][tx + 16 * x];
+#pragma unroll
+            for (int y = 0; y < 4; ++y) bv[y] = sb[l][ty + 16 * y];
+#pragma unroll
+            for (int y = 0; y < 4; ++y)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) acc[y][x] = fmaf(bv[y], av[x], acc[y][x]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int y = 0; y < 4; ++y) {
+        const int j = j0 + ty + 16 * y;
+        if (j >= n) continue;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int i = i0 + tx + 16 * x;
+            if (i < m) out[((int64_t)b * n + j) * m + i] = __float2half_rn(acc[y][x]);
+        }
+    }
+}
+
+int32_t launch_gemm_f16(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int aT, int bT, const void *A, const void *B, void *out,
+                        cudaStream_t stream) {
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    CPMK_REQUIRE(m >= 0 && n >= 0 && k >= 0 && batchA >= 1 && batchB >= 1, "bad size: m=%d k=%d n=%d batchA=%d batchB=%d", m, k, n, batchA, batchB);
+    // kernels/gemm.py:200-201
+    CPMK_REQUIRE(m % 2 == 0 && n % 2 == 0 && k % 2 == 0, "m, n, k must be even (m=%d k=%d n=%d)", m, k, n);
+    CPMK_REQUIRE(batchA == batchB || batchA == 1 || batchB == 1, "batch sizes must match or be 1 (batchA=%d batchB=%d)", batchA, batchB);
+    const int32_t batch = batchA > batchB ? batchA : batchB;
+    CPMK_REQUIRE(batch <= 65535, "batch %d exceeds 65535", batch);
+    if (m == 0 || n == 0) return CPMK_OK;
+    CPMK_REQUIRE(out, "null output pointer");
+    if (k == 0) {
+        CPMK_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)batch * n * m * sizeof(__half), stream));
+        return CPMK_OK;
+    }
+    CPMK_REQUIRE(A && B, "null operand pointer");
+    CPMK_REQUIRE((reinterpret_cast<uintptr_t>(A) & 1u) == 0 && (reinterpret_cast<uintptr_t>(B) & 1u) == 0 && (reinterpret_cast<uintptr_t>(out) & 1u) == 0,
+                 "operands must be 2-byte aligned");
+
+    // tensor-core path: contiguous extents and the output's rows multiples of 16 bytes, 16-byte aligned pointers
+    const int variant = gemm_variant();
+    const bool q_mn = !aT, p_mn = bT;
+    const bool strides_ok = (q_mn ? m % 8 == 0 : k % 8 == 0) && (p_mn ? n % 8 == 0 : k % 8 == 0) && m % 8 == 0;
+    int max_pairs = 0;
+    if (variant != kVariantGeneric && strides_ok && aligned16(A) && aligned16(B) && aligned16(out) && info.max_smem_optin >= kTc2SmemBytes) {
+        Workspace ws;
+        rc = get_workspace(stream, &ws);
+        if (rc) return rc;
+        rc = prepare_tc_kernels(info.device);
+        if (rc) return rc;
+        max_pairs = g_max_pairs[info.device & 63];
+        const int64_t tiles_r = (n + 2 * kBM - 1) / (2 * kBM), tiles_c = (m + kBN - 1) / kBN;
+        const int64_t total = tiles_r * tiles_c * batch;
+        CUtensorMap tmap_p, tmap_q;
+        OutMaps tmap_o;
+        memset(&tmap_o, 0, sizeof(tmap_o));
+        const bool enc_p = p_mn ? encode_operand_mn(&tmap_p, B, n, k, batchB, 2) : encode_operand(&tmap_p, B, n, k, batchB, kBM, 2);
+        const bool enc_q = q_mn ? encode_operand_mn(&tmap_q, A, m, k, batchA, 2) : encode_operand(&tmap_q, A, m, k, batchA, kHalfBN, 2);
+        if (max_pairs > 0 && total < (int64_t(1) << 31) && enc_p && enc_q && encode_output(&tmap_o.m[0], out, n, m, m, batch, true)) {
+            GemmParams prm;
+            memset(&prm, 0, sizeof(prm));
+            prm.R = n; prm.C = m; prm.K = k; prm.batch = batch;
+            prm.p_batched = batchB > 1; prm.q_batched = batchA > 1;
+            prm.num_kb = (k + kBKf16 - 1) / kBKf16;
+            prm.out = out;
+            prm.tma_store = 1;
+            prm.n_dst = 1;
+            prm.status = ws.status();
+            prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.total_tiles = (int32_t)total;
+            const int pairs = (int)(total < max_pairs ? total : max_pairs);
+            const dim3 grid(2 * pairs);
+            if (!p_mn && !q_mn) gemm_f16_tc2_kernel<false, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+            else if (!p_mn && q_mn) gemm_f16_tc2_kernel<false, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+            else if (p_mn && !q_mn) gemm_f16_tc2_kernel<true, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+            else gemm_f16_tc2_kernel<true, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+            CPMK_LAUNCH_CHECK();
+            g_last_path = 1;
+            g_last_variant = 2;
+            return CPMK_OK;
+        }
+    }
+    const dim3 grid((m + kSimtTile - 1) / kSimtTile, (n + kSimtTile - 1) / kSimtTile, batch);
+    CPMK_REQUIRE(grid.y <= 65535, "n = %d is too large for the generic kernel", n);
+    gemm_f16_simt_kernel<<<grid, 256, 0, stream>>>(m, k, n, batchA, batchB, aT, bT, static_cast<const __half *>(A), static_cast<const __half *>(B),
+                                                   static_cast<__half *>(out));
+    CPMK_LAUNCH_CHECK();
+    g_last_path = 2;
+    g_last_variant = 0;
+    return CPMK_OK;
+}
+
 }  // namespace
 }  // namespace cpmk
 
@@ -1073,6 +1260,11 @@ int32_t cpmk_gemm_int8_dequant_scatter(int32_t m, int32_t k, int32_t n, int32_t 
     }
     return launch_gemm<true>(m, k, n, batchA, batchB, aT != 0, bT != 0, A, B, scale_x, scale_y, broad_cast_x != 0, broad_cast_y != 0, nullptr,
                              as_stream(stream), n_dst, dst, dst_row_pitch);
+}
+
+int32_t cpmk_gemm_fp16(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT, const void *A, const void *B,
+                       void *out, cpmk_stream_t stream) {
+    return launch_gemm_f16(m, k, n, batchA, batchB, aT != 0, bT != 0, A, B, out, as_stream(stream));
 }
 
 int32_t cpmk_last_gemm_path(void) { return g_last_path; }

@@ -68,6 +68,19 @@ def gemm_int8(m: int, k: int, n: int,
     cpmk.call("cpmk_gemm_int8", m, k, n, batchA, batchB, int(bool(aT)), int(bool(bT)), A, B, out, stream_arg(stream))
 
 
+def gemm_fp16(m: int, k: int, n: int,
+              batchA: int, batchB: int,
+              aT: bool, bT: bool,
+              A: DevicePointer,    # (bA, k, m), or (bA, m, k) if aT     fp16
+              B: DevicePointer,    # (bB, n, k), or (bB, k, n) if bT     fp16
+              out: DevicePointer,  # (max(bA, bB), n, m)                 fp16
+              stream: CUDAStream):
+    """kernels/gemm.py:188-256.  out[b, j, i] = sum_l Aop[b, l, i] * Bop[b, j, l], fp32 accumulation, fp16 result."""
+    assert m % 2 == 0 and n % 2 == 0 and k % 2 == 0
+    assert batchA == batchB or batchA == 1 or batchB == 1
+    cpmk.call("cpmk_gemm_fp16", m, k, n, batchA, batchB, int(bool(aT)), int(bool(bT)), A, B, out, stream_arg(stream))
+
+
 def gemm_backward_round_scale(batch: int, n: int, m: int,
                               mat: DevicePointer,        # (batch, n, m) fp16
                               scale_y: DevicePointer,    # (batch, m)    fp16

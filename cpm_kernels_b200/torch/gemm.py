@@ -12,7 +12,7 @@ from typing import Optional
 
 import torch
 
-from ..kernels import (gemm_calc_scale, gemm_calc_scale_transpose, gemm_round, gemm_round_transpose, gemm_scale, gemm_int8,
+from ..kernels import (gemm_calc_scale, gemm_calc_scale_transpose, gemm_round, gemm_round_transpose, gemm_scale, gemm_int8, gemm_fp16,
                        gemm_backward_round_scale, gemm_backward_scale_round, gemm_scale_x, gemm_scale_y,
                        gemm_quantize_rows, gemm_quantize_cols, gemm_int8_scale)
 
@@ -165,16 +165,21 @@ class GEMMInt8(torch.autograd.Function):
         return grad_A, None, grad_B, None
 
 
-def _matmul_fp16(A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool) -> torch.Tensor:
-    a = A.transpose(-1, -2) if aT else A
-    b = B.transpose(-1, -2) if bT else B
-    return torch.matmul(a, b)
+def gemm_pth_fp16(A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool) -> torch.Tensor:
+    """torch/gemm.py:182-195: the fp16 GEMM with the operands swapped so that the result is row-major (b, M, N)."""
+    M = A.size(2) if aT else A.size(1)
+    K = A.size(1) if aT else A.size(2)
+    N = B.size(1) if bT else B.size(2)
+    out = torch.empty((max(A.size(0), B.size(0)), M, N), dtype=torch.float16, device=A.device)
+    gemm_fp16(N, K, M, B.size(0), A.size(0), bT, aT, B.data_ptr(), A.data_ptr(), out.data_ptr(),
+                 torch.cuda.current_stream().cuda_stream)
+    return out
 
 
 class GEMMFloat(torch.autograd.Function):
     """torch/gemm.py:197-231: the ``int8=False`` branch of ``bmm``.  The reference hands this fp16 GEMM to
-    cublasLt (kernels/gemm.py:188-256); it is outside the quantised path, and is likewise handed to the
-    vendor library here, through ``torch.matmul``."""
+    cublasLt (kernels/gemm.py:188-256); here it runs on the library's own tcgen05 ``kind::f16`` kernel
+    (``cpmk_gemm_fp16``: fp32 accumulation, one rounding to fp16)."""
 
     @staticmethod
     def forward(ctx, A: torch.Tensor, aT, B: torch.Tensor, bT):
@@ -184,15 +189,15 @@ class GEMMFloat(torch.autograd.Function):
         ctx.save_for_backward(A, B)
         ctx.aT = aT
         ctx.bT = bT
-        return _matmul_fp16(A, aT, B, bT)
+        return gemm_pth_fp16(A, aT, B, bT)
 
     @staticmethod
     def backward(ctx, grad_f):
         assert grad_f.is_cuda and grad_f.is_contiguous() and grad_f.dtype == torch.float16
         aT, bT = ctx.aT, ctx.bT
         A, B = ctx.saved_tensors
-        grad_A = _matmul_fp16(B, bT, grad_f, True) if aT else _matmul_fp16(grad_f, False, B, not bT)
-        grad_B = _matmul_fp16(grad_f, True, A, aT) if bT else _matmul_fp16(A, not aT, grad_f, False)
+        grad_A = gemm_pth_fp16(B, bT, grad_f, True) if aT else gemm_pth_fp16(grad_f, False, B, not bT)
+        grad_B = gemm_pth_fp16(grad_f, True, A, aT) if bT else gemm_pth_fp16(A, not aT, grad_f, False)
         if A.size(0) == 1 and grad_A.size(0) > 1:
             grad_A = grad_A.sum(dim=0, keepdim=True)
         if B.size(0) == 1 and grad_B.size(0) > 1:

@@ -123,7 +123,16 @@ int32_t cpmk_gemm_int8_dequant_scatter(int32_t m, int32_t k, int32_t n, int32_t 
                                        int32_t broad_cast_x, int32_t broad_cast_y, int32_t n_dst, void *const *dst,
                                        int64_t dst_row_pitch, cpmk_stream_t stream);
 
-/* Which GEMM kernel the last cpmk_gemm_int8* call on this thread selected:
+/* fp16 x fp16 -> fp16 GEMM with the argument conventions of cpmk_gemm_int8: out[b, j, i] = sum_l Aop[b, l, i] * Bop[b, j, l].
+ * Replaces cpm_kernels/kernels/gemm.py:188-256 gemm_fp16 (cublasLt, CUBLAS_COMPUTE_16F): the int8=False branch of
+ * cpm_kernels.torch.bmm (torch/gemm.py:182-239).  Products are accumulated in fp32 (tcgen05 kind::f16 with fp32
+ * tensor-memory accumulators) and rounded to fp16 once; the reference accumulates in fp16.  m, n, k even
+ * (kernels/gemm.py:200); the tensor-core kernel needs contiguous extents that are multiples of 8 elements and 16-byte
+ * aligned pointers, other shapes run on a generic kernel. */
+int32_t cpmk_gemm_fp16(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT,
+                       const void *A, const void *B, void *out, cpmk_stream_t stream);
+
+/* Which GEMM kernel the last cpmk_gemm_int8* / cpmk_gemm_fp16 call on this thread selected:
  * 1 = tcgen05 tensor-core kernel, 2 = generic SIMT kernel.  For tests and the benchmark. */
 int32_t cpmk_last_gemm_path(void);
 

@@ -99,6 +99,19 @@ def gemm_int8(m: int, k: int, n: int, aT: bool, bT: bool, A: np.ndarray, B: np.n
     return np.rint(out).astype(np.int32)
 
 
+def gemm_fp16(m: int, k: int, n: int, aT: bool, bT: bool, A: np.ndarray, B: np.ndarray) -> np.ndarray:
+    """cpm_kernels/kernels/gemm.py:188-256 gemm_fp16, same storage conventions as gemm_int8: A (bA, k, m) or
+    (bA, m, k) if aT; B (bB, n, k) or (bB, k, n) if bT.  Returns the exact products in float64 (b, n, m); the
+    reference's cublasLt call accumulates in fp16 and is pinned by its tests to 0.5 / 0.5 only
+    (tests/test_gemm.py:98)."""
+    a = A.astype(np.float64)
+    b = B.astype(np.float64)
+    a_km = np.swapaxes(a, 1, 2) if aT else a          # (bA, k, m)
+    b_nk = np.swapaxes(b, 1, 2) if bT else b          # (bB, n, k)
+    assert a_km.shape[1:] == (k, m) and b_nk.shape[1:] == (n, k)
+    return np.matmul(b_nk, a_km)
+
+
 def gemm_scale(mat: np.ndarray, scale_x: np.ndarray, scale_y: np.ndarray,
                broad_cast_x: bool, broad_cast_y: bool) -> np.ndarray:
     """cuda/gemm.cu:37-57.  mat int32 (batch, n, m); scale_x (batch or 1, n); scale_y (batch or 1, m).
