@@ -72,6 +72,9 @@ int32_t current_device_info(DeviceInfo *info);
 // The workspace of (current device, stream); allocates it on first use.
 int32_t get_workspace(cudaStream_t stream, Workspace *ws);
 
+// Element-wise GELU over `count` fp16 values (cpmk_gelu.cu); in == out is allowed.
+int32_t launch_gelu(int64_t count, const void *in, void *out, cudaStream_t stream);
+
 inline cudaStream_t as_stream(cpmk_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -157,6 +157,21 @@ def gemm_int8_scale(m: int, k: int, n: int,
               int(bool(broad_cast_x)), int(bool(broad_cast_y)), out, stream_arg(stream))
 
 
+def gemm_int8_scale_gelu(m: int, k: int, n: int,
+                         batchA: int, batchB: int,
+                         aT: bool, bT: bool,
+                         A: DevicePointer, B: DevicePointer,
+                         scale_x: DevicePointer, scale_y: DevicePointer,
+                         broad_cast_x: bool, broad_cast_y: bool,
+                         out: DevicePointer,        # (max(bA, bB), n, m) fp16
+                         stream: CUDAStream):
+    """gemm_int8_scale followed by gelu_forward on its result in place (kernels/gelu.py:33-50), one call."""
+    assert m % 4 == 0 and n % 4 == 0 and k % 4 == 0
+    assert batchA == batchB or batchA == 1 or batchB == 1
+    cpmk.call("cpmk_gemm_int8_dequant_gelu", m, k, n, batchA, batchB, int(bool(aT)), int(bool(bT)), A, B, scale_x, scale_y,
+              int(bool(broad_cast_x)), int(bool(broad_cast_y)), out, stream_arg(stream))
+
+
 def gemm_int8_scale_scatter(m: int, k: int, n: int,
                             batchA: int, batchB: int,
                             aT: bool, bT: bool,

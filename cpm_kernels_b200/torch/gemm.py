@@ -14,7 +14,7 @@ import torch
 
 from ..kernels import (gemm_calc_scale, gemm_calc_scale_transpose, gemm_round, gemm_round_transpose, gemm_scale, gemm_int8, gemm_fp16,
                        gemm_backward_round_scale, gemm_backward_scale_round, gemm_scale_x, gemm_scale_y,
-                       gemm_quantize_rows, gemm_quantize_cols, gemm_int8_scale)
+                       gemm_quantize_rows, gemm_quantize_cols, gemm_int8_scale, gemm_int8_scale_gelu)
 
 
 def _stream() -> int:
@@ -87,9 +87,9 @@ def gemm_and_scale(quantA: torch.Tensor, scaleA: Optional[torch.Tensor], quantB:
     return result_fp
 
 
-def _int8_forward(A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool):
+def _int8_forward(A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool, gelu: bool = False):
     """The three launches of the forward pass with one device guard and one stream lookup.
-    Returns (result, scale_A, quantized_A, scale_B, quantized_B)."""
+    Returns (result, scale_A, quantized_A, scale_B, quantized_B).  ``gelu``: GELU is applied to the result in place."""
     dev = A.device
     bA, bB = A.size(0), B.size(0)
     M = A.size(2) if aT else A.size(1)
@@ -108,8 +108,8 @@ def _int8_forward(A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool):
         (gemm_quantize_rows if bT else gemm_quantize_cols)(bB, B.size(1), B.size(2), B.data_ptr(), scale_B.data_ptr(),
                                                           quantized_B.data_ptr(), stream)
         # operands swapped (torch/gemm.py:45-52) so that the kernel-level (n, m) = (M, N) output is row-major C
-        gemm_int8_scale(N, K, M, bB, bA, bT, aT, quantized_B.data_ptr(), quantized_A.data_ptr(), scale_A.data_ptr(), scale_B.data_ptr(),
-                        bA == 1, bB == 1, result.data_ptr(), stream)
+        (gemm_int8_scale_gelu if gelu else gemm_int8_scale)(N, K, M, bB, bA, bT, aT, quantized_B.data_ptr(), quantized_A.data_ptr(),
+                                                            scale_A.data_ptr(), scale_B.data_ptr(), bA == 1, bB == 1, result.data_ptr(), stream)
     return result, scale_A, quantized_A, scale_B, quantized_B
 
 
@@ -218,3 +218,14 @@ def bmm(A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool, int8: bool = False
         assert A.dtype == torch.half and B.dtype == torch.half
         return _int8_forward(A, aT, B, bT)[0]
     return GEMMFloat.apply(A, aT, B, bT)
+
+
+def bmm_gelu(A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool) -> torch.Tensor:
+    """``gelu(bmm(A, aT, B, bT, int8=True))`` (cpm_kernels.torch.gelu after cpm_kernels.torch.bmm, as the feed-forward
+    block chains them) without a second tensor: the activation runs in place on the GEMM's result while it is still
+    in L2.  Forward only; same bits as the two calls."""
+    assert A.ndim == 3 and B.ndim == 3
+    assert A.is_cuda and B.is_cuda and A.device == B.device
+    assert A.is_contiguous() and B.is_contiguous()
+    assert A.dtype == torch.half and B.dtype == torch.half
+    return _int8_forward(A, aT, B, bT, gelu=True)[0]

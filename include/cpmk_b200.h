@@ -123,6 +123,19 @@ int32_t cpmk_gemm_int8_dequant_scatter(int32_t m, int32_t k, int32_t n, int32_t 
                                        int32_t broad_cast_x, int32_t broad_cast_y, int32_t n_dst, void *const *dst,
                                        int64_t dst_row_pitch, cpmk_stream_t stream);
 
+/* out[b, i] = gelu(mat[b, i]) on fp16, tanh form: replaces cpm_kernels/kernels/gelu.py:14-31 gelu_forward /
+ * gelu_inplace_forward (cuda/gelu.cu:6-17); `mat` is (batch, n) contiguous and out may equal mat.  Same bits as the
+ * reference's kernel for every fp16 input.  Large inputs use a 65536-entry table that the first call on a device
+ * fills on its stream (that call should not be inside a stream capture). */
+int32_t cpmk_gelu_forward(int32_t batch, int32_t n, const void *mat, void *out, cpmk_stream_t stream);
+
+/* cpmk_gemm_int8_dequant followed by GELU on the fp16 result, as the feed-forward block applies it after its first
+ * linear (cpm_kernels.torch.gelu after bmm): out = gelu(half(((float)acc * sx) * sy)), bit-identical to the two
+ * separate calls, enqueued back to back on `stream` so that the activation reads the result out of L2. */
+int32_t cpmk_gemm_int8_dequant_gelu(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT,
+                                    const void *A, const void *B, const void *scale_x, const void *scale_y,
+                                    int32_t broad_cast_x, int32_t broad_cast_y, void *out, cpmk_stream_t stream);
+
 /* fp16 x fp16 -> fp16 GEMM with the argument conventions of cpmk_gemm_int8: out[b, j, i] = sum_l Aop[b, l, i] * Bop[b, j, l].
  * Replaces cpm_kernels/kernels/gemm.py:188-256 gemm_fp16 (cublasLt, CUBLAS_COMPUTE_16F): the int8=False branch of
  * cpm_kernels.torch.bmm (torch/gemm.py:182-239).  Products are accumulated in fp32 (tcgen05 kind::f16 with fp32

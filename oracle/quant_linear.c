@@ -280,6 +280,21 @@ void orc_gemv_broadcast_mat_int8(int32_t batch, int32_t dim_out, int32_t dim_in,
         }
 }
 
+/*
+ * cuda/gelu.cu:6-17 cu_gelu_forward over `count` fp16 values.  The literals of the reference expression are doubles:
+ * products and sums run in binary64, tanhf takes and returns binary32 (evaluated here as the binary64 tanh rounded
+ * to binary32), the result is narrowed to binary32 and then to fp16.  NaN is written as 0x7fff, as __float2half does.
+ */
+void orc_gelu_forward(int64_t count, const uint16_t *in, uint16_t *out) {
+    for (int64_t i = 0; i < count; ++i) {
+        float x = h2f(in[i]);
+        float inner = (float)(0.7978845608028654 * x * (1.0 + 0.044715 * x * x));
+        float th = (float)tanh((double)inner);
+        float y = (float)(0.5 * x * (1.0 + th));
+        out[i] = (y != y) ? 0x7fff : f2h(y);
+    }
+}
+
 /* The plain reference expression `(int8_t)nearbyintf(x / s)` on one pair, for exhaustive rule checks. */
 int8_t orc_round_one(uint16_t x_bits, uint16_t s_bits) {
     return orc_cast_i8(nearbyintf(h2f(x_bits) / h2f(s_bits)));

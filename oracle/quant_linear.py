@@ -184,6 +184,24 @@ def gemv_broadcast_mat_int8(scale_mat, mat, scale_vec, vec) -> np.ndarray:
         return v.astype(np.float16)
 
 
+def gelu_forward(x: np.ndarray) -> np.ndarray:
+    """cuda/gelu.cu:6-17 cu_gelu_forward on an fp16 array of any shape:
+        x = (float)h;  x = 0.5 * x * (1.0 + tanhf(0.7978845608028654 * x * (1.0 + 0.044715 * x * x)));  out = half(x)
+    The literals are doubles, so every product and sum is carried out in binary64; the argument of tanhf is narrowed
+    to binary32 first and its result widened again; the final product is narrowed to binary32, then to fp16.  tanhf is
+    taken as correctly rounded here; against the reference's own device code this agrees on all 65536 fp16 inputs
+    (tests/golden/reference_gelu_sm100.npz).  NaN results carry the bit pattern 0x7fff that __float2half writes."""
+    assert x.dtype == np.float16
+    with np.errstate(all="ignore"):
+        xd = x.astype(np.float32).astype(np.float64)
+        inner = (0.7978845608028654 * xd * (1.0 + 0.044715 * xd * xd)).astype(np.float32)
+        th = np.tanh(inner.astype(np.float64)).astype(np.float32)
+        y = (0.5 * xd * (1.0 + th.astype(np.float64))).astype(np.float32).astype(np.float16)
+    bits = y.view(np.uint16).copy()
+    bits[np.isnan(y)] = 0x7FFF
+    return bits.view(np.float16)
+
+
 def bmm_int8(A: np.ndarray, aT: bool, B: np.ndarray, bT: bool):
     """cpm_kernels/torch/gemm.py:86-113 GEMMInt8.forward, restated with the functions above.
     A (bA, M, K) [or (bA, K, M) if aT], B (bB, K, N) [or (bB, N, K) if bT], fp16.
@@ -211,13 +229,17 @@ def build_c_oracle() -> str:
     return os.path.join(_HERE, "_build", "libquant_linear_oracle.so")
 
 
+def _c_oracle_path() -> str:
+    """The C library, rebuilt by make when quant_linear.c is newer (the reference's device code is left alone)."""
+    subprocess.run(["make", "-s", "-C", _HERE, "oracle"], check=True, stdout=subprocess.DEVNULL)
+    return os.path.join(_HERE, "_build", "libquant_linear_oracle.so")
+
+
 class COracle:
     """ctypes view of oracle/quant_linear.c.  Arrays are numpy, C-contiguous."""
 
     def __init__(self, path: str | None = None):
-        path = path or os.path.join(_HERE, "_build", "libquant_linear_oracle.so")
-        if not os.path.exists(path):
-            path = build_c_oracle()
+        path = path or _c_oracle_path()
         self.lib = ctypes.CDLL(path)
 
     @staticmethod
@@ -229,6 +251,11 @@ class COracle:
         b, n, m = mat.shape
         out = np.empty((b, n), np.float16)
         self.lib.orc_gemm_calc_scale(b, n, m, self._p(mat), self._p(out))
+        return out
+
+    def gelu_forward(self, x):
+        out = np.empty(x.shape, np.float16)
+        self.lib.orc_gelu_forward(ctypes.c_int64(x.size), self._p(x), self._p(out))
         return out
 
     def gemm_calc_scale_transpose(self, mat):

@@ -73,8 +73,11 @@ class ReferenceKernels:
         torch.zeros(1, device="cuda")       # make the primary context current
         self.drv = _Driver()
         self._fns = {}
-        for name in ("gemm", "gemv"):
-            with open(os.path.join(fatbin_dir, name + ".fatbin"), "rb") as f:
+        for name in ("gemm", "gemv", "gelu"):
+            path = os.path.join(fatbin_dir, name + ".fatbin")
+            if name == "gelu" and not os.path.exists(path):
+                continue                                  # only needed by gelu_forward
+            with open(path, "rb") as f:
                 setattr(self, "_mod_" + name, self.drv.load(f.read()))
 
     def _fn(self, mod, name):
@@ -168,6 +171,16 @@ class ReferenceKernels:
         out = torch.empty((b, n, m), dtype=torch.half, device=mat.device)
         self.drv.launch(self._fn("gemm", "cu_gemm_scale_y"), (b, n, 1), (min(m, 1024), 1, 1), self._stream(),
                         [self._i(b), self._i(n), self._i(m), self._p(mat), self._p(scale_y), self._p(out)])
+        return out
+
+    # ---- cpm_kernels/kernels/gelu.py -------------------------------------------------------------
+    def gelu_forward(self, mat: torch.Tensor) -> torch.Tensor:
+        """kernels/gelu.py:14-31: threads = min(round_up(n, 32), 1024); grid (batch, round_up(n, threads) / threads)."""
+        b, n = mat.shape
+        out = torch.empty_like(mat)
+        threads = min(_round_up(n, 32), 1024)
+        self.drv.launch(self._fn("gelu", "cu_gelu_forward"), (b, _round_up(n, threads) // threads, 1), (threads, 1, 1), self._stream(),
+                        [self._i(b), self._i(n), self._p(mat), self._p(out)])
         return out
 
     # ---- cpm_kernels/kernels/gemv.py -------------------------------------------------------------

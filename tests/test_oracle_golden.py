@@ -86,3 +86,12 @@ def test_int8_gemm_against_cublaslt(gold, c_oracle):
             for impl in (ql, c_oracle):
                 assert (impl.gemm_int8(16, 32, 8, bool(aT), bool(bT), A, B) == gold[tag + "_out"]).all()
     assert seen >= 1
+
+
+def test_gelu_restatements_match_the_reference_on_every_fp16_value():
+    """tests/golden/reference_gelu_sm100.npz holds the reference's cu_gelu_forward on all 65536 fp16 bit patterns."""
+    import os
+    table = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_gelu_sm100.npz"))["gelu_of_every_fp16"]
+    x = np.arange(65536, dtype=np.uint16).view(np.float16)
+    assert (ql.gelu_forward(x).view(np.uint16) == table).all()
+    assert (ql.COracle().gelu_forward(x).view(np.uint16) == table).all()
