@@ -422,62 +422,10 @@ def run_ours(args) -> None:
         mats = None
         del mats
 
-    # ---- the other configurations of the path, each timed with CUDA events over rotating inputs: the batched
-    #      attention-score bmm (HBM-bound: graded in GB/s), the fp16 branch of bmm, the quantisation passes, GELU ----
+    # ---- the other configurations of the path: attention-score bmm, fp16 bmm, quantisation passes, GELU ----
     other = None
     if rank == 0 and world == 1 and not args.kernels_only:
-        other = {}
-
-        def timed(fn, nbuf, iters=12, warm=3):
-            for j in range(warm):
-                fn(j % nbuf)
-            torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(stream)
-            for j in range(iters):
-                fn(j % nbuf)
-            b.record(stream)
-            torch.cuda.synchronize()
-            return a.elapsed_time(b) * 1e-3 / iters
-
-        # attention scores: 8 sequences x 32 heads, Q and K (256, 512, 128) -> (256, 512, 512); two input sets rotate
-        qs = [torch.randn((256, 512, 128), generator=gen, device=dev).half() for _ in range(2)]
-        ks = [torch.randn((256, 512, 128), generator=gen, device=dev).half() for _ in range(2)]
-        sec = timed(lambda j: ct.bmm(qs[j], False, ks[j], True, int8=True), 2)
-        alg = 2 * 256 * 512 * 128 * 2 + 256 * 512 * 512 * 2
-        from cpm_kernels_b200.torch.gemm import quantize, gemm_and_scale
-        sq, qq = quantize(qs[0], False)
-        sk, qk = quantize(ks[0], False)
-        sec_gemm = timed(lambda j: gemm_and_scale(qq, sq, qk, sk, False, True), 1)
-        alg_gemm = 2 * 256 * 512 * 128 + 256 * 512 * 512 * 2
-        other["attention_scores_bmm_int8"] = {
-            "shape": "Q, K (256, 512, 128) fp16 -> (256, 512, 512) fp16", "us": sec * 1e6, "GBps": alg / sec / 1e9,
-            "frac_of_hbm_peak": alg / sec / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes": alg,
-            "gemm_kernel_only": {"us": sec_gemm * 1e6, "GBps": alg_gemm / sec_gemm / 1e9, "frac_of_hbm_peak": alg_gemm / sec_gemm / 1e9 / peaks["hbm_gbs"]}}
-        del qs, ks, sq, qq, sk, qk
-        # fp16 branch of bmm on the same four linears (tcgen05 kind::f16, fp32 accumulation)
-        f16 = {}
-        for i, (name, n, k) in enumerate(SHAPES):
-            sec = timed(lambda j: ct.bmm(xs[i], False, ws[i], True, int8=False), 1, iters=8)
-            f16[name] = 2.0 * M_TOKENS * n * k / sec / 1e12
-        other["bmm_fp16_tflops"] = {"per_shape": f16, "peak_bf16_tflops": peaks["bf16_tflops"],
-                                    "frac_of_peak": (sum(f16.values()) / len(f16)) / peaks["bf16_tflops"]}
-        # quantisation passes (3 bytes per element algorithmic) and GELU (4 bytes per element), 4096 x 10240 operands
-        big = [torch.randn((1, 4096, 10240), generator=gen, device=dev).half() for _ in range(3)]
-        sc_r = torch.empty((1, 4096), dtype=torch.half, device=dev)
-        sc_c = torch.empty((1, 10240), dtype=torch.half, device=dev)
-        q8 = torch.empty((1, 4096, 10240), dtype=torch.int8, device=dev)
-        o16 = torch.empty((1, 4096, 10240), dtype=torch.half, device=dev)
-        st = stream.cuda_stream
-        nel = 4096 * 10240
-        for name, bytes_per, fn in (
-                ("quantize_rows", 3, lambda j: ck.gemm_quantize_rows(1, 4096, 10240, big[j].data_ptr(), sc_r.data_ptr(), q8.data_ptr(), st)),
-                ("quantize_cols", 3, lambda j: ck.gemm_quantize_cols(1, 4096, 10240, big[j].data_ptr(), sc_c.data_ptr(), q8.data_ptr(), st)),
-                ("gelu_forward", 4, lambda j: ck.gelu_forward(1, nel, big[j].data_ptr(), o16.data_ptr(), st))):
-            sec = timed(fn, 3)
-            other[name] = {"shape": "(1, 4096, 10240) fp16", "us": sec * 1e6, "GBps": bytes_per * nel / sec / 1e9,
-                           "frac_of_hbm_peak": bytes_per * nel / sec / 1e9 / peaks["hbm_gbs"]}
-        del big, q8, o16
+        other = measure_other_configs(("attention", "fp16", "passes"), dev, gen, stream, peaks, xs, ws)
 
     status = cpmk.read_status()
     if world > 1:
@@ -508,6 +456,87 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+def measure_other_configs(cases, dev, gen, stream, peaks, xs=None, ws=None, iters=12):
+    """The configurations of the path beside the headline step, each timed with CUDA events over rotating inputs:
+    "attention": the batched attention-score bmm (HBM-bound, graded in GB/s); "fp16": the int8=False branch of bmm on
+    the four linears; "passes": quantisation by rows / columns and GELU on a 4096 x 10240 operand."""
+    import torch
+    import cpm_kernels_b200.kernels as ck
+    import cpm_kernels_b200.torch as ct
+    other = {}
+
+    def timed(fn, nbuf, iters=iters, warm=3):
+        for j in range(warm):
+            fn(j % nbuf)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for j in range(iters):
+            fn(j % nbuf)
+        b.record(stream)
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1e-3 / iters
+
+    if "attention" in cases:
+        # 8 sequences x 32 heads, Q and K (256, 512, 128) -> (256, 512, 512); two input sets rotate
+        qs = [torch.randn((256, 512, 128), generator=gen, device=dev).half() for _ in range(2)]
+        ks = [torch.randn((256, 512, 128), generator=gen, device=dev).half() for _ in range(2)]
+        sec = timed(lambda j: ct.bmm(qs[j], False, ks[j], True, int8=True), 2)
+        alg = 2 * 256 * 512 * 128 * 2 + 256 * 512 * 512 * 2
+        from cpm_kernels_b200.torch.gemm import quantize, gemm_and_scale
+        sq, qq = quantize(qs[0], False)
+        sk, qk = quantize(ks[0], False)
+        sec_gemm = timed(lambda j: gemm_and_scale(qq, sq, qk, sk, False, True), 1)
+        alg_gemm = 2 * 256 * 512 * 128 + 256 * 512 * 512 * 2
+        other["attention_scores_bmm_int8"] = {
+            "shape": "Q, K (256, 512, 128) fp16 -> (256, 512, 512) fp16", "us": sec * 1e6, "GBps": alg / sec / 1e9,
+            "frac_of_hbm_peak": alg / sec / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes": alg,
+            "gemm_kernel_only": {"us": sec_gemm * 1e6, "GBps": alg_gemm / sec_gemm / 1e9, "frac_of_hbm_peak": alg_gemm / sec_gemm / 1e9 / peaks["hbm_gbs"]}}
+        del qs, ks, sq, qq, sk, qk
+    if "fp16" in cases:
+        # fp16 branch of bmm on the same four linears (tcgen05 kind::f16, fp32 accumulation)
+        f16 = {}
+        for i, (name, n, k) in enumerate(SHAPES):
+            sec = timed(lambda j: ct.bmm(xs[i], False, ws[i], True, int8=False), 1, iters=8)
+            f16[name] = 2.0 * M_TOKENS * n * k / sec / 1e12
+        other["bmm_fp16_tflops"] = {"per_shape": f16, "peak_bf16_tflops": peaks["bf16_tflops"],
+                                    "frac_of_peak": (sum(f16.values()) / len(f16)) / peaks["bf16_tflops"]}
+    if "passes" in cases:
+        # quantisation passes (3 bytes per element algorithmic) and GELU (4 bytes per element), 4096 x 10240 operands
+        big = [torch.randn((1, 4096, 10240), generator=gen, device=dev).half() for _ in range(3)]
+        sc_r = torch.empty((1, 4096), dtype=torch.half, device=dev)
+        sc_c = torch.empty((1, 10240), dtype=torch.half, device=dev)
+        q8 = torch.empty((1, 4096, 10240), dtype=torch.int8, device=dev)
+        o16 = torch.empty((1, 4096, 10240), dtype=torch.half, device=dev)
+        st = stream.cuda_stream
+        nel = 4096 * 10240
+        for name, bytes_per, fn in (
+                ("quantize_rows", 3, lambda j: ck.gemm_quantize_rows(1, 4096, 10240, big[j].data_ptr(), sc_r.data_ptr(), q8.data_ptr(), st)),
+                ("quantize_cols", 3, lambda j: ck.gemm_quantize_cols(1, 4096, 10240, big[j].data_ptr(), sc_c.data_ptr(), q8.data_ptr(), st)),
+                ("gelu_forward", 4, lambda j: ck.gelu_forward(1, nel, big[j].data_ptr(), o16.data_ptr(), st))):
+            sec = timed(fn, 3)
+            other[name] = {"shape": "(1, 4096, 10240) fp16", "us": sec * 1e6, "GBps": bytes_per * nel / sec / 1e9,
+                           "frac_of_hbm_peak": bytes_per * nel / sec / 1e9 / peaks["hbm_gbs"]}
+    return other
+
+
+def run_case(args):
+    """``--case attention|fp16|passes``: only that configuration, a few launches, for profiler captures.  Prints a
+    small JSON object of its own (not the benchmark line)."""
+    import torch
+    from cpm_kernels_b200.library import cpmk
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    cpmk.check_device()
+    gen = torch.Generator(device=dev).manual_seed(0)
+    xs = ws = None
+    if args.case == "fp16":
+        xs = [torch.randn((1, M_TOKENS, k), generator=gen, device=dev).half() for _, n, k in SHAPES]
+        ws = [(torch.randn((1, n, k), generator=gen, device=dev) * 0.02).half() for _, n, k in SHAPES]
+    out = measure_other_configs((args.case,), dev, gen, torch.cuda.current_stream(), measured_peaks(), xs, ws, iters=max(1, args.steps))
+    print(json.dumps({"case": args.case, "result": out}), flush=True)
+
+
 def main():
     global M_TOKENS
     ap = argparse.ArgumentParser()
@@ -521,10 +550,14 @@ def main():
                     help="tokens per step; anything but the default is a reduced case for profiler captures, not a bench value")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the e2e, GEMV and CPU-baseline legs (profiler captures of the step's kernels)")
+    ap.add_argument("--case", default="linears", choices=["linears", "attention", "fp16", "passes"],
+                    help="anything but 'linears' runs only that secondary configuration (profiler captures; no benchmark line)")
     args = ap.parse_args()
     M_TOKENS = args.tokens
     if args.impl == "reference":
         run_reference(args)
+    elif args.case != "linears":
+        run_case(args)
     else:
         run_ours(args)
 

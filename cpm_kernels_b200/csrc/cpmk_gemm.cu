@@ -61,7 +61,43 @@ struct GemmParams {
     int32_t tma_store;            // the two-CTA kernel writes its output with TMA stores (needs 16-byte row pitch)
     int32_t n_dst;                // number of destinations each output tile is stored to (1, or one per GPU when scattering)
     uint32_t *status;
+    // tile index -> (batch, column block, row block) without integer division: multipliers and shifts for
+    // tiles_r * tiles_c and for tiles_r (set_tile_divisors)
+    uint32_t per_batch, per_batch_mul, per_batch_shr, tiles_r_mul, tiles_r_shr;
 };
+
+// Division of a 31-bit value by a constant through a multiply-high: q = umulhi(x, mul) >> shr with
+// mul = ceil(2^(31 + ceil(log2 d)) / d), shr = ceil(log2 d) - 1; exact for 0 <= x < 2^31 (d = 1: q = x).
+inline void find_divisor(uint32_t d, uint32_t *mul, uint32_t *shr) {
+    if (d <= 1) {
+        *mul = 0;
+        *shr = 0;
+        return;
+    }
+    uint32_t lg = 0;
+    while ((1ull << lg) < d) ++lg;
+    const uint32_t p = 31 + lg;
+    *mul = (uint32_t)(((1ull << p) + d - 1) / d);
+    *shr = p - 32;
+}
+__host__ __device__ __forceinline__ uint32_t fast_div(uint32_t x, uint32_t d, uint32_t mul, uint32_t shr) {
+#if defined(__CUDA_ARCH__)
+    return d == 1 ? x : (__umulhi(x, mul) >> shr);
+#else
+    return d == 1 ? x : (uint32_t)(((uint64_t)x * mul) >> 32) >> shr;
+#endif
+}
+inline void set_tile_divisors(GemmParams *prm) {
+    prm->per_batch = (uint32_t)prm->tiles_r * (uint32_t)prm->tiles_c;
+    find_divisor(prm->per_batch, &prm->per_batch_mul, &prm->per_batch_shr);
+    find_divisor((uint32_t)prm->tiles_r, &prm->tiles_r_mul, &prm->tiles_r_shr);
+}
+__device__ __forceinline__ void tile_coords(const GemmParams &prm, int tile, int &b, int &c_blk, int &r_blk) {
+    b = (int)fast_div((uint32_t)tile, prm.per_batch, prm.per_batch_mul, prm.per_batch_shr);
+    const int rem = tile - b * (int)prm.per_batch;
+    c_blk = (int)fast_div((uint32_t)rem, (uint32_t)prm.tiles_r, prm.tiles_r_mul, prm.tiles_r_shr);
+    r_blk = rem - c_blk * prm.tiles_r;
+}
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int32_t c0, int32_t c1, int32_t c2, uint32_t bar) {
     asm volatile(
@@ -256,9 +292,8 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_const
             uint32_t stage = 0, phase = 0;
             bool alive = true;
             for (int tile = blockIdx.x; alive && tile < prm.total_tiles; tile += gridDim.x) {
-                const int b = tile / tiles_per_batch;
-                const int rem = tile - b * tiles_per_batch;
-                const int c_blk = rem / prm.tiles_r, r_blk = rem - c_blk * prm.tiles_r;
+                int b, c_blk, r_blk;
+                tile_coords(prm, tile, b, c_blk, r_blk);
                 for (int kb = 0; kb < prm.num_kb; ++kb) {
                     if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, prm.status, kErrProducerWait)) { alive = false; break; }
                     const uint32_t p_dst = tiles_base + stage * kStageBytes;
@@ -303,9 +338,8 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_const
         const int quarter = warp & 3;                       // TMEM lanes [32*quarter, 32*quarter + 32)
         uint32_t acc = 0, acc_phase = 0;
         for (int tile = blockIdx.x; tile < prm.total_tiles; tile += gridDim.x) {
-            const int b = tile / tiles_per_batch;
-            const int rem = tile - b * tiles_per_batch;
-            const int c_blk = rem / prm.tiles_r, r_blk = rem - c_blk * prm.tiles_r;
+            int b, c_blk, r_blk;
+            tile_coords(prm, tile, b, c_blk, r_blk);
             if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, prm.status, kErrEpilogueWait)) break;
             tcgen05_fence_after();
             epilogue_rows<DEQUANT>(prm, tmem_base, acc, quarter, lane, b, r_blk * kBM, c_blk * kBN);
@@ -351,7 +385,7 @@ constexpr int kHalfBN = kBN / 2;                       // rows of the column ope
 constexpr int kQBytes2 = kHalfBN * kBK;                // 16 KiB
 constexpr int kStageBytes2 = kPBytes + kQBytes2;       // 32 KiB
 constexpr int kOutStageBytes = 32 * 128;                // one epilogue warp's staging tile: 32 rows x 128 bytes
-constexpr int kOutStagingBytes = 8 * 2 * kOutStageBytes; // eight epilogue warps, double-buffered: 64 KiB
+constexpr int kOutStagingBytes = 8 * 2 * kOutStageBytes; // eight epilogue warps, two tiles each: 64 KiB (with five operand stages)
 constexpr int kTc2SmemBytes = kStages2 * kStageBytes2 + kOutStagingBytes + 1024 + kBarrierBytes;
 constexpr uint32_t kInstrDesc2 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)((2 * kBM) >> 4) << 24);
 
@@ -369,8 +403,11 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
     return out;
 }
+// Arrive on a barrier of either CTA of the pair.  The arrival only hands a resource back (an accumulator that has been
+// read); nothing written by this thread is published through it, so the default CTA-scope release is enough -- a
+// cluster-scope release made every epilogue warp wait ~1000 cycles per tile for its earlier writes to drain.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA load issued by one CTA of a pair; the completion bytes go to `bar`, a shared::cluster barrier address
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int32_t c0, int32_t c1, int32_t c2, uint32_t bar) {
@@ -434,42 +471,64 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+// The dequantisation scales one epilogue warp needs for one tile, held in registers: the scale of the lane's output
+// row, and the 128 column scales of the warp's half of the tile spread over the lanes (lane l holds columns
+// 4 l .. 4 l + 3 as two half2 words; the epilogue broadcasts them with shuffles).  Loaded one tile ahead.
+// The values stay as loaded (fp16 bits) until the epilogue uses them: nothing here depends on the loads' results, so
+// the warp does not wait for them.
+struct TileScales {
+    unsigned short row;
+    uint2 cols;
+};
+__device__ __forceinline__ TileScales load_tile_scales(const GemmParams &prm, int b, int row, int warp_col, int lane) {
+    TileScales ts;
+    ts.row = row < prm.R ? __ldg(reinterpret_cast<const unsigned short *>(prm.scale_r) + (prm.bcast_r ? 0 : (int64_t)b * prm.R) + row) : (unsigned short)0;
+    const int c = warp_col + 4 * lane;                       // C % 8 == 0 on this path: the four columns are in or out together
+    ts.cols = c < prm.C ? __ldg(reinterpret_cast<const uint2 *>(prm.scale_c + (prm.bcast_c ? 0 : (int64_t)b * prm.C) + c)) : make_uint2(0u, 0u);
+    return ts;
+}
+
 // Epilogue of one warp for one finished accumulator, written through shared memory with TMA stores: the warp's
 // 32 rows x 256 columns leave as 128-byte-wide pieces (64 fp16 or 32 int32 columns): each lane converts its row,
 // writes it into a swizzled 32 x 128-byte staging tile (16-byte chunk j of row r at chunk j ^ (r & 7): no bank
 // conflicts, and what the store's 128-byte swizzle expects), and lane 0 issues the store.  Two staging tiles per
 // warp alternate, so converting piece i+1 overlaps the store of piece i; the stores are full lines and need no
 // edge predicates.
-template <bool DEQUANT, bool F16 = false>
+// NB staging tiles per warp (2 or 4) form two groups of NB / 2: the pieces of a group are staged, made visible to the
+// TMA unit with ONE proxy fence, and stored together, while the other group's stores drain.
+template <bool DEQUANT, bool F16, int NB>
 __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const OutMaps *tmap_o, uint32_t staging, uint32_t &buf,
                                                   uint32_t tmem_base, uint32_t acc, int quarter, int lane, int b, int row_base, int col_base,
-                                                  int half) {
-    const int row = row_base + quarter * 32 + lane;
-    const bool row_ok = row < prm.R;
-    float sr = 0.f;
-    if (DEQUANT && !F16 && row_ok) sr = __half2float(__ldg(prm.scale_r + (prm.bcast_r ? 0 : (int64_t)b * prm.R) + row));
-    const __half *sc = (DEQUANT && !F16) ? prm.scale_c + (prm.bcast_c ? 0 : (int64_t)b * prm.C) : nullptr;
+                                                  int half, const TileScales &ts) {
+    const float sr = __half2float(__ushort_as_half(ts.row));
     const int warp_col = col_base + half * (kBN / 2);                // this warp's 128 columns
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN + half * (kBN / 2);
     const uint32_t sw = (uint32_t)(lane & 7);
     constexpr int kSteps = (kBN / 2) / 32;                           // four steps of 32 columns
     constexpr int kStepsPerPiece = DEQUANT ? 2 : 1;                  // a stored piece is 128 bytes wide: 64 fp16 / 32 int32
 
-    // Software pipeline over the steps: the tensor-memory load and the column scales of step i+1 are requested
-    // before step i is converted, so their latencies hide behind the arithmetic and the shared-memory writes.
+    // Software pipeline over the steps: the tensor-memory load of step i+1 is requested before step i is converted,
+    // so its latency hides behind the arithmetic and the shared-memory writes.  No global load happens in here: the
+    // scales were fetched a tile ahead (TileScales), so the proxy fence before each store has nothing slow to wait for.
     uint32_t v[2][32];
-    uint4 cs[2][4];
-    auto request = [&](int st, int slot) {
-        tmem_ld_32x32b_x32(taddr + st * 32, v[slot]);
-        if (DEQUANT && !F16) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                const int c = warp_col + st * 32 + g * 8;
-                cs[slot][g] = c < prm.C ? __ldg(reinterpret_cast<const uint4 *>(sc + c)) : make_uint4(0, 0, 0, 0);   // C % 8 == 0 here
-            }
-        }
-    };
+    auto request = [&](int st, int slot) { tmem_ld_32x32b_x32(taddr + st * 32, v[slot]); };
     if (warp_col >= prm.C) return;                                   // uniform across the warp
+    constexpr int kGroup = NB / 2;                                   // pieces per fence and commit group
+    int staged = 0, staged_col0 = 0, staged_col1 = 0;                // pieces of the current group waiting to be stored
+    auto flush = [&]() {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            // one store per piece and destination (peers' buffers are reached over NVLink)
+            for (int i = 0; i < staged; ++i)
+                for (int d = 0; d < prm.n_dst; ++d)
+                    tma_store_3d(&tmap_o->m[d], staging + (buf + (uint32_t)i) * kOutStageBytes, i == 0 ? staged_col0 : staged_col1,
+                                 row_base + quarter * 32, b);
+            bulk_commit();
+        }
+        buf = (buf + kGroup) % NB;
+        staged = 0;
+    };
     request(0, 0);
 #pragma unroll
     for (int st = 0; st < kSteps; ++st) {
@@ -481,10 +540,10 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const O
         const bool last_of_piece = (st % kStepsPerPiece) == kStepsPerPiece - 1;
         const int piece_col = col0 - (st % kStepsPerPiece) * 32;
         if (piece_col >= prm.C) continue;                            // nothing of this piece is inside the output (uniform)
-        const uint32_t tile = staging + buf * kOutStageBytes;
+        const uint32_t tile = staging + (buf + (uint32_t)staged) * kOutStageBytes;
         const uint32_t my_row = tile + (uint32_t)lane * 128u;
-        if (first_of_piece) {
-            // the store issued two pieces ago read this tile: it must have finished reading
+        if (first_of_piece && staged == 0) {
+            // the stores committed two groups ago read these tiles: they must have finished reading
             if (lane == 0) bulk_wait_read<1>();
             __syncwarp();
         }
@@ -503,7 +562,14 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const O
             const uint32_t chunk0 = (uint32_t)(st % kStepsPerPiece) * 4u;      // 16-byte chunks 0-3 or 4-7 of the 128-byte row
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
-                const __half2 *sh = reinterpret_cast<const __half2 *>(&cs[slot][g]);
+                // columns 32 st + 8 g .. + 7 of the warp's 128: their scales sit in lanes 8 st + 2 g and 8 st + 2 g + 1
+                const int src = 8 * st + 2 * g;
+                uint32_t c4[4];
+                c4[0] = __shfl_sync(0xffffffffu, ts.cols.x, src);
+                c4[1] = __shfl_sync(0xffffffffu, ts.cols.y, src);
+                c4[2] = __shfl_sync(0xffffffffu, ts.cols.x, src + 1);
+                c4[3] = __shfl_sync(0xffffffffu, ts.cols.y, src + 1);
+                const __half2 *sh = reinterpret_cast<const __half2 *>(c4);
                 uint32_t o[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -520,16 +586,12 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const O
                 st_shared_v4(my_row + (((uint32_t)g ^ sw) << 4), v[slot][4 * g], v[slot][4 * g + 1], v[slot][4 * g + 2], v[slot][4 * g + 3]);
         }
         if (last_of_piece) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) {
-                // one store per destination, all reading the same staged tile (peers' buffers are reached over NVLink)
-                for (int d = 0; d < prm.n_dst; ++d) tma_store_3d(&tmap_o->m[d], tile, piece_col, row_base + quarter * 32, b);
-                bulk_commit();
-            }
-            buf ^= 1u;
+            if (staged == 0) staged_col0 = piece_col;
+            else staged_col1 = piece_col;
+            if (++staged == kGroup) flush();
         }
     }
+    if (staged > 0) flush();
 }
 
 // P_MN / Q_MN: the row / column operand is stored with its rows contiguous (k is the slow axis) instead of k:
@@ -537,18 +599,22 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const O
 // shared-memory tiles are MN-major, and bits 15 / 16 of the instruction descriptor say so.
 // F16: fp16 operands (kBKf16 elements of k per stage, kind::f16, fp32 accumulators) and an fp16 result with no
 // scales; everything else -- stage bytes, barriers, tile walk, epilogue staging -- is the int8 pipeline's.
-template <bool DEQUANT, bool P_MN, bool Q_MN, bool F16>
+// STAGES operand stages of 32 KiB and 7 - STAGES output staging tiles per epilogue warp share the same 224 KiB.
+// Five stages and two tiles are used; three and four (half as many proxy fences in the epilogue) measured the same on
+// reductions of a single stage, where the epilogue is all there is.
+template <bool DEQUANT, bool P_MN, bool Q_MN, bool F16, int STAGES>
 __device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CUtensorMap &tmap_q, const OutMaps &tmap_o, const GemmParams &prm) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t staging_base = tiles_base + kStages2 * kStageBytes2;       // 1024-byte aligned: swizzle atoms
-    const uint32_t bars_base = staging_base + kOutStagingBytes;
+    const uint32_t staging_base = tiles_base + STAGES * kStageBytes2;       // 1024-byte aligned: swizzle atoms
+    constexpr int kOutBufs = 7 - STAGES;                          // staging tiles per epilogue warp
+    const uint32_t bars_base = staging_base + kEpiWarps2 * kOutBufs * kOutStageBytes;
     const uint32_t full_bar = bars_base;                          // used in the leader only
-    const uint32_t empty_bar = bars_base + 8 * kStages2;
-    const uint32_t tmem_full_bar = bars_base + 16 * kStages2;
+    const uint32_t empty_bar = bars_base + 8 * STAGES;
+    const uint32_t tmem_full_bar = bars_base + 16 * STAGES;
     const uint32_t tmem_empty_bar = tmem_full_bar + 16;           // used in the leader only
     uint8_t *bars_generic = smem_raw + (bars_base - smem_u32(smem_raw));
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars_generic + 16 * kStages2 + 32);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars_generic + 16 * STAGES + 32);
     volatile uint32_t *abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -556,7 +622,7 @@ __device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CU
     const bool leader = rank == 0;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages2; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar + 8 * s, 1);
             mbar_init(empty_bar + 8 * s, 1);
         }
@@ -583,9 +649,8 @@ __device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CU
             uint32_t stage = 0, phase = 0;
             bool alive = true;
             for (int tile = pair; alive && tile < prm.total_tiles; tile += num_pairs) {
-                const int b = tile / tiles_per_batch;
-                const int rem = tile - b * tiles_per_batch;
-                const int c_blk = rem / prm.tiles_r, r_blk = rem - c_blk * prm.tiles_r;
+                int b, c_blk, r_blk;
+                tile_coords(prm, tile, b, c_blk, r_blk);
                 const int row0 = r_blk * (2 * kBM) + (int)rank * kBM;
                 const int col0 = c_blk * kBN + (int)rank * kHalfBN;
                 for (int kb = 0; kb < prm.num_kb; ++kb) {
@@ -605,7 +670,7 @@ __device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CU
                         tma_load_3d_pair(p_dst + kPBytes + kMnBlockF16, &tmap_q, col0 + 64, kb * kKe, prm.q_batched ? b : 0, leader_full);
                     } else if (Q_MN) tma_load_3d_pair(p_dst + kPBytes, &tmap_q, col0, kb * kKe, prm.q_batched ? b : 0, leader_full);
                     else tma_load_3d_pair(p_dst + kPBytes, &tmap_q, kb * kKe, col0, prm.q_batched ? b : 0, leader_full);
-                    if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
         }
@@ -637,7 +702,7 @@ __device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CU
                         else umma_i8_pair(d_tmem, pd, qd, idesc, (kb | j) != 0 ? 1u : 0u);
                     }
                     umma_commit_pair(empty_bar + 8 * stage, 3);
-                    if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!alive) break;
                 umma_commit_pair(tmem_full_bar + 8 * acc, 3);
@@ -648,18 +713,28 @@ __device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CU
     } else {
         // ---------------- epilogue (both CTAs; each owns 128 of the tile's 256 rows) ----------------
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;                // which 128 of the tile's 256 columns this warp writes
+        constexpr bool kScales = DEQUANT && !F16;
         uint32_t acc = 0, acc_phase = 0, out_buf = 0;
+        auto scales_of = [&](int tile) {
+            int b, c_blk, r_blk;
+            tile_coords(prm, tile, b, c_blk, r_blk);
+            return load_tile_scales(prm, b, r_blk * (2 * kBM) + (int)rank * kBM + quarter * 32 + lane, c_blk * kBN + half * (kBN / 2), lane);
+        };
+        TileScales ts = {(unsigned short)0, make_uint2(0u, 0u)}, ts_next = ts;
+        if (kScales && prm.tma_store && pair < prm.total_tiles) ts = scales_of(pair);
         for (int tile = pair; tile < prm.total_tiles; tile += num_pairs) {
-            const int b = tile / tiles_per_batch;
-            const int rem = tile - b * tiles_per_batch;
-            const int c_blk = rem / prm.tiles_r, r_blk = rem - c_blk * prm.tiles_r;
+            int b, c_blk, r_blk;
+            tile_coords(prm, tile, b, c_blk, r_blk);
+            // the next tile's scales travel while this tile is converted
+            if (kScales && prm.tma_store && tile + num_pairs < prm.total_tiles) ts_next = scales_of(tile + num_pairs);
             if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, prm.status, kErrEpilogueWait)) break;
             tcgen05_fence_after();
-            const int half = (warp - 2) >> 2;            // which 128 of the tile's 256 columns this warp writes
-            if (F16 || prm.tma_store)                    // (the fp16 GEMM is only launched with TMA stores)
-                epilogue_rows_tma<DEQUANT, F16>(prm, &tmap_o, staging_base + (uint32_t)(warp - 2) * 2u * kOutStageBytes, out_buf, tmem_base, acc, quarter,
-                                           lane, b, r_blk * (2 * kBM) + (int)rank * kBM, c_blk * kBN, half);
-            else
+            if (F16 || prm.tma_store) {                  // (the fp16 GEMM is only launched with TMA stores)
+                epilogue_rows_tma<DEQUANT, F16, kOutBufs>(prm, &tmap_o, staging_base + (uint32_t)(warp - 2) * kOutBufs * kOutStageBytes, out_buf, tmem_base, acc, quarter,
+                                           lane, b, r_blk * (2 * kBM) + (int)rank * kBM, c_blk * kBN, half, ts);
+                ts = ts_next;
+            } else
                 epilogue_rows<DEQUANT>(prm, tmem_base, acc, quarter, lane, b, r_blk * (2 * kBM) + (int)rank * kBM, c_blk * kBN, half * 4, half * 4 + 4);
             tcgen05_fence_before();
             __syncwarp();
@@ -688,7 +763,7 @@ template <bool DEQUANT, bool P_MN, bool Q_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads2, 1)
 gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ OutMaps tmap_o, const GemmParams prm) {
-    tc2_pipeline<DEQUANT, P_MN, Q_MN, false>(tmap_p, tmap_q, tmap_o, prm);
+    tc2_pipeline<DEQUANT, P_MN, Q_MN, false, kStages2>(tmap_p, tmap_q, tmap_o, prm);
 }
 
 // fp16 x fp16 -> fp16 with fp32 accumulation on the same pipeline (the reference's gemm_fp16, kernels/gemm.py:188-256)
@@ -696,7 +771,7 @@ template <bool P_MN, bool Q_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads2, 1)
 gemm_f16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
                     const __grid_constant__ OutMaps tmap_o, const GemmParams prm) {
-    tc2_pipeline<true, P_MN, Q_MN, true>(tmap_p, tmap_q, tmap_o, prm);
+    tc2_pipeline<true, P_MN, Q_MN, true, kStages2>(tmap_p, tmap_q, tmap_o, prm);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1054,6 +1129,7 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
             const bool enc_q = q_mn ? encode_operand_mn(&tmap_q, A, m, k, batchA) : encode_operand(&tmap_q, A, m, k, batchA, kHalfBN);
             if (total < (int64_t(1) << 31) && enc_p && enc_q) {
                 prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.total_tiles = (int32_t)total;
+            set_tile_divisors(&prm);
                 const int pairs = (int)(total < max_pairs ? total : max_pairs);
                 const dim3 grid(2 * pairs);
                 OutMaps tmap_o;
@@ -1066,7 +1142,7 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
                     set_error("scattered output needs a row pitch that is a multiple of 16 bytes and 16-byte aligned destinations");
                     return CPMK_EINVAL;
                 }
-                if (!p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, false, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+if (!p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, false, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
                 else if (!p_mn && q_mn) gemm_i8_tc2_kernel<DEQUANT, false, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
                 else if (p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, true, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
                 else gemm_i8_tc2_kernel<DEQUANT, true, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
@@ -1085,6 +1161,7 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
         if (!any_mn && variant != kVariantTwoCta && total_tiles < (int64_t(1) << 31) && encode_operand(&tmap_p, B, n, k, batchB, kBM) &&
             encode_operand(&tmap_q, A, m, k, batchA, kBN)) {
             prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.total_tiles = (int32_t)total_tiles;
+            set_tile_divisors(&prm);
             const int grid = (int)(total_tiles < info.sm_count ? total_tiles : info.sm_count);
             gemm_i8_tc_kernel<DEQUANT><<<grid, kTcThreads, kTcSmemBytes, stream>>>(tmap_p, tmap_q, prm);
             CPMK_LAUNCH_CHECK();
@@ -1210,9 +1287,10 @@ int32_t launch_gemm_f16(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t
             prm.n_dst = 1;
             prm.status = ws.status();
             prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.total_tiles = (int32_t)total;
+            set_tile_divisors(&prm);
             const int pairs = (int)(total < max_pairs ? total : max_pairs);
             const dim3 grid(2 * pairs);
-            if (!p_mn && !q_mn) gemm_f16_tc2_kernel<false, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+if (!p_mn && !q_mn) gemm_f16_tc2_kernel<false, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
             else if (!p_mn && q_mn) gemm_f16_tc2_kernel<false, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
             else if (p_mn && !q_mn) gemm_f16_tc2_kernel<true, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
             else gemm_f16_tc2_kernel<true, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
