@@ -103,7 +103,7 @@ constexpr uint32_t kErrGemvConsumer = 0x202;
 // Rows longer than one stage slot are streamed in chunks of `chunk` halves (<= 4096): a stage then holds the
 // same chunk of eight consecutive rows, and each warp carries its row's sum across the chunks.
 template <bool SHARED>
-__global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int64_t total_rows, int32_t dim_out, int32_t dim_in, int32_t chunk,
+__global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int64_t rows_base, int64_t rows_extra, int32_t dim_out, int32_t dim_in, int32_t chunk,
                                                                              int32_t stages, const __half *__restrict__ mat,
                                                                              const __half *__restrict__ vec, __half *__restrict__ out,
                                                                              uint32_t *status) {
@@ -129,8 +129,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int
     }
     __syncthreads();
 
-    // this block's rows: [r0, r1)
-    const int64_t r0 = total_rows * blockIdx.x / gridDim.x, r1 = total_rows * (blockIdx.x + 1) / gridDim.x;
+    // this block's rows [r0, r1): total_rows = rows_base * gridDim.x + rows_extra, the first rows_extra blocks take one more
+    // (host-computed: a 64-bit division here would sit in front of the first copy)
+    const int64_t bx = blockIdx.x;
+    const int64_t r0 = bx * rows_base + (bx < rows_extra ? bx : rows_extra), r1 = r0 + rows_base + (bx < rows_extra ? 1 : 0);
     const int groups = (int)((r1 - r0 + kStreamRows - 1) / kStreamRows);
 
     if (warp == kStreamRows) {
@@ -157,7 +159,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int
         bool alive = true;
         for (int g = 0; alive && g < groups; ++g) {
             const int64_t row = r0 + (int64_t)g * kStreamRows + warp;
-            const int b = SHARED ? 0 : (int)((row < r1 ? row : r0) / dim_out);
+            // (one matrix: every row belongs to batch entry 0; otherwise one division per group, overlapped with the copy)
+            const int b = (SHARED || rows_base * gridDim.x + rows_extra == dim_out) ? 0 : (int)((row < r1 ? row : r0) / dim_out);
             float acc0 = 0.f, acc1 = 0.f;
             for (int c = 0; c < chunks; ++c) {
                 if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kErrGemvConsumer)) { alive = false; break; }
@@ -589,8 +592,8 @@ int32_t launch_gemv_rows(int32_t batch, int32_t dim_out, int32_t dim_in, const v
             int stages = (int)(kStreamRingBytes / ((int64_t)chunk * 2 * kStreamRows));
             if (stages > 16) stages = 16;
             const size_t smem = (size_t)stages * chunk * 2 * kStreamRows;
-            gemv_rows_stream_kernel<SHARED><<<info.sm_count, kStreamThreads, smem, stream>>>(total_rows, dim_out, dim_in, chunk, stages, w, x, y,
-                                                                                            ws.status());
+            gemv_rows_stream_kernel<SHARED><<<info.sm_count, kStreamThreads, smem, stream>>>(total_rows / info.sm_count, total_rows % info.sm_count,
+                                                                                            dim_out, dim_in, chunk, stages, w, x, y, ws.status());
             CPMK_LAUNCH_CHECK();
             return CPMK_OK;
         }

@@ -30,9 +30,11 @@ __global__ void __launch_bounds__(kBlock, NV <= 4 ? 6 : 4) quant_rows_kernel(int
                                                             __half *__restrict__ scale, int8_t *__restrict__ out) {
     __shared__ float warp_max[kBlock / 32];
     const int tid = threadIdx.x;
-    const int rows_per_block = kBlock / group;
+    // group is a power of two: shifts, not divisions (a division's latency would sit in front of the first load)
+    const int group_log2 = 31 - __clz(group);
+    const int rows_per_block = kBlock >> group_log2;
     const int lane_in_row = tid & (group - 1);
-    const int64_t row = (int64_t)blockIdx.x * rows_per_block + tid / group;
+    const int64_t row = (int64_t)blockIdx.x * rows_per_block + (tid >> group_log2);
     const bool row_ok = FULL || row < rows;
     const int nvec = m >> 3;
     const uint4 *src = reinterpret_cast<const uint4 *>(mat + (row_ok ? row : 0) * (int64_t)m);
@@ -58,7 +60,7 @@ __global__ void __launch_bounds__(kBlock, NV <= 4 ? 6 : 4) quant_rows_kernel(int
         if (group > 32) {
             if ((tid & 31) == 0) warp_max[tid >> 5] = amax;
             __syncthreads();
-            const int first_warp = (tid / group) * (group >> 5);
+            const int first_warp = (tid >> group_log2) * (group >> 5);
             amax = warp_max[first_warp];
             for (int w = 1; w < (group >> 5); ++w) amax = fmaxf(amax, warp_max[first_warp + w]);
         }
