@@ -513,7 +513,8 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const O
     uint32_t v[2][32];
     auto request = [&](int st, int slot) { tmem_ld_32x32b_x32(taddr + st * 32, v[slot]); };
     if (warp_col >= prm.C) return;                                   // uniform across the warp
-    constexpr int kGroup = NB / 2;                                   // pieces per fence and commit group
+    constexpr int kGroup = NB >= 2 ? NB / 2 : 1;                     // pieces per fence and commit group
+    constexpr int kPendingGroups = NB / kGroup - 1;                  // commit groups that may still be reading when a group is reused
     int staged = 0, staged_col0 = 0, staged_col1 = 0;                // pieces of the current group waiting to be stored
     auto flush = [&]() {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -544,7 +545,7 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const O
         const uint32_t my_row = tile + (uint32_t)lane * 128u;
         if (first_of_piece && staged == 0) {
             // the stores committed two groups ago read these tiles: they must have finished reading
-            if (lane == 0) bulk_wait_read<1>();
+            if (lane == 0) bulk_wait_read<kPendingGroups>();
             __syncwarp();
         }
         if (F16) {
