@@ -251,8 +251,15 @@ __global__ void __launch_bounds__(kBlock) quant_cols_round_kernel(int32_t n, int
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float2 f = __half22float2(h[j]);
-                bits[2 * j] = (uint8_t)round_reference(f.x, s[2 * j]);
-                bits[2 * j + 1] = (uint8_t)round_reference(f.y, s[2 * j + 1]);
+                const float2 magic = make_float2(CPMK_ROUND_MAGIC, CPMK_ROUND_MAGIC);
+                const float2 up = __ffma2_rn(f, make_float2(r_up[2 * j], r_up[2 * j + 1]), magic);
+                const float2 dn = __ffma2_rn(f, make_float2(r_dn[2 * j], r_dn[2 * j + 1]), magic);
+                // a tie inside the domain: up = dn + 1 (false for NaN / the out-of-domain marker), the even neighbour;
+                // anything else irregular: the reference expression
+                const bool fast_x = (up.x == dn.x || up.x - dn.x == 1.f) && (SRC != 1 || range < 0x100u);
+                const bool fast_y = (up.y == dn.y || up.y - dn.y == 1.f) && (SRC != 1 || range < 0x100u);
+                bits[2 * j] = fast_x ? resolve_tie(__float_as_uint(up.x), __float_as_uint(dn.x)) : (uint8_t)round_reference(f.x, s[2 * j]);
+                bits[2 * j + 1] = fast_y ? resolve_tie(__float_as_uint(up.y), __float_as_uint(dn.y)) : (uint8_t)round_reference(f.y, s[2 * j + 1]);
             }
         }
         uint2 q;
@@ -388,12 +395,24 @@ __global__ void __launch_bounds__(kCsThreads, 2) quant_cols_stream_kernel(int32_
                                 bits[2 * j] = __float_as_uint(dn.x);
                                 bits[2 * j + 1] = __float_as_uint(dn.y);
                             }
-                            if (!(bad.x + bad.y == 0.f)) {
+                            const float bad_sum = bad.x + bad.y;
+                            if (!(bad_sum == 0.f)) {
+                                if (bad_sum < 64.f) {
+                                    // exact ties only (each contributes 1): the even neighbour, no division.  Columns whose
+                                    // scale has few significant bits tie on many rows, so this path must stay cheap.
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    const float2 f = __half22float2(h[j]);
-                                    bits[2 * j] = (uint8_t)round_reference(f.x, s[2 * j]);
-                                    bits[2 * j + 1] = (uint8_t)round_reference(f.y, s[2 * j + 1]);
+                                    for (int j = 0; j < 4; ++j) {
+                                        const float2 up = __ffma2_rn(__half22float2(h[j]), make_float2(r_up[2 * j], r_up[2 * j + 1]), magic);
+                                        bits[2 * j] = resolve_tie(__float_as_uint(up.x), bits[2 * j]);
+                                        bits[2 * j + 1] = resolve_tie(__float_as_uint(up.y), bits[2 * j + 1]);
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) {
+                                        const float2 f = __half22float2(h[j]);
+                                        bits[2 * j] = (uint8_t)round_reference(f.x, s[2 * j]);
+                                        bits[2 * j + 1] = (uint8_t)round_reference(f.y, s[2 * j + 1]);
+                                    }
                                 }
                             }
                             uint2 q;

@@ -30,6 +30,12 @@ __device__ __forceinline__ __half2 absmax8(const uint4 &v, __half2 m) {
     return m;
 }
 
+// The code of one element whose two roundings are `up_bits` and `dn_bits`: dn when they agree, else the even one of
+// the two neighbouring integers (cpmk_round_tie_even).  Only for elements inside the rule's domain.
+__device__ __forceinline__ uint32_t resolve_tie(uint32_t up_bits, uint32_t dn_bits) {
+    return up_bits == dn_bits ? dn_bits : cpmk_round_tie_even(up_bits, dn_bits);
+}
+
 // Rounds the 8 halves of `v` with one scale.  r_up is NaN when the scale is outside the rule's
 // domain, which sends every element to the reference expression.  The two roundings of each pair of
 // elements are one packed fp32 FMA each (fma.rn.f32x2).
@@ -55,12 +61,24 @@ __device__ __forceinline__ uint2 round8_one_scale(const uint4 &v, float s, float
         b[2 * i] = __float_as_uint(dn[i].x);
         b[2 * i + 1] = __float_as_uint(dn[i].y);
     }
-    if (!(bad.x + bad.y == 0.f)) {
+    const float bad_sum = bad.x + bad.y;
+    if (!(bad_sum == 0.f)) {
+        if (bad_sum < 64.f) {
+            // finite: the disagreements are exact ties (up = dn + 1), resolved to the even neighbour without a division
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __half22float2(h[i]);
-            b[2 * i] = (uint8_t)round_reference(f.x, s);
-            b[2 * i + 1] = (uint8_t)round_reference(f.y, s);
+            for (int i = 0; i < 4; ++i) {
+                const float2 up = __ffma2_rn(__half22float2(h[i]), ru, magic);
+                b[2 * i] = resolve_tie(__float_as_uint(up.x), b[2 * i]);
+                b[2 * i + 1] = resolve_tie(__float_as_uint(up.y), b[2 * i + 1]);
+            }
+        } else {
+            // NaN: a NaN / infinite element or a scale outside the rule's domain -- the reference expression itself
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]);
+                b[2 * i] = (uint8_t)round_reference(f.x, s);
+                b[2 * i + 1] = (uint8_t)round_reference(f.y, s);
+            }
         }
     }
     uint2 out;

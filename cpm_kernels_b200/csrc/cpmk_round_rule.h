@@ -74,4 +74,15 @@ CPMK_RULE_FN int cpmk_round_pair(float x, float r_up, float r_dn, uint32_t *bits
     return up == dn;
 }
 
+/*
+ * When the two roundings disagree inside the domain, x / s is an exact half-integer (anything else lies at least
+ * 2^-12 away from one, further than the two perturbed products reach), up and dn are the two neighbouring integers,
+ * and round-half-even picks the even one.  Adding the magic constant keeps the integer's parity in the lowest bit of
+ * the bit pattern (1.5 * 2^23 is even), so the answer is dn when its lowest bit is clear and up otherwise.
+ * Proven by the same enumeration as the rule itself (tests/csrc/round_rule_check.c).
+ */
+CPMK_RULE_FN uint32_t cpmk_round_tie_even(uint32_t up_bits, uint32_t dn_bits) {
+    return (dn_bits & 1u) ? up_bits : dn_bits;
+}
+
 #endif /* CPMK_ROUND_RULE_H_ */

@@ -2,7 +2,8 @@
  * Exhaustive host-side proof of the division-free rounding rule in
  * cpm_kernels_b200/csrc/cpmk_round_rule.h: for every fp16 scale s in the rule's domain and every
  * finite fp16 x with |x| * r_up <= limit, "up == dn" implies that the low byte of dn equals the
- * reference expression (int8_t)nearbyintf((float)x / (float)s)  (cuda/gemm.cu:16).
+ * reference expression (int8_t)nearbyintf((float)x / (float)s)  (cuda/gemm.cu:16), and "up != dn" implies that
+ * up and dn are neighbouring integers of which the even one (cpmk_round_tie_even) equals that expression.
  *
  * Usage: round_rule_check <first_scale_bits> <last_scale_bits> <stride>
  * Prints "pairs=<n> ties=<t> mismatches=<k>" and exits 0 iff k == 0.
@@ -37,7 +38,14 @@ int main(int argc, char **argv) {
                     ++bad;
                 }
             } else {
+                /* disagreement inside the domain: an exact tie, resolved to the even neighbour */
                 ++ties;
+                float up = fmaf(x, r_up, CPMK_ROUND_MAGIC), dn = fmaf(x, r_dn, CPMK_ROUND_MAGIC);
+                uint32_t got = cpmk_round_tie_even(cpmk_float_bits(up), cpmk_float_bits(dn));
+                if (fabsf(up - dn) != 1.0f || (int8_t)(uint8_t)(got & 0xff) != want) {
+                    if (bad < 10) fprintf(stderr, "tie mismatch x=%04x s=%04x up=%g dn=%g got=%d want=%d\n", xb, sb, up, dn, (int8_t)(got & 0xff), want);
+                    ++bad;
+                }
             }
         }
     }
