@@ -373,53 +373,80 @@ __global__ void __launch_bounds__(kCsThreads, 2) quant_cols_stream_kernel(int32_
             if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kErrColqConsumer)) break;
             if (col_ok) {
                 const uint8_t *src = ring + (size_t)stage * kCsStageBytes + (size_t)t * 16;
+                if (PASS == 0) {
 #pragma unroll
-                for (int r = 0; r < kCsRows; ++r) {
-                    if (r < nr) {
-                        const uint4 w = *reinterpret_cast<const uint4 *>(src + (size_t)r * (kCsCols * 2));
-                        const __half2 *h = reinterpret_cast<const __half2 *>(&w);
-                        if (PASS == 0) {
+                    for (int r = 0; r < kCsRows; ++r) {
+                        if (r < nr) {
+                            const uint4 w = *reinterpret_cast<const uint4 *>(src + (size_t)r * (kCsCols * 2));
+                            const __half2 *h = reinterpret_cast<const __half2 *>(&w);
 #pragma unroll
                             for (int j = 0; j < 4; ++j) m2[j] = __hmax2(__habs2(h[j]), m2[j]);
-                        } else {
-                            uint32_t bits[8];
-                            float2 bad = make_float2(0.f, 0.f);
-                            const float2 magic = make_float2(CPMK_ROUND_MAGIC, CPMK_ROUND_MAGIC);
+                        }
+                    }
+                } else {
+                    // every row of the stage goes out on the division-free path with no branch in between (a branch per
+                    // row makes each row wait for the previous one's dependency chain); rows with a tie, a NaN or an
+                    // out-of-domain scale are redone afterwards
+                    uint32_t redo = 0u, irregular = 0u;       // rows with a disagreement / of those, rows with a NaN sum
+                    const float2 magic = make_float2(CPMK_ROUND_MAGIC, CPMK_ROUND_MAGIC);
+                    const float2 minus_one = make_float2(-1.f, -1.f);
+                    int8_t *orow = obase + (int64_t)row * m;
+#pragma unroll
+                    for (int r = 0; r < kCsRows; ++r) {
+                        // (slots of rows beyond nr hold older data: computed, never stored, never counted)
+                        const uint4 w = *reinterpret_cast<const uint4 *>(src + (size_t)r * (kCsCols * 2));
+                        const __half2 *h = reinterpret_cast<const __half2 *>(&w);
+                        float2 dn[4];
+                        float2 bad = make_float2(0.f, 0.f);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 f = __half22float2(h[j]);
+                            const float2 up = __ffma2_rn(f, make_float2(r_up[2 * j], r_up[2 * j + 1]), magic);
+                            dn[j] = __ffma2_rn(f, make_float2(r_dn[2 * j], r_dn[2 * j + 1]), magic);
+                            const float2 d = __ffma2_rn(dn[j], minus_one, up);
+                            bad = __ffma2_rn(d, d, bad);
+                        }
+                        uint2 q;
+                        q.x = __byte_perm(__byte_perm(__float_as_uint(dn[0].x), __float_as_uint(dn[0].y), 0x0040),
+                                          __byte_perm(__float_as_uint(dn[1].x), __float_as_uint(dn[1].y), 0x0040), 0x5410);
+                        q.y = __byte_perm(__byte_perm(__float_as_uint(dn[2].x), __float_as_uint(dn[2].y), 0x0040),
+                                          __byte_perm(__float_as_uint(dn[3].x), __float_as_uint(dn[3].y), 0x0040), 0x5410);
+                        const float bad_sum = bad.x + bad.y;
+                        if (r < nr) {
+                            *reinterpret_cast<uint2 *>(orow + (int64_t)r * m) = q;
+                            redo |= (bad_sum == 0.f ? 0u : 1u) << r;
+                            irregular |= (bad_sum < 64.f ? 0u : 1u) << r;          // NaN compares false
+                        }
+                    }
+                    while (redo) {
+                        const int r = __ffs((int)redo) - 1;
+                        redo &= redo - 1u;
+                        const uint4 w = *reinterpret_cast<const uint4 *>(src + (size_t)r * (kCsCols * 2));
+                        const __half2 *h = reinterpret_cast<const __half2 *>(&w);
+                        uint32_t bits[8];
+                        if (!((irregular >> r) & 1u)) {
+                            // exact ties only: the even neighbour, no division.  Columns whose scale has few
+                            // significant bits tie on many rows, so this path must stay cheap.
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 const float2 f = __half22float2(h[j]);
                                 const float2 up = __ffma2_rn(f, make_float2(r_up[2 * j], r_up[2 * j + 1]), magic);
                                 const float2 dn = __ffma2_rn(f, make_float2(r_dn[2 * j], r_dn[2 * j + 1]), magic);
-                                const float2 d = __fadd2_rn(up, make_float2(-dn.x, -dn.y));
-                                bad = __ffma2_rn(d, d, bad);
-                                bits[2 * j] = __float_as_uint(dn.x);
-                                bits[2 * j + 1] = __float_as_uint(dn.y);
+                                bits[2 * j] = resolve_tie(__float_as_uint(up.x), __float_as_uint(dn.x));
+                                bits[2 * j + 1] = resolve_tie(__float_as_uint(up.y), __float_as_uint(dn.y));
                             }
-                            const float bad_sum = bad.x + bad.y;
-                            if (!(bad_sum == 0.f)) {
-                                if (bad_sum < 64.f) {
-                                    // exact ties only (each contributes 1): the even neighbour, no division.  Columns whose
-                                    // scale has few significant bits tie on many rows, so this path must stay cheap.
+                        } else {
 #pragma unroll
-                                    for (int j = 0; j < 4; ++j) {
-                                        const float2 up = __ffma2_rn(__half22float2(h[j]), make_float2(r_up[2 * j], r_up[2 * j + 1]), magic);
-                                        bits[2 * j] = resolve_tie(__float_as_uint(up.x), bits[2 * j]);
-                                        bits[2 * j + 1] = resolve_tie(__float_as_uint(up.y), bits[2 * j + 1]);
-                                    }
-                                } else {
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) {
-                                        const float2 f = __half22float2(h[j]);
-                                        bits[2 * j] = (uint8_t)round_reference(f.x, s[2 * j]);
-                                        bits[2 * j + 1] = (uint8_t)round_reference(f.y, s[2 * j + 1]);
-                                    }
-                                }
+                            for (int j = 0; j < 4; ++j) {
+                                const float2 f = __half22float2(h[j]);
+                                bits[2 * j] = (uint8_t)round_reference(f.x, s[2 * j]);
+                                bits[2 * j + 1] = (uint8_t)round_reference(f.y, s[2 * j + 1]);
                             }
-                            uint2 q;
-                            q.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
-                            q.y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
-                            *reinterpret_cast<uint2 *>(obase + (int64_t)(row + r) * m) = q;
                         }
+                        uint2 q;
+                        q.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+                        q.y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
+                        *reinterpret_cast<uint2 *>(orow + (int64_t)r * m) = q;
                     }
                 }
             }
@@ -716,6 +743,8 @@ int32_t launch_quant_cols(int32_t batch, int32_t n, int32_t m, const void *mat, 
             strips = (m + strip_cols - 1) / strip_cols;
             int64_t sp = target / ((int64_t)strips * batch);
             if (sp > by_rows) sp = by_rows;
+            // (folding the per-range maxima once in a small kernel between the passes, instead of in each block's prologue
+            // of the rounding pass, measured no faster: the extra kernel boundary costs what the prologues save)
             const int64_t by_scratch = (int64_t)(Workspace::kScratchBytes / (sizeof(__half) * (size_t)batch * (size_t)m));
             if (sp > by_scratch) sp = by_scratch;
             if (sp > 65535) sp = 65535;
