@@ -209,10 +209,11 @@ def run_ours(args) -> None:
     layers = [ColumnParallelInt8Linear(w) for w in ws] if world > 1 else None
     # preferred exchange: the GEMM epilogue stores each rank's output slice into every rank's full-width output
     # (peer-mapped symmetric memory); falls back to an NCCL all-gather beside the GEMM if that cannot be set up
-    fused_layers, exchange = None, "none"
+    fused_layers, exchange, fused_two_streams = None, "none", False
+    fused_margin = os.environ.get("CPMK_BENCH_FUSED_SM_MARGIN", "32")
     if world > 1:
         exchange = "nccl all_gather_into_tensor on a side stream"
-        if args.exchange == "fused":
+        if args.exchange in ("fused", "fused1"):
             try:
                 fused_layers = [FusedColumnParallelInt8Linear(w) for w in ws]
                 for fl in fused_layers:
@@ -224,6 +225,9 @@ def run_ours(args) -> None:
         if fused_layers is None:
             # the collective's kernels run beside the persistent GEMM grid: leave them a few SMs
             os.environ.setdefault("CPMK_GEMM_SM_MARGIN", "16")
+        elif args.exchange == "fused":
+            fused_two_streams = True
+            exchange += "; linears alternate between two streams, scatter GEMM grids leave %s SMs free" % fused_margin
 
     gemm_events = []
 
@@ -231,8 +235,21 @@ def run_ours(args) -> None:
         """The four linears through the public API.  With record_gemm, CUDA events bracket each GEMM launch."""
         results = []
         if fused_layers is not None and gather and not record_gemm:
-            for fl, x in zip(fused_layers, xs):
-                results.append(fl(x))
+            # The linears of the synthetic stack are independent, so they alternate between two streams: while one
+            # linear's GEMM drains its output over NVLink, the next one's quantisation passes and GEMM run beside it
+            # (the scatter GEMM's persistent grid leaves part of the SMs free for that: CPMK_GEMM_SM_MARGIN).
+            if fused_two_streams:
+                comm_stream.wait_stream(stream)
+                os.environ["CPMK_GEMM_SM_MARGIN"] = fused_margin      # read by the library at each launch
+            for i, (fl, x) in enumerate(zip(fused_layers, xs)):
+                if fused_two_streams and (i & 1):
+                    with torch.cuda.stream(comm_stream):
+                        results.append(fl(x))
+                else:
+                    results.append(fl(x))
+            if fused_two_streams:
+                stream.wait_stream(comm_stream)
+                os.environ.pop("CPMK_GEMM_SM_MARGIN", None)
             return results
         for i, (x, w) in enumerate(zip(xs, ws)):
             if record_gemm:
@@ -568,8 +585,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
-                    help="N > 1: how the output slices reach every rank (fused = stored by the GEMM epilogue; nccl = all-gather)")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "fused1", "nccl"],
+                    help="N > 1: how the output slices reach every rank (fused = stored by the GEMM epilogue, linears on two alternating streams; fused1 = the same on one stream; nccl = all-gather)")
     ap.add_argument("--tokens", type=int, default=M_TOKENS,
                     help="tokens per step; anything but the default is a reduced case for profiler captures, not a bench value")
     ap.add_argument("--kernels-only", action="store_true",
