@@ -210,4 +210,3 @@ def test_scattered_output_to_pitched_destinations(G, m, k, n, batch):
     with pytest.raises(RuntimeError, match="pitch"):
         ck.gemm_int8_scale_scatter(m, k, n, batch, batch, True, False, Ad.data_ptr(), Bd.data_ptr(), sxd.data_ptr(), syd.data_ptr(), False, False,
                                    dst, m - 8, G.stream())
-

@@ -106,4 +106,3 @@ def test_empty_and_zero_k(G):
     assert (G.host(out) == 0).all()
     with pytest.raises(AssertionError):
         ck.gemm_fp16(3, 8, 8, 1, 1, True, False, 0, 0, out.data_ptr(), G.stream())
-
