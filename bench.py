@@ -8,7 +8,7 @@ Workload (N = 1): the four CPM-Bee-10B layer linears at M = 4096 tokens (fused Q
 synthetic data.  One step = one pass over the four linears through the public entry point
 ``cpm_kernels_b200.torch.bmm(x, False, W, True, int8=True)``, which -- like the reference's bmm -- quantises
 BOTH operands on every call (per-row absmax scale + int8 rounding), runs the int8 GEMM and dequantises to fp16:
-three kernels per linear, twelve per step.  ``value`` counts 2*M*N*K operations of the four GEMMs over the whole
+two kernels per linear (both operands quantised in one launch, then the GEMM), eight per step.  ``value`` counts 2*M*N*K operations of the four GEMMs over the whole
 step time (quantisation passes included), inputs resident in HBM.  ``e2e`` is the same step driven from pinned
 host buffers: activations copied host->device and fp16 outputs device->host inside the timed region.
 
@@ -451,7 +451,7 @@ def run_ours(args) -> None:
     # ---- the other configurations of the path: attention-score bmm, fp16 bmm, quantisation passes, GELU ----
     other = None
     if rank == 0 and world == 1 and not args.kernels_only:
-        other = measure_other_configs(("attention", "prequantised", "fp16", "passes"), dev, gen, stream, peaks, xs, ws)
+        other = measure_other_configs(("attention", "prequantised", "transposed", "fp16", "passes"), dev, gen, stream, peaks, xs, ws)
 
     status = cpmk.read_status()
     if world > 1:
@@ -467,7 +467,7 @@ def run_ours(args) -> None:
         "config": {"workload": WORKLOAD if M_TOKENS == 4096 else WORKLOAD + " [REDUCED to %d tokens: profiling case, not a bench value]" % M_TOKENS, "tokens": M_TOKENS, "parallelism": "column-parallel x%d; exchange = %s" % (world, exchange) if world > 1 else "single GPU",
                    "l2": "per-step working set (fp16 weights 302 MB + activations 134 MB + outputs 252 MB) exceeds the 126 MB L2; no explicit flush",
                    "weights": "re-quantised on every call, as the reference's bmm does"},
-        "roofline": roofline, "e2e": e2e, "gpu_launches": 12 * args.steps, "clocks": clocks,
+        "roofline": roofline, "e2e": e2e, "gpu_launches": 8 * args.steps, "clocks": clocks,
         "gemv": gemv, "other_configs": other, "phases": phases, "device_status_word": status,
         "peaks": {k: peaks.get(k) for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained", "source")},
     }
@@ -485,7 +485,8 @@ def run_ours(args) -> None:
 def measure_other_configs(cases, dev, gen, stream, peaks, xs=None, ws=None, iters=12):
     """The configurations of the path beside the headline step, each timed with CUDA events over rotating inputs:
     "attention": the batched attention-score bmm (HBM-bound, graded in GB/s); "fp16": the int8=False branch of bmm on
-    the four linears; "prequantised": the headline linears with weights quantised once; "passes": quantisation by rows / columns and GELU on
+    the four linears; "prequantised": the headline linears with weights quantised once; "transposed": the same linears with weights
+    stored (K, N); "passes": quantisation by rows / columns and GELU on
     a 4096 x 10240 operand."""
     import torch
     import cpm_kernels_b200.kernels as ck
@@ -534,6 +535,17 @@ def measure_other_configs(cases, dev, gen, stream, peaks, xs=None, ws=None, iter
         sec = timed(pre_step, 1, iters=10)
         other["linears_weights_prequantised"] = {"ms_per_step": sec * 1e3, "TOPS": total_ops() / sec / 1e12, "launches_per_step": 8}
         del wq
+    if "transposed" in cases:
+        # the transposed-weight variant of the configuration: weights stored (K, N), so that bmm(x, False, w, False)
+        # quantises them by columns (gemm_calc_scale_transpose / gemm_round_transpose) and the GEMM reads an MN-major operand
+        wt = [w.transpose(1, 2).contiguous() for w in ws]
+
+        def t_step(j):
+            for i in range(len(SHAPES)):
+                ct.bmm(xs[i], False, wt[i], False, int8=True)
+        sec = timed(t_step, 1, iters=10)
+        other["linears_transposed_weights"] = {"ms_per_step": sec * 1e3, "TOPS": total_ops() / sec / 1e12, "launches_per_step": 16}
+        del wt
     if "fp16" in cases:
         # fp16 branch of bmm on the same four linears (tcgen05 kind::f16, fp32 accumulation)
         f16 = {}

@@ -25,16 +25,35 @@ constexpr int kBlock = 256;
 // MODE 0: scale and codes (fused);  1: scale only;  2: codes only, scale given.
 // ------------------------------------------------------------------------------------------------
 // FULL: every block has all its rows and every thread all NV vectors (no bounds predicates).
-template <int NV, int MODE, bool FULL>
+// PAIR: one launch quantises two operands of the same row length (the activations and the weight of a linear layer):
+// blocks from `second.first_block` on work on the second operand.  One grid instead of two saves the ramp and the tail
+// of the smaller launch.
+struct SecondOperand {
+    int64_t rows;
+    const __half *mat;
+    __half *scale;
+    int8_t *out;
+    unsigned first_block;
+};
+template <int NV, int MODE, bool FULL, bool PAIR = false>
 __global__ void __launch_bounds__(kBlock, NV <= 4 ? 6 : 4) quant_rows_kernel(int64_t rows, int32_t m, int group, const __half *__restrict__ mat,
-                                                            __half *__restrict__ scale, int8_t *__restrict__ out) {
+                                                            __half *__restrict__ scale, int8_t *__restrict__ out,
+                                                            const SecondOperand second = SecondOperand()) {
     __shared__ float warp_max[kBlock / 32];
     const int tid = threadIdx.x;
+    unsigned block = blockIdx.x;
+    if (PAIR && block >= second.first_block) {
+        block -= second.first_block;
+        rows = second.rows;
+        mat = second.mat;
+        scale = second.scale;
+        out = second.out;
+    }
     // group is a power of two: shifts, not divisions (a division's latency would sit in front of the first load)
     const int group_log2 = 31 - __clz(group);
     const int rows_per_block = kBlock >> group_log2;
     const int lane_in_row = tid & (group - 1);
-    const int64_t row = (int64_t)blockIdx.x * rows_per_block + (tid >> group_log2);
+    const int64_t row = (int64_t)block * rows_per_block + (tid >> group_log2);
     const bool row_ok = FULL || row < rows;
     const int nvec = m >> 3;
     const uint4 *src = reinterpret_cast<const uint4 *>(mat + (row_ok ? row : 0) * (int64_t)m);
@@ -655,6 +674,52 @@ int32_t launch_quant_rows(int32_t batch, int32_t n, int32_t m, const void *mat, 
     return CPMK_OK;
 }
 
+// Fused scale + round of two operands with rows of the same length in one launch (see SecondOperand).
+int32_t launch_quant_rows_pair(int64_t rows0, const void *mat0, void *scale0, void *out0, int64_t rows1, const void *mat1, void *scale1,
+                               void *out1, int32_t m, cudaStream_t stream, bool *done) {
+    *done = false;
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    if (rows0 <= 0 || rows1 <= 0 || m <= 0) return CPMK_OK;
+    const bool vec_ok = (m % 8 == 0) && m <= 256 * 8 * 8 && aligned16(mat0) && aligned16(mat1) && (reinterpret_cast<uintptr_t>(out0) & 7u) == 0 &&
+                        (reinterpret_cast<uintptr_t>(out1) & 7u) == 0;
+    if (!vec_ok) return CPMK_OK;
+    const int nvec = m / 8;
+    int group = 8;
+    while (group < 256 && group * 4 < nvec) group <<= 1;
+    const int nv = (nvec + group - 1) / group;
+    const int rows_per_block = kBlock / group;
+    const int64_t blocks0 = ceil_div64(rows0, rows_per_block), blocks1 = ceil_div64(rows1, rows_per_block);
+    if (blocks0 + blocks1 >= (int64_t(1) << 31)) return CPMK_OK;
+    SecondOperand second;
+    second.rows = rows1;
+    second.mat = static_cast<const __half *>(mat1);
+    second.scale = static_cast<__half *>(scale1);
+    second.out = static_cast<int8_t *>(out1);
+    second.first_block = (unsigned)blocks0;
+    const dim3 grid((unsigned)(blocks0 + blocks1));
+    const bool full = (rows0 % rows_per_block == 0) && (rows1 % rows_per_block == 0) && (nvec == group * nv) &&
+                      (nv == 1 || nv == 2 || nv == 4 || nv == 6 || nv == 8);
+    const __half *src = static_cast<const __half *>(mat0);
+    __half *sc = static_cast<__half *>(scale0);
+    int8_t *dst = static_cast<int8_t *>(out0);
+#define CPMK_LAUNCH_ROWS_PAIR(NVT)                                                                                               \
+    do {                                                                                                                         \
+        if (full) quant_rows_kernel<NVT, 0, true, true><<<grid, kBlock, 0, stream>>>(rows0, m, group, src, sc, dst, second);     \
+        else quant_rows_kernel<NVT, 0, false, true><<<grid, kBlock, 0, stream>>>(rows0, m, group, src, sc, dst, second);         \
+    } while (0)
+    if (nv <= 1) CPMK_LAUNCH_ROWS_PAIR(1);
+    else if (nv <= 2) CPMK_LAUNCH_ROWS_PAIR(2);
+    else if (nv <= 4) CPMK_LAUNCH_ROWS_PAIR(4);
+    else if (nv <= 6) CPMK_LAUNCH_ROWS_PAIR(6);
+    else CPMK_LAUNCH_ROWS_PAIR(8);
+#undef CPMK_LAUNCH_ROWS_PAIR
+    CPMK_LAUNCH_CHECK();
+    *done = true;
+    return CPMK_OK;
+}
+
 struct ColPlan {
     int strips, splits, rows_per_split;
 };
@@ -819,6 +884,26 @@ int32_t cpmk_gemm_round(int32_t batch, int32_t n, int32_t m, const void *mat, co
 
 int32_t cpmk_quantize_rows(int32_t batch, int32_t n, int32_t m, const void *mat, void *scale_out, void *q_out, cpmk_stream_t stream) {
     return launch_quant_rows<0>(batch, n, m, mat, scale_out, q_out, as_stream(stream));
+}
+
+int32_t cpmk_quantize_rows_pair(int32_t batch0, int32_t n0, const void *mat0, void *scale_out0, void *q_out0, int32_t batch1, int32_t n1,
+                                const void *mat1, void *scale_out1, void *q_out1, int32_t m, cpmk_stream_t stream) {
+    int32_t rc = check_shape(batch0, n0, m);
+    if (rc) return rc;
+    rc = check_shape(batch1, n1, m);
+    if (rc) return rc;
+    bool done = false;
+    if ((int64_t)batch0 * n0 > 0 && (int64_t)batch1 * n1 > 0 && m > 0) {
+        CPMK_REQUIRE(mat0 && mat1 && scale_out0 && scale_out1 && q_out0 && q_out1, "null tensor pointer");
+        rc = launch_quant_rows_pair((int64_t)batch0 * n0, mat0, scale_out0, q_out0, (int64_t)batch1 * n1, mat1, scale_out1, q_out1, m,
+                                    as_stream(stream), &done);
+        if (rc) return rc;
+    }
+    if (done) return CPMK_OK;
+    // shapes the vector kernel does not take, or an empty operand: one call per operand
+    rc = launch_quant_rows<0>(batch0, n0, m, mat0, scale_out0, q_out0, as_stream(stream));
+    if (rc) return rc;
+    return launch_quant_rows<0>(batch1, n1, m, mat1, scale_out1, q_out1, as_stream(stream));
 }
 
 int32_t cpmk_gemm_calc_scale_transpose(int32_t batch, int32_t n, int32_t m, const void *inp, void *out, cpmk_stream_t stream) {

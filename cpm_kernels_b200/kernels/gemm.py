@@ -141,6 +141,14 @@ def gemm_quantize_cols(batch: int, n: int, m: int,
     cpmk.call("cpmk_quantize_cols", batch, n, m, mat, scale, out, stream_arg(stream))
 
 
+def gemm_quantize_rows_pair(batch0: int, n0: int, mat0: DevicePointer, scale0: DevicePointer, out0: DevicePointer,
+                            batch1: int, n1: int, mat1: DevicePointer, scale1: DevicePointer, out1: DevicePointer,
+                            m: int, stream: CUDAStream):
+    """gemm_quantize_rows on two operands with rows of the same length m, (batch0, n0, m) and (batch1, n1, m), in one
+    launch: the activations and the weight of a linear layer (torch/gemm.py:98-102 quantises them back to back)."""
+    cpmk.call("cpmk_quantize_rows_pair", batch0, n0, mat0, scale0, out0, batch1, n1, mat1, scale1, out1, m, stream_arg(stream))
+
+
 def gemm_int8_scale(m: int, k: int, n: int,
                     batchA: int, batchB: int,
                     aT: bool, bT: bool,

@@ -101,15 +101,21 @@ class FusedColumnParallelInt8Linear:
         return self._buffers[m_tokens]
 
     def forward(self, x: torch.Tensor, sync_before: bool = False) -> torch.Tensor:
-        from .torch.gemm import quantize
-        from .kernels import gemm_int8_scale_scatter
+        from .kernels import gemm_int8_scale_scatter, gemm_quantize_rows_pair
         assert x.ndim == 3 and x.size(0) == 1 and x.is_contiguous() and x.is_cuda
         m_tokens, k = x.size(1), x.size(2)
         n_local = self.weight.size(1)
         n_total = n_local * self.world
         y, handle = self._buffer(m_tokens)
-        scale_x, q_x = quantize(x, False)
-        scale_w, q_w = quantize(self.weight, False)
+        # activations and this rank's weight rows in one launch (both are stored with K contiguous)
+        dev = x.device
+        scale_x = torch.empty((1, m_tokens), dtype=torch.half, device=dev)
+        q_x = torch.empty(x.shape, dtype=torch.int8, device=dev)
+        scale_w = torch.empty((1, n_local), dtype=torch.half, device=dev)
+        q_w = torch.empty(self.weight.shape, dtype=torch.int8, device=dev)
+        with torch.cuda.device(dev):
+            gemm_quantize_rows_pair(1, m_tokens, x.data_ptr(), scale_x.data_ptr(), q_x.data_ptr(), 1, n_local, self.weight.data_ptr(),
+                                    scale_w.data_ptr(), q_w.data_ptr(), k, torch.cuda.current_stream().cuda_stream)
         if sync_before:
             handle.barrier(channel=0)
         dst = [int(handle.buffer_ptrs[p]) + 2 * self.rank * n_local for p in range(self.world)]

@@ -14,7 +14,7 @@ import torch
 
 from ..kernels import (gemm_calc_scale, gemm_calc_scale_transpose, gemm_round, gemm_round_transpose, gemm_scale, gemm_int8, gemm_fp16,
                        gemm_backward_round_scale, gemm_backward_scale_round, gemm_scale_x, gemm_scale_y,
-                       gemm_quantize_rows, gemm_quantize_cols, gemm_int8_scale, gemm_int8_scale_gelu)
+                       gemm_quantize_rows, gemm_quantize_rows_pair, gemm_quantize_cols, gemm_int8_scale, gemm_int8_scale_gelu)
 
 
 def _stream() -> int:
@@ -102,11 +102,16 @@ def _int8_forward(A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool, gelu: bo
     result = torch.empty((max(bA, bB), M, N), dtype=torch.float16, device=dev)
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream().cuda_stream
-        # A is quantised along K per row of the (M, K) operand: by columns of its storage when it is stored (K, M)
-        (gemm_quantize_cols if aT else gemm_quantize_rows)(bA, A.size(1), A.size(2), A.data_ptr(), scale_A.data_ptr(),
-                                                          quantized_A.data_ptr(), stream)
-        (gemm_quantize_rows if bT else gemm_quantize_cols)(bB, B.size(1), B.size(2), B.data_ptr(), scale_B.data_ptr(),
-                                                          quantized_B.data_ptr(), stream)
+        if not aT and bT:
+            # both operands are stored with K contiguous (activations (M, K), nn.Linear weights (N, K)): one launch for both
+            gemm_quantize_rows_pair(bA, A.size(1), A.data_ptr(), scale_A.data_ptr(), quantized_A.data_ptr(),
+                                    bB, B.size(1), B.data_ptr(), scale_B.data_ptr(), quantized_B.data_ptr(), K, stream)
+        else:
+            # A is quantised along K per row of the (M, K) operand: by columns of its storage when it is stored (K, M)
+            (gemm_quantize_cols if aT else gemm_quantize_rows)(bA, A.size(1), A.size(2), A.data_ptr(), scale_A.data_ptr(),
+                                                              quantized_A.data_ptr(), stream)
+            (gemm_quantize_rows if bT else gemm_quantize_cols)(bB, B.size(1), B.size(2), B.data_ptr(), scale_B.data_ptr(),
+                                                              quantized_B.data_ptr(), stream)
         # operands swapped (torch/gemm.py:45-52) so that the kernel-level (n, m) = (M, N) output is row-major C
         (gemm_int8_scale_gelu if gelu else gemm_int8_scale)(N, K, M, bB, bA, bT, aT, quantized_B.data_ptr(), quantized_A.data_ptr(),
                                                             scale_A.data_ptr(), scale_B.data_ptr(), bA == 1, bB == 1, result.data_ptr(), stream)

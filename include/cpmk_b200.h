@@ -70,6 +70,13 @@ int32_t cpmk_gemm_round_transpose(int32_t batch, int32_t n, int32_t m, const voi
  * the same tensor): one read of `mat`, writes both scale_out (batch, n) and q_out (batch, n, m). */
 int32_t cpmk_quantize_rows(int32_t batch, int32_t n, int32_t m, const void *mat, void *scale_out, void *q_out, cpmk_stream_t stream);
 
+/* cpmk_quantize_rows on two operands whose rows have the same length m, in one launch: (batch0, n0, m) and
+ * (batch1, n1, m), e.g. the activations and the weight of a linear layer, which cpm_kernels/torch/gemm.py:98-102
+ * quantises back to back.  Same results as two cpmk_quantize_rows calls. */
+int32_t cpmk_quantize_rows_pair(int32_t batch0, int32_t n0, const void *mat0, void *scale_out0, void *q_out0,
+                                int32_t batch1, int32_t n1, const void *mat1, void *scale_out1, void *q_out1,
+                                int32_t m, cpmk_stream_t stream);
+
 /* Fused gemm_calc_scale_transpose + gemm_round_transpose (same call sites, transposed operand):
  * writes scale_out (batch, m) and q_out (batch, n, m).  Uses the library workspace. */
 int32_t cpmk_quantize_cols(int32_t batch, int32_t n, int32_t m, const void *mat, void *scale_out, void *q_out, cpmk_stream_t stream);

@@ -192,3 +192,26 @@ def test_non_default_stream_and_second_device_state(G):
     st.synchronize()
     want_s = ql.gemm_calc_scale_transpose(xh)
     assert G.same_bits(s, want_s) and (G.host(q) == ql.gemm_round_transpose(xh, want_s)).all()
+
+
+@pytest.mark.parametrize("rows0,rows1,m", [((1, 64), (1, 96), 4096), ((2, 33), (1, 7), 512), ((1, 5), (3, 4), 20), ((1, 4096), (1, 1000), 10240),
+                                           ((1, 16), (1, 8), 128), ((1, 0), (1, 8), 64)])
+def test_two_operands_in_one_launch(G, rows0, rows1, m):
+    """cpmk_quantize_rows_pair gives what two cpmk_quantize_rows calls give (and so the oracle's bits)."""
+    import cpm_kernels_b200.kernels as ck
+    x0 = randn_fp16((rows0[0], rows0[1], m), 1, 1.0)
+    x1 = randn_fp16((rows1[0], rows1[1], m), 2, 0.02)
+    outs = []
+    for x in (x0, x1):
+        xd = x.cuda()
+        outs.append((xd, torch.full(x.shape[:2], 9.0, dtype=torch.half, device="cuda"), torch.full(x.shape, 9, dtype=torch.int8, device="cuda")))
+    (a, sa, qa), (b, sb, qb) = outs
+    ck.gemm_quantize_rows_pair(rows0[0], rows0[1], a.data_ptr(), sa.data_ptr(), qa.data_ptr(),
+                               rows1[0], rows1[1], b.data_ptr(), sb.data_ptr(), qb.data_ptr(), m, G.stream())
+    for x, s, q in ((x0, sa, qa), (x1, sb, qb)):
+        if x.numel() == 0:
+            continue
+        want_s = ql.gemm_calc_scale(np16(x))
+        assert G.same_bits(s, want_s)
+        assert (G.host(q) == ql.gemm_round(np16(x), want_s)).all()
+    G.assert_no_device_error()
