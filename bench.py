@@ -570,6 +570,16 @@ def measure_other_configs(cases, dev, gen, stream, peaks, xs=None, ws=None, iter
             sec = timed(fn, 3)
             other[name] = {"shape": "(1, 4096, 10240) fp16", "us": sec * 1e6, "GBps": bytes_per * nel / sec / 1e9,
                            "frac_of_hbm_peak": bytes_per * nel / sec / 1e9 / peaks["hbm_gbs"]}
+        del big, q8, o16
+        # layer norm -> affine -> column quantisation of a (batch 8, hidden 4096, seq 512) activation in one call;
+        # algorithmic traffic 3 bytes per element (fp16 in, int8 out); the reference's four kernels move 13
+        lx = [torch.randn((8, 4096, 512), generator=gen, device=dev).half() for _ in range(4)]
+        lw = (torch.randn((4096,), generator=gen, device=dev) * 0.1 + 1.0).half()
+        sec = timed(lambda j: ct.layernorm_quantize(lx[j], 1e-6, lw, None, False), 4)
+        nel = 8 * 4096 * 512
+        other["layernorm_quantize_cols"] = {"shape": "(8, 4096, 512) fp16, RMS form", "us": sec * 1e6, "GBps": 3 * nel / sec / 1e9,
+                                            "frac_of_hbm_peak": 3 * nel / sec / 1e9 / peaks["hbm_gbs"]}
+        del lx
     return other
 
 

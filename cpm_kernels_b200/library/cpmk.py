@@ -41,6 +41,7 @@ SIGNATURES = {
     "cpmk_gemm_int8_dequant": [_i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p, _p],
     "cpmk_gemm_int8_dequant_scatter": [_i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _i, _i, POINTER(c_void_p), ctypes.c_int64, _p],
     "cpmk_quantize_rows_pair": [_i, _i, _p, _p, _p, _i, _i, _p, _p, _p, _i, _p],
+    "cpmk_layernorm_quantize_cols": [_i, _i, _i, _p, ctypes.c_float, _i, _p, _p, _p, _p, _p],
     "cpmk_gelu_forward": [_i, _i, _p, _p, _p],
     "cpmk_gemm_int8_dequant_gelu": [_i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p, _p],
     "cpmk_gemm_fp16": [_i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p],

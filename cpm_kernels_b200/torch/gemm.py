@@ -234,3 +234,32 @@ def bmm_gelu(A: torch.Tensor, aT: bool, B: torch.Tensor, bT: bool) -> torch.Tens
     assert A.is_contiguous() and B.is_contiguous()
     assert A.dtype == torch.half and B.dtype == torch.half
     return _int8_forward(A, aT, B, bT, gelu=True)[0]
+
+
+def layernorm_quantize(x: torch.Tensor, eps: float, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, rd_mean: bool = True):
+    """Layer norm of ``x`` (batch, hidden, seq) over the hidden axis, times ``weight`` (plus ``bias``), quantised per
+    (batch, seq) column: ``(scale (batch, seq) fp16, codes (batch, hidden, seq) int8)``, the operand B that
+    ``bmm(W, False, layernorm(x), False, int8=True)`` would quantise, without the fp16 tensors in between
+    (cpm_kernels/torch/layernorm.py:8-30 and torch/gemm.py:98-102 in one call; same bits).  Forward only."""
+    from ..kernels import layernorm_quantize_cols
+    assert x.is_cuda and x.is_contiguous() and x.ndim == 3 and x.dtype == torch.half
+    assert weight.is_cuda and weight.is_contiguous() and weight.ndim == 1 and weight.dtype == torch.half and weight.numel() == x.size(1)
+    if bias is not None:
+        assert bias.is_cuda and bias.is_contiguous() and bias.dtype == torch.half and bias.numel() == x.size(1)
+    scale = torch.empty((x.size(0), x.size(2)), dtype=torch.half, device=x.device)
+    codes = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    with torch.cuda.device(x.device):
+        layernorm_quantize_cols(x.size(0), x.size(1), x.size(2), x.data_ptr(), eps, rd_mean, weight.data_ptr(),
+                                bias.data_ptr() if bias is not None else 0, scale.data_ptr(), codes.data_ptr(),
+                                torch.cuda.current_stream().cuda_stream)
+    return scale, codes
+
+
+def bmm_quantized_b(A: torch.Tensor, aT: bool, scale_B: torch.Tensor, quantized_B: torch.Tensor, bT: bool) -> torch.Tensor:
+    """``bmm(A, aT, B, bT, int8=True)`` for an operand B that is already quantised along K (``layernorm_quantize``
+    gives it for bT = False): A is quantised here, then the GEMM with its dequantising epilogue.  Forward only."""
+    assert A.ndim == 3 and quantized_B.ndim == 3
+    assert A.is_cuda and A.is_contiguous() and A.dtype == torch.half
+    assert quantized_B.is_cuda and quantized_B.is_contiguous() and quantized_B.dtype == torch.int8
+    scale_A, quantized_A = quantize(A, aT)
+    return gemm_and_scale(quantized_A, scale_A, quantized_B, scale_B, aT, bT)

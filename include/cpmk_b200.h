@@ -130,6 +130,18 @@ int32_t cpmk_gemm_int8_dequant_scatter(int32_t m, int32_t k, int32_t n, int32_t 
                                        int32_t broad_cast_x, int32_t broad_cast_y, int32_t n_dst, void *const *dst,
                                        int64_t dst_row_pitch, cpmk_stream_t stream);
 
+/* Layer norm over the MIDDLE axis of mat (batch, n, m) fp16, per-row affine, and quantisation along that same axis,
+ * without storing the intermediate tensors: what cpm_kernels runs as four kernels between a layer norm and the int8
+ * linear that follows it in the (batch, hidden, seq) layout --
+ *   cu_layernorm_forward(eps, rd_mean)                      cuda/layernorm.cu:6-71,  kernels/layernorm.py:18-38
+ *   cu_arith_ln_mul (beta == NULL) / cu_arith_ln_mul_add    cuda/arith.cu:97-127,    kernels/arith.py:134-215
+ *   cu_gemm_calc_scale_transpose, cu_gemm_round_transpose   cuda/gemm.cu:22-33, 79-98
+ * (torch/layernorm.py:8-30 followed by torch/gemm.py:98-102 for an operand B with bT = False).
+ * alpha, beta: (n) fp16; scale_out (batch, m) fp16; q_out (batch, n, m) int8.  rd_mean = 0 is the RMS form.
+ * Same bits as the chain (the statistics are summed in the reference's order).  m must be a multiple of 8. */
+int32_t cpmk_layernorm_quantize_cols(int32_t batch, int32_t n, int32_t m, const void *mat, float eps, int32_t rd_mean,
+                                     const void *alpha, const void *beta, void *scale_out, void *q_out, cpmk_stream_t stream);
+
 /* out[b, i] = gelu(mat[b, i]) on fp16, tanh form: replaces cpm_kernels/kernels/gelu.py:14-31 gelu_forward /
  * gelu_inplace_forward (cuda/gelu.cu:6-17); `mat` is (batch, n) contiguous and out may equal mat.  Same bits as the
  * reference's kernel for every fp16 input.  Large inputs use a 65536-entry table that the first call on a device

@@ -202,6 +202,79 @@ def gelu_forward(x: np.ndarray) -> np.ndarray:
     return bits.view(np.float16)
 
 
+def _shuffle_down_sum32(v: np.ndarray) -> np.ndarray:
+    """Lane 0 of the reference's warpReduceSum (cuda/includes/reduce.cuh:6-10) over the last axis (length 32), in
+    binary32: x += shfl_down(x, 16), then 8, 4, 2, 1."""
+    a = v[..., :16] + v[..., 16:32]
+    b = a[..., :8] + a[..., 8:16]
+    c = b[..., :4] + b[..., 4:8]
+    d = c[..., :2] + c[..., 2:4]
+    return d[..., 0] + d[..., 1]
+
+
+def _layernorm_column_sum(v: np.ndarray) -> np.ndarray:
+    """The reference's nested summation of one quantity over the rows (cuda/layernorm.cu:19-45): v is (batch, n, m)
+    binary32; rows are taken in chunks of 1024, each chunk as 32 blocks of 32 rows; a block's 32 rows and a chunk's 32
+    block sums are each combined by the shuffle tree above (missing rows / blocks count as zero), and the chunk sums are
+    accumulated in order."""
+    b, n, m = v.shape
+    n_pad = (n + 1023) // 1024 * 1024
+    vp = np.zeros((b, n_pad, m), np.float32)
+    vp[:, :n, :] = v
+    blocks = vp.reshape(b, n_pad // 1024, 32, 32, m)                  # (batch, chunk, block, row lane, column)
+    block_sums = _shuffle_down_sum32(np.moveaxis(blocks, 3, -1))       # (batch, chunk, block, column)
+    chunk_sums = _shuffle_down_sum32(np.moveaxis(block_sums, 2, -1))   # (batch, chunk, column)
+    total = np.zeros((b, m), np.float32)
+    for c in range(chunk_sums.shape[1]):
+        total = total + chunk_sums[:, c, :]
+    return total
+
+
+def layernorm_forward(x: np.ndarray, eps: float, rd_mean: bool) -> np.ndarray:
+    """cuda/layernorm.cu:6-71 cu_layernorm_forward: x (batch, n, m) fp16, normalised over the MIDDLE axis n per
+    (batch, column).  mean = S1 / n, var = S2 / n - mean * mean (one fused multiply-add, as nvcc contracts it),
+    rstd = rsqrtf(var + eps), out = half(((float)x - mean) * rstd)  [rd_mean]  or  half((float)x * rstd).
+    rsqrtf is taken as correctly rounded here; the device's approximation differs from that in the last place for
+    some arguments, which moves a few outputs by one fp16 step (tests/test_oracle_golden.py states how many)."""
+    assert x.dtype == np.float16 and x.ndim == 3
+    n = x.shape[1]
+    xf = x.astype(np.float32)
+    with np.errstate(all="ignore"):
+        s2 = _layernorm_column_sum(xf * xf) / np.float32(n)
+        if rd_mean:
+            mean = _layernorm_column_sum(xf) / np.float32(n)
+            var = (s2.astype(np.float64) - mean.astype(np.float64) * mean.astype(np.float64)).astype(np.float32)   # fma
+        else:
+            mean = np.zeros_like(s2)
+            var = s2
+        rstd = (1.0 / np.sqrt((var + np.float32(eps)).astype(np.float64))).astype(np.float32)
+        if rd_mean:
+            y = (xf - mean[:, None, :]) * rstd[:, None, :]
+        else:
+            y = xf * rstd[:, None, :]
+        return y.astype(np.float16)
+
+
+def arith_ln_mul(x: np.ndarray, alpha: np.ndarray) -> np.ndarray:
+    """cuda/arith.cu:115-127: out = __hmul2(x, alpha[row]) -- one rounding to fp16."""
+    return (x.astype(np.float32) * alpha.astype(np.float32)[None, :, None]).astype(np.float16)
+
+
+def arith_ln_mul_add(x: np.ndarray, alpha: np.ndarray, beta: np.ndarray) -> np.ndarray:
+    """cuda/arith.cu:97-112: out = __hfma2(x, alpha[row], beta[row]) -- fused, one rounding to fp16."""
+    prod = x.astype(np.float64) * alpha.astype(np.float64)[None, :, None]
+    return (prod + beta.astype(np.float64)[None, :, None]).astype(np.float16)
+
+
+def layernorm_quantize_cols(x: np.ndarray, eps: float, rd_mean: bool, alpha: np.ndarray, beta=None):
+    """The chain layer norm -> affine -> column quantisation that feeds a CPM-layout linear
+    (torch/layernorm.py:8-30, torch/gemm.py:98-102): returns (scale (batch, m) fp16, codes (batch, n, m) int8)."""
+    y = layernorm_forward(x, eps, rd_mean)
+    y = arith_ln_mul_add(y, alpha, beta) if beta is not None else arith_ln_mul(y, alpha)
+    scale = gemm_calc_scale_transpose(y)
+    return scale, gemm_round_transpose(y, scale)
+
+
 def bmm_int8(A: np.ndarray, aT: bool, B: np.ndarray, bT: bool):
     """cpm_kernels/torch/gemm.py:86-113 GEMMInt8.forward, restated with the functions above.
     A (bA, M, K) [or (bA, K, M) if aT], B (bB, K, N) [or (bB, N, K) if bT], fp16.

@@ -73,10 +73,10 @@ class ReferenceKernels:
         torch.zeros(1, device="cuda")       # make the primary context current
         self.drv = _Driver()
         self._fns = {}
-        for name in ("gemm", "gemv", "gelu"):
+        for name in ("gemm", "gemv", "gelu", "layernorm", "arith"):
             path = os.path.join(fatbin_dir, name + ".fatbin")
-            if name == "gelu" and not os.path.exists(path):
-                continue                                  # only needed by gelu_forward
+            if name not in ("gemm", "gemv") and not os.path.exists(path):
+                continue                                  # only needed by the functions of that file
             with open(path, "rb") as f:
                 setattr(self, "_mod_" + name, self.drv.load(f.read()))
 
@@ -181,6 +181,37 @@ class ReferenceKernels:
         threads = min(_round_up(n, 32), 1024)
         self.drv.launch(self._fn("gelu", "cu_gelu_forward"), (b, _round_up(n, threads) // threads, 1), (threads, 1, 1), self._stream(),
                         [self._i(b), self._i(n), self._p(mat), self._p(out)])
+        return out
+
+    # ---- cpm_kernels/kernels/layernorm.py, arith.py ----------------------------------------------
+    def layernorm_forward(self, mat: torch.Tensor, eps: float, rd_mean: bool) -> torch.Tensor:
+        """kernels/layernorm.py:18-38: grid (batch, round_up(m, 32) / 32), block (32, 32)."""
+        b, n, m = mat.shape
+        out = torch.empty_like(mat)
+        self.drv.launch(self._fn("layernorm", "cu_layernorm_forward"), (b, _round_up(m, 32) // 32, 1), (32, 32, 1), self._stream(),
+                        [self._i(b), self._i(n), self._i(m), self._p(mat), self._p(out), ctypes.c_float(eps), ctypes.c_bool(rd_mean)])
+        return out
+
+    def arith_ln_mul(self, x: torch.Tensor, alpha: torch.Tensor) -> torch.Tensor:
+        """kernels/arith.py:188-215: m halved (half2 elements); threads = min(round_up(m, 32), 1024); grid (batch, n, round_up(m, threads) / threads)."""
+        b, n, m = x.shape
+        assert m % 2 == 0
+        out = torch.empty_like(x)
+        m2 = m // 2
+        threads = min(_round_up(m2, 32), 1024)
+        self.drv.launch(self._fn("arith", "cu_arith_ln_mul"), (b, n, _round_up(m2, threads) // threads), (threads, 1, 1), self._stream(),
+                        [ctypes.c_int64(b), ctypes.c_int64(n), ctypes.c_int64(m2), self._p(x), self._p(alpha), self._p(out)])
+        return out
+
+    def arith_ln_mul_add(self, x: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
+        """kernels/arith.py:134-161: as arith_ln_mul with a per-row addend."""
+        b, n, m = x.shape
+        assert m % 2 == 0
+        out = torch.empty_like(x)
+        m2 = m // 2
+        threads = min(_round_up(m2, 32), 1024)
+        self.drv.launch(self._fn("arith", "cu_arith_ln_mul_add"), (b, n, _round_up(m2, threads) // threads), (threads, 1, 1), self._stream(),
+                        [ctypes.c_int64(b), ctypes.c_int64(n), ctypes.c_int64(m2), self._p(x), self._p(alpha), self._p(beta), self._p(out)])
         return out
 
     # ---- cpm_kernels/kernels/gemv.py -------------------------------------------------------------

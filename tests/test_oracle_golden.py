@@ -95,3 +95,29 @@ def test_gelu_restatements_match_the_reference_on_every_fp16_value():
     x = np.arange(65536, dtype=np.uint16).view(np.float16)
     assert (ql.gelu_forward(x).view(np.uint16) == table).all()
     assert (ql.COracle().gelu_forward(x).view(np.uint16) == table).all()
+
+
+def test_layernorm_chain_restatement_matches_the_reference():
+    """tests/golden/reference_layernorm_sm100.npz: the reference's layer norm -> affine -> column quantisation chain.
+    The restatement reproduces the affine step, the scales and the codes exactly; the normalised tensor itself
+    differs in at most a handful of elements by one fp16 step (the device's rsqrtf is not correctly rounded)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_layernorm_sm100.npz"))
+    cases = {"mean_bias": (1e-5, True), "rms": (1e-6, False), "ragged": (1e-5, True), "hidden4096": (1e-6, False),
+             "ragged_rms_bias": (1e-5, False)}
+    ln_mismatches = 0
+    for name, (eps, rd_mean) in cases.items():
+        x = g[name + "_x"].view(np.float16)
+        alpha = g[name + "_alpha"].view(np.float16)
+        beta = g[name + "_beta"].view(np.float16) if name + "_beta" in g else None
+        ln = ql.layernorm_forward(x, eps, rd_mean)
+        want_ln = g[name + "_ln"].view(np.float16)
+        differ = ln.view(np.uint16) != want_ln.view(np.uint16)
+        ln_mismatches += int(differ.sum())
+        assert np.abs(ln[differ].view(np.int16).astype(np.int32) - want_ln[differ].view(np.int16).astype(np.int32)).max(initial=0) <= 1
+        aff = ql.arith_ln_mul_add(want_ln, alpha, beta) if beta is not None else ql.arith_ln_mul(want_ln, alpha)
+        assert (aff.view(np.uint16) == g[name + "_affine"]).all()
+        scale, codes = ql.layernorm_quantize_cols(x, eps, rd_mean, alpha, beta)
+        assert (scale.view(np.uint16) == g[name + "_scale"]).all()
+        assert (codes == g[name + "_codes"]).all()
+    assert ln_mismatches <= 3
