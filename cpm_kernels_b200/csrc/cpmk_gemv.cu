@@ -136,22 +136,32 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int
     const int groups = (int)((r1 - r0 + kStreamRows - 1) / kStreamRows);
 
     if (warp == kStreamRows) {
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            bool alive = true;
-            for (int g = 0; alive && g < groups; ++g) {
-                const int64_t row = r0 + (int64_t)g * kStreamRows;
-                const int n = (int)((r1 - row) < kStreamRows ? (r1 - row) : kStreamRows);
-                for (int c = 0; c < chunks; ++c) {
-                    if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrGemvProducer)) { alive = false; break; }
-                    const int c0 = c * chunk;
-                    const uint32_t bytes = (uint32_t)((dim_in - c0) < chunk ? (dim_in - c0) : chunk) * 2u;
-                    mbar_expect_tx(full_bar + 8 * stage, (uint32_t)n * bytes);
-                    for (int i = 0; i < n; ++i)
-                        bulk_load_1d(ring_base + stage * stage_bytes + (uint32_t)i * slot_bytes, mat + (row + i) * (int64_t)dim_in + c0, bytes,
+        // Producer warp.  A single thread issuing eight copies one after another takes over a microsecond per stage
+        // (measured), which delays the first stage and barely keeps up afterwards: whole rows of a group are
+        // contiguous in memory and in the ring, so they travel as ONE copy; chunks of long rows are issued by one
+        // lane each.
+        uint32_t stage = 0, phase = 0;
+        bool alive = true;
+        for (int g = 0; alive && g < groups; ++g) {
+            const int64_t row = r0 + (int64_t)g * kStreamRows;
+            const int n = (int)((r1 - row) < kStreamRows ? (r1 - row) : kStreamRows);
+            for (int c = 0; c < chunks; ++c) {
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrGemvProducer) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { alive = false; break; }
+                const int c0 = c * chunk;
+                const uint32_t bytes = (uint32_t)((dim_in - c0) < chunk ? (dim_in - c0) : chunk) * 2u;
+                if (lane == 0) mbar_expect_tx(full_bar + 8 * stage, (uint32_t)n * bytes);
+                if (chunks == 1) {
+                    if (lane == 0) bulk_load_1d(ring_base + stage * stage_bytes, mat + row * (int64_t)dim_in, (uint32_t)n * bytes, full_bar + 8 * stage);
+                } else {
+                    __syncwarp();
+                    if (lane < n)
+                        bulk_load_1d(ring_base + stage * stage_bytes + (uint32_t)lane * slot_bytes, mat + (row + lane) * (int64_t)dim_in + c0, bytes,
                                      full_bar + 8 * stage);
-                    if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
                 }
+                if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
             }
         }
     } else {
@@ -245,15 +255,20 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_transpose_stream_kerne
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 
     if (warp == kStreamRows) {
-        if (lane == 0) {
+        {
+            // one lane per row segment: a single thread issuing the eight copies of a stage takes over a microsecond
             uint32_t stage = 0, phase = 0;
             for (int g = 0; g < groups; ++g) {
-                if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrGemvProducer)) break;
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrGemvProducer) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
                 const int row = i0 + g * kStreamRows;
                 const int n = (i1 - row) < kStreamRows ? (i1 - row) : kStreamRows;
-                mbar_expect_tx(full_bar + 8 * stage, (uint32_t)n * seg_bytes);
-                for (int r = 0; r < n; ++r)
-                    bulk_load_1d(ring_base + stage * kTsStageBytes + (uint32_t)r * (kTsCols * 2), base + (int64_t)(row + r) * dim_out, seg_bytes,
+                if (lane == 0) mbar_expect_tx(full_bar + 8 * stage, (uint32_t)n * seg_bytes);
+                __syncwarp();
+                if (lane < n)
+                    bulk_load_1d(ring_base + stage * kTsStageBytes + (uint32_t)lane * (kTsCols * 2), base + (int64_t)(row + lane) * dim_out, seg_bytes,
                                  full_bar + 8 * stage);
                 if (++stage == kTsStages) { stage = 0; phase ^= 1u; }
             }

@@ -339,19 +339,23 @@ __global__ void __launch_bounds__(kCsThreads, 2) quant_cols_stream_kernel(int32_
     __syncthreads();
 
     if (warp == kCsRows) {
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            for (int gi = 0; gi < groups; ++gi) {
-                const int g = PASS == 0 ? gi : groups - 1 - gi;
-                if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrColqProducer)) break;
-                const int row = i0 + g * kCsRows;
-                const int nr = (i1 - row) < kCsRows ? (i1 - row) : kCsRows;
-                mbar_expect_tx(full_bar + 8 * stage, (uint32_t)nr * seg_bytes);
-                for (int r = 0; r < nr; ++r)
-                    bulk_load_1d(ring_base + stage * kCsStageBytes + (uint32_t)r * (kCsCols * 2), base + (int64_t)(row + r) * m, seg_bytes,
-                                 full_bar + 8 * stage);
-                if (++stage == kCsStages) { stage = 0; phase ^= 1u; }
-            }
+        // producer warp, one lane per row segment: a single thread issuing the eight copies of a stage one after another
+        // took ~2600 cycles per stage (measured), about as long as the consumers need for it
+        uint32_t stage = 0, phase = 0;
+        for (int gi = 0; gi < groups; ++gi) {
+            const int g = PASS == 0 ? gi : groups - 1 - gi;
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrColqProducer) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            const int row = i0 + g * kCsRows;
+            const int nr = (i1 - row) < kCsRows ? (i1 - row) : kCsRows;
+            if (lane == 0) mbar_expect_tx(full_bar + 8 * stage, (uint32_t)nr * seg_bytes);
+            __syncwarp();
+            if (lane < nr)
+                bulk_load_1d(ring_base + stage * kCsStageBytes + (uint32_t)lane * (kCsCols * 2), base + (int64_t)(row + lane) * m, seg_bytes,
+                             full_bar + 8 * stage);
+            if (++stage == kCsStages) { stage = 0; phase ^= 1u; }
         }
     } else {
         const int t = threadIdx.x;                           // 0..255: columns c0 + 8 t .. + 7
