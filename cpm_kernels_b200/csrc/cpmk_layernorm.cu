@@ -18,13 +18,16 @@ namespace cpmk {
 namespace {
 
 constexpr int kLnBlock = 256;
-constexpr int kLnStripCols = 64;        // columns per block: 128-byte row segments
+constexpr int kLnStripCols = 64;        // pass A: columns per block (128-byte row segments)
+constexpr int kLnWideCols = 512;        // passes B and C: columns per block (1 KiB row segments: 64 threads x 8 columns)
+constexpr int kLnRowLanes = kLnBlock / (kLnWideCols / 8);   // 4 row lanes per block
 constexpr int kLnChunkRows = 1024;      // the reference's outer loop step (WARP_SZ * WARP_SZ)
 
-// lane 0 of x += shfl_down(x, 16), 8, 4, 2, 1 over v[0..31], for two columns at once
-__device__ __forceinline__ float2 tree_sum32(float2 (&v)[32]) {
+// lane 0 of x += shfl_down(x, 16), 8, 4, 2, 1 over 32 values, for two columns at once; v holds the 16 sums of the
+// first level (rows l and l + 16)
+__device__ __forceinline__ float2 tree_sum16(float2 (&v)[16]) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
+    for (int o = 8; o > 0; o >>= 1) {
 #pragma unroll
         for (int l = 0; l < o; ++l) {
             v[l].x = __fadd_rn(v[l].x, v[l + o].x);
@@ -35,10 +38,11 @@ __device__ __forceinline__ float2 tree_sum32(float2 (&v)[32]) {
 }
 
 // Pass A: the sums of x (if RD_MEAN) and of x * x over one chunk of 1024 rows for a strip of 64 columns.
-// Thread (cp, g): column pair cp of the strip, blocks g, g + 8, g + 16, g + 24 of the chunk's 32 row blocks.
+// Thread (cp, g): column pair cp of the strip, row block g of the chunk's 32 blocks of 32 rows.
 // sums layout: [quantity (0: x, 1: x*x)][batch][chunk][m] floats.
+constexpr int kLnSumsBlock = 1024;      // pass A: 32 column pairs x 32 row blocks, one 32-row block per thread
 template <bool RD_MEAN>
-__global__ void __launch_bounds__(kLnBlock) ln_chunk_sums_kernel(int32_t n, int32_t m, int32_t chunks, const __half *__restrict__ mat,
+__global__ void __launch_bounds__(kLnSumsBlock) ln_chunk_sums_kernel(int32_t n, int32_t m, int32_t chunks, const __half *__restrict__ mat,
                                                                  float *__restrict__ sums) {
     __shared__ float block_sums[2][32][kLnStripCols];
     const int cp = threadIdx.x & 31, g = threadIdx.x >> 5;
@@ -46,25 +50,30 @@ __global__ void __launch_bounds__(kLnBlock) ln_chunk_sums_kernel(int32_t n, int3
     const int col = blockIdx.x * kLnStripCols + 2 * cp;
     const bool col_ok = col < m;                                   // m is even: both columns of the pair are in or out
     const __half *base = mat + (int64_t)b * n * m + col;
-    for (int blk = g; blk < 32; blk += 8) {
+    {
+        const int blk = g;
         const int r0 = chunk * kLnChunkRows + blk * 32;
         __half2 h[32];
 #pragma unroll
         for (int l = 0; l < 32; ++l)
             h[l] = (col_ok && r0 + l < n) ? __ldg(reinterpret_cast<const __half2 *>(base + (int64_t)(r0 + l) * m)) : __float2half2_rn(0.f);
-        float2 v[32];
+        // the first level of the tree pairs rows l and l + 16: formed as the values are converted, 16 partial sums live
+        float2 v[16];
 #pragma unroll
-        for (int l = 0; l < 32; ++l) {
-            const float2 f = __half22float2(h[l]);
-            v[l] = make_float2(__fmul_rn(f.x, f.x), __fmul_rn(f.y, f.y));
+        for (int l = 0; l < 16; ++l) {
+            const float2 f = __half22float2(h[l]), g2 = __half22float2(h[l + 16]);
+            v[l] = make_float2(__fadd_rn(__fmul_rn(f.x, f.x), __fmul_rn(g2.x, g2.x)), __fadd_rn(__fmul_rn(f.y, f.y), __fmul_rn(g2.y, g2.y)));
         }
-        const float2 s2 = tree_sum32(v);
+        const float2 s2 = tree_sum16(v);
         block_sums[1][blk][2 * cp] = s2.x;
         block_sums[1][blk][2 * cp + 1] = s2.y;
         if (RD_MEAN) {
 #pragma unroll
-            for (int l = 0; l < 32; ++l) v[l] = __half22float2(h[l]);
-            const float2 s1 = tree_sum32(v);
+            for (int l = 0; l < 16; ++l) {
+                const float2 f = __half22float2(h[l]), g2 = __half22float2(h[l + 16]);
+                v[l] = make_float2(__fadd_rn(f.x, g2.x), __fadd_rn(f.y, g2.y));
+            }
+            const float2 s1 = tree_sum16(v);
             block_sums[0][blk][2 * cp] = s1.x;
             block_sums[0][blk][2 * cp + 1] = s1.y;
         }
@@ -98,13 +107,14 @@ struct LnParams {
 };
 
 // Passes B (PASS 0: column maxima of |y| over a row range) and C (PASS 1: scales and codes).
-// Thread (t8, rl): columns c0 + 8 t8 .. + 7 of the strip, rows rl, rl + 32, ... of the block's row range.
+// Thread (t8, rl): columns c0 + 8 t8 .. + 7 of the 512-column strip, rows rl, rl + 4, ... of the block's row range
+// (whole 1 KiB row segments per block: narrow strips leave most of every DRAM page to other blocks at other times).
 template <int PASS, bool RD_MEAN, bool BIAS>
-__global__ void __launch_bounds__(kLnBlock) ln_quant_kernel(const LnParams p) {
-    __shared__ __align__(16) __half lane_max[32][kLnStripCols];
-    const int t8 = threadIdx.x & 7, rl = threadIdx.x >> 3;
+__global__ void __launch_bounds__(kLnBlock, 3) ln_quant_kernel(const LnParams p) {
+    __shared__ __align__(16) __half lane_max[kLnRowLanes][kLnWideCols];
+    const int t8 = threadIdx.x & (kLnWideCols / 8 - 1), rl = threadIdx.x / (kLnWideCols / 8);
     const int b = blockIdx.z, split = blockIdx.y, batch = gridDim.z;
-    const int col = blockIdx.x * kLnStripCols + 8 * t8;
+    const int col = blockIdx.x * kLnWideCols + 8 * t8;
     const bool col_ok = col < p.m;                                 // m is a multiple of 8 on this path
     const int r_begin = split * p.rows_per_split;
     const int r_end = min(p.n, r_begin + p.rows_per_split);
@@ -169,20 +179,31 @@ __global__ void __launch_bounds__(kLnBlock) ln_quant_kernel(const LnParams p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) m2[j] = __float2half2_rn(0.f);
         if (col_ok) {
-            for (int r = r_begin + rl; r < r_end; r += 32) {
-                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(base + (int64_t)r * p.m));
-                __half2 y[4];
-                transform(v, r, y);
+            // four rows per iteration, loads first: one 16-byte load in flight per thread does not cover the latency
+            for (int r0 = r_begin + rl; r0 < r_end; r0 += 4 * kLnRowLanes) {
+                uint4 v[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) m2[j] = __hmax2(__habs2(y[j]), m2[j]);
+                for (int u = 0; u < 4; ++u)
+                    v[u] = r0 + kLnRowLanes * u < r_end ? __ldg(reinterpret_cast<const uint4 *>(base + (int64_t)(r0 + kLnRowLanes * u) * p.m))
+                                                        : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (r0 + kLnRowLanes * u < r_end) {
+                        __half2 y[4];
+                        transform(v[u], r0 + kLnRowLanes * u, y);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) m2[j] = __hmax2(__habs2(y[j]), m2[j]);
+                    }
+                }
             }
         }
         *reinterpret_cast<uint4 *>(&lane_max[rl][8 * t8]) = *reinterpret_cast<const uint4 *>(m2);
         __syncthreads();
-        if (threadIdx.x < kLnStripCols) {
-            __half mx = lane_max[0][threadIdx.x];
-            for (int l = 1; l < 32; ++l) mx = __hmax(mx, lane_max[l][threadIdx.x]);
-            const int gc = blockIdx.x * kLnStripCols + threadIdx.x;
+        for (int c = threadIdx.x; c < kLnWideCols; c += kLnBlock) {
+            __half mx = lane_max[0][c];
+#pragma unroll
+            for (int l = 1; l < kLnRowLanes; ++l) mx = __hmax(mx, lane_max[l][c]);
+            const int gc = blockIdx.x * kLnWideCols + c;
             if (gc < p.m) p.amax_partial[((int64_t)split * batch + b) * p.m + gc] = mx;
         }
         return;
@@ -216,8 +237,17 @@ __global__ void __launch_bounds__(kLnBlock) ln_quant_kernel(const LnParams p) {
     if (split == 0 && rl == 0) *reinterpret_cast<uint4 *>(p.scale + (int64_t)b * p.m + col) = *reinterpret_cast<const uint4 *>(sh);
     int8_t *obase = p.out + (int64_t)b * p.n * p.m + col;
     const float2 magic = make_float2(CPMK_ROUND_MAGIC, CPMK_ROUND_MAGIC);
-    for (int r = r_begin + rl; r < r_end; r += 32) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(base + (int64_t)r * p.m));
+    for (int r0 = r_begin + rl; r0 < r_end; r0 += 2 * kLnRowLanes) {
+      uint4 vv[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+          vv[u] = r0 + kLnRowLanes * u < r_end ? __ldg(reinterpret_cast<const uint4 *>(base + (int64_t)(r0 + kLnRowLanes * u) * p.m))
+                                               : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int r = r0 + kLnRowLanes * u;
+        if (r >= r_end) break;
+        const uint4 v = vv[u];
         __half2 y[4];
         transform(v, r, y);
         uint32_t bits[8];
@@ -245,12 +275,13 @@ __global__ void __launch_bounds__(kLnBlock) ln_quant_kernel(const LnParams p) {
         q.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
         q.y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
         *reinterpret_cast<uint2 *>(obase + (int64_t)r * p.m) = q;
+      }
     }
 }
 
 template <bool RD_MEAN, bool BIAS>
 int32_t launch_ln_quant(const LnParams &p, int32_t batch, const dim3 &grid_a, const dim3 &grid_bc, float *sums, cudaStream_t stream) {
-    ln_chunk_sums_kernel<RD_MEAN><<<grid_a, kLnBlock, 0, stream>>>(p.n, p.m, p.chunks, p.mat, sums);
+    ln_chunk_sums_kernel<RD_MEAN><<<grid_a, kLnSumsBlock, 0, stream>>>(p.n, p.m, p.chunks, p.mat, sums);
     CPMK_LAUNCH_CHECK();
     ln_quant_kernel<0, RD_MEAN, BIAS><<<grid_bc, kLnBlock, 0, stream>>>(p);
     CPMK_LAUNCH_CHECK();
@@ -290,9 +321,11 @@ extern "C" int32_t cpmk_layernorm_quantize_cols(int32_t batch, int32_t n, int32_
     p.mat = static_cast<const __half *>(mat);
     p.alpha = static_cast<const __half *>(alpha);
     p.beta = static_cast<const __half *>(beta);
-    const int strips = (m + kLnStripCols - 1) / kLnStripCols;
-    // row ranges: enough blocks for ~4 per SM, at least 32 rows each
-    int64_t splits = ((int64_t)info.sm_count * 4) / ((int64_t)strips * batch);
+    const int strips = (m + kLnStripCols - 1) / kLnStripCols;            // pass A
+    const int wide_strips = (m + kLnWideCols - 1) / kLnWideCols;        // passes B and C
+    // row ranges: about two blocks per SM, so that all of them are resident at once (three fit; a second, nearly empty
+    // wave would double the time), at least 32 rows each
+    int64_t splits = ((int64_t)info.sm_count * 2) / ((int64_t)wide_strips * batch);
     const int64_t by_rows = (n + 31) / 32;
     if (splits > by_rows) splits = by_rows;
     if (splits > 65535) splits = 65535;
@@ -309,7 +342,7 @@ extern "C" int32_t cpmk_layernorm_quantize_cols(int32_t batch, int32_t n, int32_
     p.amax_partial = reinterpret_cast<__half *>(ws.scratch() + ((sums_bytes + 255) / 256) * 256);
     p.scale = static_cast<__half *>(scale_out);
     p.out = static_cast<int8_t *>(q_out);
-    const dim3 grid_a(strips, p.chunks, batch), grid_bc(strips, p.splits, batch);
+    const dim3 grid_a(strips, p.chunks, batch), grid_bc(wide_strips, p.splits, batch);
     CPMK_REQUIRE(p.chunks <= 65535, "n = %d is too large", n);
     if (rd_mean) return beta ? launch_ln_quant<true, true>(p, batch, grid_a, grid_bc, sums, stream) : launch_ln_quant<true, false>(p, batch, grid_a, grid_bc, sums, stream);
     return beta ? launch_ln_quant<false, true>(p, batch, grid_a, grid_bc, sums, stream) : launch_ln_quant<false, false>(p, batch, grid_a, grid_bc, sums, stream);
