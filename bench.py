@@ -240,7 +240,7 @@ def run_ours(args) -> None:
             # (the scatter GEMM's persistent grid leaves part of the SMs free for that: CPMK_GEMM_SM_MARGIN).
             if fused_two_streams:
                 comm_stream.wait_stream(stream)
-                os.environ["CPMK_GEMM_SM_MARGIN"] = fused_margin      # read by the library at each launch
+                cpmk.set_gemm_sm_margin(int(fused_margin))
             for i, (fl, x) in enumerate(zip(fused_layers, xs)):
                 if fused_two_streams and (i & 1):
                     with torch.cuda.stream(comm_stream):
@@ -249,7 +249,7 @@ def run_ours(args) -> None:
                     results.append(fl(x))
             if fused_two_streams:
                 stream.wait_stream(comm_stream)
-                os.environ.pop("CPMK_GEMM_SM_MARGIN", None)
+                cpmk.set_gemm_sm_margin(-1)
             return results
         for i, (x, w) in enumerate(zip(xs, ws)):
             if record_gemm:

@@ -17,6 +17,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "cpmk_common.cuh"
@@ -987,6 +988,7 @@ bool encode_output_raw(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int64_
     return r == CUDA_SUCCESS;
 }
 
+std::atomic<int> g_sm_margin{-1};
 thread_local int32_t g_last_path = 0;
 thread_local int32_t g_last_variant = 0;
 
@@ -1117,10 +1119,13 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
         // CPMK_GEMM_SM_MARGIN=n leaves n SMs free of the persistent GEMM grid, so that kernels of a concurrent stream
         // (the collective that gathers output slices across GPUs) find room to run beside it
         int max_pairs = g_max_pairs[info.device & 63];
-        if (const char *mg = getenv("CPMK_GEMM_SM_MARGIN")) {
-            const int margin_pairs = (atoi(mg) + 1) / 2;
-            if (margin_pairs > 0 && max_pairs - margin_pairs >= 8) max_pairs -= margin_pairs;
+        int margin = g_sm_margin.load(std::memory_order_relaxed);      // cpmk_set_gemm_sm_margin; negative: the environment
+        if (margin < 0) {
+            const char *mg = getenv("CPMK_GEMM_SM_MARGIN");
+            margin = mg ? atoi(mg) : 0;
         }
+        const int margin_pairs = (margin + 1) / 2;
+        if (margin_pairs > 0 && max_pairs - margin_pairs >= 8) max_pairs -= margin_pairs;
         const bool any_mn = p_mn || q_mn;                   // MN-major operands are implemented in the two-CTA kernel only
         if ((variant != kVariantOneCta || scatter) && max_pairs > 0 && (n > kBM || variant == kVariantTwoCta || any_mn || scatter)) {
             const int64_t tiles_r = (n + 2 * kBM - 1) / (2 * kBM), tiles_c = (m + kBN - 1) / kBN;
@@ -1358,6 +1363,11 @@ int32_t cpmk_gemm_int8_dequant_gelu(int32_t m, int32_t k, int32_t n, int32_t bat
 int32_t cpmk_gemm_fp16(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT, const void *A, const void *B,
                        void *out, cpmk_stream_t stream) {
     return launch_gemm_f16(m, k, n, batchA, batchB, aT != 0, bT != 0, A, B, out, as_stream(stream));
+}
+
+int32_t cpmk_set_gemm_sm_margin(int32_t sms) {
+    g_sm_margin.store(sms < 0 ? -1 : sms, std::memory_order_relaxed);
+    return CPMK_OK;
 }
 
 int32_t cpmk_last_gemm_path(void) { return g_last_path; }

@@ -42,6 +42,7 @@ SIGNATURES = {
     "cpmk_gemm_int8_dequant_scatter": [_i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _i, _i, POINTER(c_void_p), ctypes.c_int64, _p],
     "cpmk_quantize_rows_pair": [_i, _i, _p, _p, _p, _i, _i, _p, _p, _p, _i, _p],
     "cpmk_layernorm_quantize_cols": [_i, _i, _i, _p, ctypes.c_float, _i, _p, _p, _p, _p, _p],
+    "cpmk_set_gemm_sm_margin": [_i],
     "cpmk_gelu_forward": [_i, _i, _p, _p, _p],
     "cpmk_gemm_int8_dequant_gelu": [_i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p, _p],
     "cpmk_gemm_fp16": [_i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p],
@@ -93,6 +94,11 @@ def read_status() -> int:
     word = c_uint32(0)
     check_status(lib.cpmk_read_status(ctypes.byref(word)), "cpmk_read_status")
     return word.value
+
+
+def set_gemm_sm_margin(sms: int) -> None:
+    """Keep the persistent GEMM grid off ``sms`` SMs (0: use all; negative: follow CPMK_GEMM_SM_MARGIN)."""
+    call("cpmk_set_gemm_sm_margin", int(sms))
 
 
 def last_gemm_variant() -> int:

@@ -164,6 +164,12 @@ int32_t cpmk_gemm_int8_dequant_gelu(int32_t m, int32_t k, int32_t n, int32_t bat
 int32_t cpmk_gemm_fp16(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT,
                        const void *A, const void *B, void *out, cpmk_stream_t stream);
 
+/* Keeps the persistent grid of the tensor-core GEMM off `sms` SMs from now on (process-wide), so that kernels of
+ * another stream -- a collective, or the quantisation passes of the next layer -- find room to run beside it.
+ * 0 = use every SM; a negative value returns the choice to the environment variable CPMK_GEMM_SM_MARGIN.
+ * No counterpart in the reference (cublasLt picks its own grid). */
+int32_t cpmk_set_gemm_sm_margin(int32_t sms);
+
 /* Which GEMM kernel the last cpmk_gemm_int8* / cpmk_gemm_fp16 call on this thread selected:
  * 1 = tcgen05 tensor-core kernel, 2 = generic SIMT kernel.  For tests and the benchmark. */
 int32_t cpmk_last_gemm_path(void);
