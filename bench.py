@@ -211,6 +211,8 @@ def run_ours(args) -> None:
     # (peer-mapped symmetric memory); falls back to an NCCL all-gather beside the GEMM if that cannot be set up
     fused_layers, exchange, fused_two_streams = None, "none", False
     fused_margin = os.environ.get("CPMK_BENCH_FUSED_SM_MARGIN", "32")
+    n_side = max(1, int(os.environ.get("CPMK_BENCH_FUSED_STREAMS", "2")) - 1)
+    side_streams = ([comm_stream] + [torch.cuda.Stream() for _ in range(n_side - 1)]) if world > 1 else []
     if world > 1:
         exchange = "nccl all_gather_into_tensor on a side stream"
         if args.exchange in ("fused", "fused1"):
@@ -239,16 +241,19 @@ def run_ours(args) -> None:
             # linear's GEMM drains its output over NVLink, the next one's quantisation passes and GEMM run beside it
             # (the scatter GEMM's persistent grid leaves part of the SMs free for that: CPMK_GEMM_SM_MARGIN).
             if fused_two_streams:
-                comm_stream.wait_stream(stream)
+                for s2 in side_streams:
+                    s2.wait_stream(stream)
                 cpmk.set_gemm_sm_margin(int(fused_margin))
             for i, (fl, x) in enumerate(zip(fused_layers, xs)):
-                if fused_two_streams and (i & 1):
-                    with torch.cuda.stream(comm_stream):
+                lane = i % (len(side_streams) + 1) if fused_two_streams else 0
+                if lane:
+                    with torch.cuda.stream(side_streams[lane - 1]):
                         results.append(fl(x))
                 else:
                     results.append(fl(x))
             if fused_two_streams:
-                stream.wait_stream(comm_stream)
+                for s2 in side_streams:
+                    stream.wait_stream(s2)
                 cpmk.set_gemm_sm_margin(-1)
             return results
         for i, (x, w) in enumerate(zip(xs, ws)):
