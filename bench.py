@@ -211,7 +211,7 @@ def run_ours(args) -> None:
     # (peer-mapped symmetric memory); falls back to an NCCL all-gather beside the GEMM if that cannot be set up
     fused_layers, exchange, fused_two_streams = None, "none", False
     fused_margin = os.environ.get("CPMK_BENCH_FUSED_SM_MARGIN", "32")
-    n_side = max(1, int(os.environ.get("CPMK_BENCH_FUSED_STREAMS", "2")) - 1)
+    n_side = max(1, int(os.environ.get("CPMK_BENCH_FUSED_STREAMS", "4")) - 1)
     side_streams = ([comm_stream] + [torch.cuda.Stream() for _ in range(n_side - 1)]) if world > 1 else []
     if world > 1:
         exchange = "nccl all_gather_into_tensor on a side stream"
@@ -229,7 +229,7 @@ def run_ours(args) -> None:
             os.environ.setdefault("CPMK_GEMM_SM_MARGIN", "16")
         elif args.exchange == "fused":
             fused_two_streams = True
-            exchange += "; linears alternate between two streams, scatter GEMM grids leave %s SMs free" % fused_margin
+            exchange += "; the linears run on %d streams, scatter GEMM grids leave %s SMs free" % (n_side + 1, fused_margin)
 
     gemm_events = []
 
@@ -237,8 +237,8 @@ def run_ours(args) -> None:
         """The four linears through the public API.  With record_gemm, CUDA events bracket each GEMM launch."""
         results = []
         if fused_layers is not None and gather and not record_gemm:
-            # The linears of the synthetic stack are independent, so they alternate between two streams: while one
-            # linear's GEMM drains its output over NVLink, the next one's quantisation passes and GEMM run beside it
+            # The linears of the synthetic stack are independent, so they are spread over several streams: while one
+            # linear's GEMM drains its output over NVLink, the others' quantisation passes and GEMMs run beside it
             # (the scatter GEMM's persistent grid leaves part of the SMs free for that: CPMK_GEMM_SM_MARGIN).
             if fused_two_streams:
                 for s2 in side_streams:
