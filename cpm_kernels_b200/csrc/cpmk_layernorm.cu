@@ -214,11 +214,18 @@ __global__ void __launch_bounds__(kLnBlock, 3) ln_quant_kernel(const LnParams p)
     __half2 m2[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) m2[j] = __float2half2_rn(0.f);
-    for (int sp = 0; sp < p.splits; ++sp) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p.amax_partial + ((int64_t)sp * batch + b) * p.m + col));
-        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+    for (int sp0 = 0; sp0 < p.splits; sp0 += 8) {              // eight independent loads at a time
+        uint4 v[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) m2[j] = __hmax2(h[j], m2[j]);
+        for (int u = 0; u < 8; ++u)
+            v[u] = sp0 + u < p.splits ? __ldg(reinterpret_cast<const uint4 *>(p.amax_partial + ((int64_t)(sp0 + u) * batch + b) * p.m + col))
+                                      : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const __half2 *h = reinterpret_cast<const __half2 *>(&v[u]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) m2[j] = __hmax2(h[j], m2[j]);
+        }
     }
     float s[8], r_up[8], r_dn[8];
     __align__(16) __half sh[8];
