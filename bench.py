@@ -560,7 +560,7 @@ def measure_other_configs(cases, dev, gen, stream, peaks, xs=None, ws=None, iter
         other["bmm_fp16_tflops"] = {"per_shape": f16, "peak_bf16_tflops": peaks["bf16_tflops"],
                                     "frac_of_peak": (sum(f16.values()) / len(f16)) / peaks["bf16_tflops"]}
     if "passes" in cases:
-        # quantisation passes (3 bytes per element algorithmic) and GELU (4 bytes per element), 4096 x 10240 operands
+        # quantisation passes (3 bytes per element algorithmic), GELU and transpose (4 bytes per element), 4096 x 10240 operands
         big = [torch.randn((1, 4096, 10240), generator=gen, device=dev).half() for _ in range(3)]
         sc_r = torch.empty((1, 4096), dtype=torch.half, device=dev)
         sc_c = torch.empty((1, 10240), dtype=torch.half, device=dev)
@@ -571,7 +571,8 @@ def measure_other_configs(cases, dev, gen, stream, peaks, xs=None, ws=None, iter
         for name, bytes_per, fn in (
                 ("quantize_rows", 3, lambda j: ck.gemm_quantize_rows(1, 4096, 10240, big[j].data_ptr(), sc_r.data_ptr(), q8.data_ptr(), st)),
                 ("quantize_cols", 3, lambda j: ck.gemm_quantize_cols(1, 4096, 10240, big[j].data_ptr(), sc_c.data_ptr(), q8.data_ptr(), st)),
-                ("gelu_forward", 4, lambda j: ck.gelu_forward(1, nel, big[j].data_ptr(), o16.data_ptr(), st))):
+                ("gelu_forward", 4, lambda j: ck.gelu_forward(1, nel, big[j].data_ptr(), o16.data_ptr(), st)),
+                ("transpose", 4, lambda j: ck.transpose(1, 4096, 10240, big[j].data_ptr(), o16.data_ptr(), st))):
             sec = timed(fn, 3)
             other[name] = {"shape": "(1, 4096, 10240) fp16", "us": sec * 1e6, "GBps": bytes_per * nel / sec / 1e9,
                            "frac_of_hbm_peak": bytes_per * nel / sec / 1e9 / peaks["hbm_gbs"]}

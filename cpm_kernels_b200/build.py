@@ -22,12 +22,12 @@ NVCC_FLAGS = [
 ]
 
 
-MODULES = {"gemm": "gemm_module.cu", "gemv": "gemv_module.cu"}
+MODULES = {"gemm": "gemm_module.cu", "gemv": "gemv_module.cu", "transpose": "transpose_module.cu"}
 MODULE_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fatbin"]
 
 
 def module_path(name: str) -> str:
-    """Path of the built kernel module ``name`` ("gemm" or "gemv"): the file the reference's loader reads as
+    """Path of the built kernel module ``name`` ("gemm", "gemv" or "transpose"): the file the reference's loader reads as
     ``cuda/<name>.fatbin`` (cpm_kernels/kernels/base.py:59-71)."""
     return os.path.join(LIB_DIR, name + ".fatbin")
 

@@ -5,6 +5,7 @@ from .gemm import (gemm_calc_scale, gemm_calc_scale_transpose, gemm_round, gemm_
                    gemm_quantize_rows, gemm_quantize_rows_pair, gemm_quantize_cols, gemm_int8_scale, gemm_int8_scale_gelu, gemm_int8_scale_scatter)
 from .gelu import gelu_forward, gelu_inplace_forward
 from .layernorm import layernorm_quantize_cols
+from .transpose import transpose
 from .gemv import (gemv_fp16, gemv_fp16_light, gemv_fp16_transpose, gemv_fp16_transpose_light,
                    gemv_broadcast_mat_fp16, gemv_broadcast_mat_fp16_light, gemv_calc_scale, gemv_round,
                    gemv_broadcast_mat_int8)

@@ -148,6 +148,10 @@ int32_t cpmk_layernorm_quantize_cols(int32_t batch, int32_t n, int32_t m, const 
  * fills on its stream (that call should not be inside a stream capture). */
 int32_t cpmk_gelu_forward(int32_t batch, int32_t n, const void *mat, void *out, cpmk_stream_t stream);
 
+/* out[b, c, r] = in[b, r, c] on fp16: replaces cpm_kernels/kernels/transpose.py:11-27 transpose (cuda/transpose.cu:6-22);
+ * `in` is (batch, n, m) contiguous, `out` (batch, m, n).  Pure data movement, same bits.  in and out must not overlap. */
+int32_t cpmk_transpose(int32_t batch, int32_t n, int32_t m, const void *in, void *out, cpmk_stream_t stream);
+
 /* cpmk_gemm_int8_dequant followed by GELU on the fp16 result, as the feed-forward block applies it after its first
  * linear (cpm_kernels.torch.gelu after bmm): out = gelu(half(((float)acc * sx) * sy)), bit-identical to the two
  * separate calls, enqueued back to back on `stream` so that the activation reads the result out of L2. */

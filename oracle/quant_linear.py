@@ -202,6 +202,12 @@ def gelu_forward(x: np.ndarray) -> np.ndarray:
     return bits.view(np.float16)
 
 
+def transpose(x: np.ndarray) -> np.ndarray:
+    """cuda/transpose.cu:6-22 cu_transpose: out[b, c, r] = in[b, r, c] for a (batch, n, m) array; no arithmetic."""
+    assert x.ndim == 3
+    return np.ascontiguousarray(np.swapaxes(x, 1, 2))
+
+
 def _shuffle_down_sum32(v: np.ndarray) -> np.ndarray:
     """Lane 0 of the reference's warpReduceSum (cuda/includes/reduce.cuh:6-10) over the last axis (length 32), in
     binary32: x += shfl_down(x, 16), then 8, 4, 2, 1."""

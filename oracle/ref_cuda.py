@@ -73,7 +73,7 @@ class ReferenceKernels:
         torch.zeros(1, device="cuda")       # make the primary context current
         self.drv = _Driver()
         self._fns = {}
-        for name in ("gemm", "gemv", "gelu", "layernorm", "arith"):
+        for name in ("gemm", "gemv", "gelu", "layernorm", "arith", "transpose"):
             path = os.path.join(fatbin_dir, name + ".fatbin")
             if name not in ("gemm", "gemv") and not os.path.exists(path):
                 continue                                  # only needed by the functions of that file
@@ -181,6 +181,15 @@ class ReferenceKernels:
         threads = min(_round_up(n, 32), 1024)
         self.drv.launch(self._fn("gelu", "cu_gelu_forward"), (b, _round_up(n, threads) // threads, 1), (threads, 1, 1), self._stream(),
                         [self._i(b), self._i(n), self._p(mat), self._p(out)])
+        return out
+
+    # ---- cpm_kernels/kernels/transpose.py --------------------------------------------------------
+    def transpose(self, mat: torch.Tensor) -> torch.Tensor:
+        """kernels/transpose.py:11-27: grid (batch, round_up(n, 32) / 32, round_up(m, 32) / 32), block (32, 32)."""
+        b, n, m = mat.shape
+        out = torch.empty((b, m, n), dtype=torch.half, device=mat.device)
+        self.drv.launch(self._fn("transpose", "cu_transpose"), (b, _round_up(n, 32) // 32, _round_up(m, 32) // 32), (32, 32, 1), self._stream(),
+                        [self._i(b), self._i(n), self._i(m), self._p(mat), self._p(out)])
         return out
 
     # ---- cpm_kernels/kernels/layernorm.py, arith.py ----------------------------------------------

@@ -82,8 +82,8 @@ def test_kernel_level_preconditions_are_the_references(built_library):
 
 
 def test_kernel_modules_are_built_and_export_the_reference_symbols():
-    """lib/gemm.fatbin and lib/gemv.fatbin exist after a build, and their sources define every kernel name the
-    reference's loader looks up (cpm_kernels/kernels/gemm.py:6-19, kernels/gemv.py:6-16)."""
+    """lib/gemm.fatbin, lib/gemv.fatbin and lib/transpose.fatbin exist after a build, and their sources define every kernel name the
+    reference's loader looks up (cpm_kernels/kernels/gemm.py:6-19, kernels/gemv.py:6-16, kernels/transpose.py:4-9)."""
     import os
     import re
     from cpm_kernels_b200 import build
@@ -93,6 +93,7 @@ def test_kernel_modules_are_built_and_export_the_reference_symbols():
                  "cu_gemm_backward_round_scale", "cu_gemm_backward_scale_round", "cu_gemm_scale_x", "cu_gemm_scale_y"],
         "gemv": ["cu_gemv_calc_scale", "cu_gemv_round", "cu_gemv_broadcast_mat_int8", "cu_gemv_fp16", "cu_gemv_fp16_transpose",
                  "cu_gemv_broadcast_mat_fp16"],
+        "transpose": ["cu_transpose"],
     }
     for mod, kernels in names.items():
         assert os.path.getsize(build.module_path(mod)) > 0

@@ -121,3 +121,15 @@ def test_layernorm_chain_restatement_matches_the_reference():
         assert (scale.view(np.uint16) == g[name + "_scale"]).all()
         assert (codes == g[name + "_codes"]).all()
     assert ln_mismatches <= 3
+
+
+def test_transpose_oracle_by_definition():
+    """cuda/transpose.cu:6-22: out[b, c, r] = in[b, r, c], checked element by element on a small ragged case."""
+    rng = np.random.default_rng(4)
+    x = rng.integers(0, 65536, size=(3, 5, 7), dtype=np.uint16).view(np.float16)
+    y = ql.transpose(x)
+    assert y.shape == (3, 7, 5) and y.flags["C_CONTIGUOUS"]
+    for b in range(3):
+        for r in range(5):
+            for c in range(7):
+                assert y.view(np.uint16)[b, c, r] == x.view(np.uint16)[b, r, c]
