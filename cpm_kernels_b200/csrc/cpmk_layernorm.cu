@@ -23,59 +23,72 @@ constexpr int kLnWideCols = 512;        // passes B and C: columns per block (1 
 constexpr int kLnRowLanes = kLnBlock / (kLnWideCols / 8);   // 4 row lanes per block
 constexpr int kLnChunkRows = 1024;      // the reference's outer loop step (WARP_SZ * WARP_SZ)
 
-// lane 0 of x += shfl_down(x, 16), 8, 4, 2, 1 over 32 values, for two columns at once; v holds the 16 sums of the
-// first level (rows l and l + 16)
-__device__ __forceinline__ float2 tree_sum16(float2 (&v)[16]) {
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) {
-#pragma unroll
-        for (int l = 0; l < o; ++l) {
-            v[l].x = __fadd_rn(v[l].x, v[l + o].x);
-            v[l].y = __fadd_rn(v[l].y, v[l + o].y);
-        }
-    }
-    return v[0];
-}
-
 // Pass A: the sums of x (if RD_MEAN) and of x * x over one chunk of 1024 rows for a strip of 64 columns.
-// Thread (cp, g): column pair cp of the strip, row block g of the chunk's 32 blocks of 32 rows.
+// Thread (c8, g): columns 8 c8 .. 8 c8 + 7 of the strip, row block g of the chunk's 32 blocks of 32 rows.
+// The shuffle-down tree over the 32 rows of a block -- x[l] + x[l + 16], then offsets 8, 4, 2, 1 -- is evaluated
+// in four groups of the eight rows l4, l4 + 4, ..., l4 + 28: a group yields the tree's third-level value c[l4],
+//   c[l4] = ((x[l4] + x[l4+16]) + (x[l4+8] + x[l4+24])) + ((x[l4+4] + x[l4+20]) + (x[l4+12] + x[l4+28])),
+// and the block's sum is (c[0] + c[2]) + (c[1] + c[3]): the same additions, with eight 16-byte loads in flight.
 // sums layout: [quantity (0: x, 1: x*x)][batch][chunk][m] floats.
-constexpr int kLnSumsBlock = 1024;      // pass A: 32 column pairs x 32 row blocks, one 32-row block per thread
+constexpr int kLnSumsBlock = 256;       // pass A: 8 column groups x 32 row blocks, one 32-row block per thread
 template <bool RD_MEAN>
-__global__ void __launch_bounds__(kLnSumsBlock) ln_chunk_sums_kernel(int32_t n, int32_t m, int32_t chunks, const __half *__restrict__ mat,
-                                                                 float *__restrict__ sums) {
-    __shared__ float block_sums[2][32][kLnStripCols];
-    const int cp = threadIdx.x & 31, g = threadIdx.x >> 5;
+__global__ void __launch_bounds__(kLnSumsBlock, 2) ln_chunk_sums_kernel(int32_t n, int32_t m, int32_t chunks, const __half *__restrict__ mat,
+                                                                    float *__restrict__ sums) {
+    __shared__ __align__(16) float block_sums[2][32][kLnStripCols];
+    const int c8 = threadIdx.x & 7, g = threadIdx.x >> 3;
     const int b = blockIdx.z, chunk = blockIdx.y, batch = gridDim.z;
-    const int col = blockIdx.x * kLnStripCols + 2 * cp;
-    const bool col_ok = col < m;                                   // m is even: both columns of the pair are in or out
-    const __half *base = mat + (int64_t)b * n * m + col;
+    const int col = blockIdx.x * kLnStripCols + 8 * c8;
+    const bool col_ok = col < m;                                   // m is a multiple of 8: a thread's columns are all in or all out
     {
-        const int blk = g;
-        const int r0 = chunk * kLnChunkRows + blk * 32;
-        __half2 h[32];
+        const int r0 = chunk * kLnChunkRows + g * 32;
+        const __half *base = mat + (int64_t)b * n * m + (int64_t)r0 * m + col;
+        float c2[4][8], c1[4][8];
 #pragma unroll
-        for (int l = 0; l < 32; ++l)
-            h[l] = (col_ok && r0 + l < n) ? __ldg(reinterpret_cast<const __half2 *>(base + (int64_t)(r0 + l) * m)) : __float2half2_rn(0.f);
-        // the first level of the tree pairs rows l and l + 16: formed as the values are converted, 16 partial sums live
-        float2 v[16];
+        for (int l4 = 0; l4 < 4; ++l4) {
+            uint4 x[8];
 #pragma unroll
-        for (int l = 0; l < 16; ++l) {
-            const float2 f = __half22float2(h[l]), g2 = __half22float2(h[l + 16]);
-            v[l] = make_float2(__fadd_rn(__fmul_rn(f.x, f.x), __fmul_rn(g2.x, g2.x)), __fadd_rn(__fmul_rn(f.y, f.y), __fmul_rn(g2.y, g2.y)));
-        }
-        const float2 s2 = tree_sum16(v);
-        block_sums[1][blk][2 * cp] = s2.x;
-        block_sums[1][blk][2 * cp + 1] = s2.y;
-        if (RD_MEAN) {
+            for (int k = 0; k < 8; ++k)
+                x[k] = (col_ok && r0 + l4 + 4 * k < n) ? __ldg(reinterpret_cast<const uint4 *>(base + (l4 + 4 * k) * m)) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-            for (int l = 0; l < 16; ++l) {
-                const float2 f = __half22float2(h[l]), g2 = __half22float2(h[l + 16]);
-                v[l] = make_float2(__fadd_rn(f.x, g2.x), __fadd_rn(f.y, g2.y));
+            for (int j = 0; j < 4; ++j) {
+                float2 f[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) f[k] = __half22float2(reinterpret_cast<const __half2 *>(&x[k])[j]);
+                {
+                    const float a0 = __fadd_rn(__fmul_rn(f[0].x, f[0].x), __fmul_rn(f[4].x, f[4].x));
+                    const float a1 = __fadd_rn(__fmul_rn(f[1].x, f[1].x), __fmul_rn(f[5].x, f[5].x));
+                    const float a2 = __fadd_rn(__fmul_rn(f[2].x, f[2].x), __fmul_rn(f[6].x, f[6].x));
+                    const float a3 = __fadd_rn(__fmul_rn(f[3].x, f[3].x), __fmul_rn(f[7].x, f[7].x));
+                    c2[l4][2 * j] = __fadd_rn(__fadd_rn(a0, a2), __fadd_rn(a1, a3));
+                }
+                {
+                    const float a0 = __fadd_rn(__fmul_rn(f[0].y, f[0].y), __fmul_rn(f[4].y, f[4].y));
+                    const float a1 = __fadd_rn(__fmul_rn(f[1].y, f[1].y), __fmul_rn(f[5].y, f[5].y));
+                    const float a2 = __fadd_rn(__fmul_rn(f[2].y, f[2].y), __fmul_rn(f[6].y, f[6].y));
+                    const float a3 = __fadd_rn(__fmul_rn(f[3].y, f[3].y), __fmul_rn(f[7].y, f[7].y));
+                    c2[l4][2 * j + 1] = __fadd_rn(__fadd_rn(a0, a2), __fadd_rn(a1, a3));
+                }
+                if (RD_MEAN) {
+                    c1[l4][2 * j] = __fadd_rn(__fadd_rn(__fadd_rn(f[0].x, f[4].x), __fadd_rn(f[2].x, f[6].x)),
+                                              __fadd_rn(__fadd_rn(f[1].x, f[5].x), __fadd_rn(f[3].x, f[7].x)));
+                    c1[l4][2 * j + 1] = __fadd_rn(__fadd_rn(__fadd_rn(f[0].y, f[4].y), __fadd_rn(f[2].y, f[6].y)),
+                                                  __fadd_rn(__fadd_rn(f[1].y, f[5].y), __fadd_rn(f[3].y, f[7].y)));
+                }
             }
-            const float2 s1 = tree_sum16(v);
-            block_sums[0][blk][2 * cp] = s1.x;
-            block_sums[0][blk][2 * cp + 1] = s1.y;
+        }
+        float s2[8], s1[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            s2[i] = __fadd_rn(__fadd_rn(c2[0][i], c2[2][i]), __fadd_rn(c2[1][i], c2[3][i]));
+            if (RD_MEAN) s1[i] = __fadd_rn(__fadd_rn(c1[0][i], c1[2][i]), __fadd_rn(c1[1][i], c1[3][i]));
+        }
+        float4 *dst2 = reinterpret_cast<float4 *>(&block_sums[1][g][8 * c8]);
+        dst2[0] = make_float4(s2[0], s2[1], s2[2], s2[3]);
+        dst2[1] = make_float4(s2[4], s2[5], s2[6], s2[7]);
+        if (RD_MEAN) {
+            float4 *dst1 = reinterpret_cast<float4 *>(&block_sums[0][g][8 * c8]);
+            dst1[0] = make_float4(s1[0], s1[1], s1[2], s1[3]);
+            dst1[1] = make_float4(s1[4], s1[5], s1[6], s1[7]);
         }
     }
     __syncthreads();
@@ -110,7 +123,7 @@ struct LnParams {
 // Thread (t8, rl): columns c0 + 8 t8 .. + 7 of the 512-column strip, rows rl, rl + 4, ... of the block's row range
 // (whole 1 KiB row segments per block: narrow strips leave most of every DRAM page to other blocks at other times).
 template <int PASS, bool RD_MEAN, bool BIAS>
-__global__ void __launch_bounds__(kLnBlock, 3) ln_quant_kernel(const LnParams p) {
+__global__ void __launch_bounds__(kLnBlock, PASS == 0 ? 3 : 2) ln_quant_kernel(const LnParams p) {
     __shared__ __align__(16) __half lane_max[kLnRowLanes][kLnWideCols];
     const int t8 = threadIdx.x & (kLnWideCols / 8 - 1), rl = threadIdx.x / (kLnWideCols / 8);
     const int b = blockIdx.z, split = blockIdx.y, batch = gridDim.z;
@@ -160,15 +173,11 @@ __global__ void __launch_bounds__(kLnBlock, 3) ln_quant_kernel(const LnParams p)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float2 f = __half22float2(h[j]);
-            __half y0, y1;
-            if (RD_MEAN) {
-                y0 = __float2half(__fmul_rn(__fsub_rn(f.x, mean[2 * j]), rstd[2 * j]));
-                y1 = __float2half(__fmul_rn(__fsub_rn(f.y, mean[2 * j + 1]), rstd[2 * j + 1]));
-            } else {
-                y0 = __float2half(__fmul_rn(f.x, rstd[2 * j]));
-                y1 = __float2half(__fmul_rn(f.y, rstd[2 * j + 1]));
-            }
-            const __half2 yy = __halves2half2(y0, y1), a2 = __half2half2(a);
+            // one packed conversion: each half is rounded to nearest on its own, as two __float2half calls would
+            const __half2 yy = RD_MEAN ? __floats2half2_rn(__fmul_rn(__fsub_rn(f.x, mean[2 * j]), rstd[2 * j]),
+                                                           __fmul_rn(__fsub_rn(f.y, mean[2 * j + 1]), rstd[2 * j + 1]))
+                                       : __floats2half2_rn(__fmul_rn(f.x, rstd[2 * j]), __fmul_rn(f.y, rstd[2 * j + 1]));
+            const __half2 a2 = __half2half2(a);
             y[j] = BIAS ? __hfma2(yy, a2, __half2half2(bb)) : __hmul2(yy, a2);
         }
     };
@@ -227,7 +236,8 @@ __global__ void __launch_bounds__(kLnBlock, 3) ln_quant_kernel(const LnParams p)
             for (int j = 0; j < 4; ++j) m2[j] = __hmax2(h[j], m2[j]);
         }
     }
-    float s[8], r_up[8], r_dn[8];
+    float s[8];
+    float2 ru[4], rd[4];
     __align__(16) __half sh[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -236,53 +246,70 @@ __global__ void __launch_bounds__(kLnBlock, 3) ln_quant_kernel(const LnParams p)
         sh[2 * j + 1] = scale_from_amax(a.y);
         s[2 * j] = __half2float(sh[2 * j]);
         s[2 * j + 1] = __half2float(sh[2 * j + 1]);
-        cpmk_round_prepare(s[2 * j], &r_up[2 * j], &r_dn[2 * j]);
-        cpmk_round_prepare(s[2 * j + 1], &r_up[2 * j + 1], &r_dn[2 * j + 1]);
-        if (!(cpmk_scale_in_domain(s[2 * j]) && cpmk_round_domain_ok(a.x, r_up[2 * j]))) r_up[2 * j] = __int_as_float(0x7fc00000);
-        if (!(cpmk_scale_in_domain(s[2 * j + 1]) && cpmk_round_domain_ok(a.y, r_up[2 * j + 1]))) r_up[2 * j + 1] = __int_as_float(0x7fc00000);
+        cpmk_round_prepare(s[2 * j], &ru[j].x, &rd[j].x);
+        cpmk_round_prepare(s[2 * j + 1], &ru[j].y, &rd[j].y);
+        // a column outside the rule's domain gets a NaN multiplier: its elements then fail the agreement test below
+        if (!(cpmk_scale_in_domain(s[2 * j]) && cpmk_round_domain_ok(a.x, ru[j].x))) ru[j].x = __int_as_float(0x7fc00000);
+        if (!(cpmk_scale_in_domain(s[2 * j + 1]) && cpmk_round_domain_ok(a.y, ru[j].y))) ru[j].y = __int_as_float(0x7fc00000);
     }
     if (split == 0 && rl == 0) *reinterpret_cast<uint4 *>(p.scale + (int64_t)b * p.m + col) = *reinterpret_cast<const uint4 *>(sh);
     int8_t *obase = p.out + (int64_t)b * p.n * p.m + col;
     const float2 magic = make_float2(CPMK_ROUND_MAGIC, CPMK_ROUND_MAGIC);
-    for (int r0 = r_begin + rl; r0 < r_end; r0 += 2 * kLnRowLanes) {
-      uint4 vv[2];
+    constexpr int kRowsInFlight = 4;
+    for (int r0 = r_begin + rl; r0 < r_end; r0 += kRowsInFlight * kLnRowLanes) {
+        uint4 vv[kRowsInFlight];
 #pragma unroll
-      for (int u = 0; u < 2; ++u)
-          vv[u] = r0 + kLnRowLanes * u < r_end ? __ldg(reinterpret_cast<const uint4 *>(base + (int64_t)(r0 + kLnRowLanes * u) * p.m))
-                                               : make_uint4(0u, 0u, 0u, 0u);
+        for (int u = 0; u < kRowsInFlight; ++u)
+            vv[u] = r0 + kLnRowLanes * u < r_end ? __ldg(reinterpret_cast<const uint4 *>(base + (int64_t)(r0 + kLnRowLanes * u) * p.m))
+                                                 : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int r = r0 + kLnRowLanes * u;
-        if (r >= r_end) break;
-        const uint4 v = vv[u];
-        __half2 y[4];
-        transform(v, r, y);
-        uint32_t bits[8];
-        bool agree = true, regular = true;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float2 f = __half22float2(y[j]);
-            const float2 up = __ffma2_rn(f, make_float2(r_up[2 * j], r_up[2 * j + 1]), magic);
-            const float2 dn = __ffma2_rn(f, make_float2(r_dn[2 * j], r_dn[2 * j + 1]), magic);
-            agree = agree && up.x == dn.x && up.y == dn.y;
-            // a tie inside the domain has up = dn + 1; NaN and the out-of-domain marker fail both comparisons
-            regular = regular && (up.x == dn.x || up.x - dn.x == 1.f) && (up.y == dn.y || up.y - dn.y == 1.f);
-            bits[2 * j] = resolve_tie(__float_as_uint(up.x), __float_as_uint(dn.x));
-            bits[2 * j + 1] = resolve_tie(__float_as_uint(up.y), __float_as_uint(dn.y));
-        }
-        if (!agree && !regular) {
+        for (int u = 0; u < kRowsInFlight; ++u) {
+            const int r = r0 + kLnRowLanes * u;
+            if (r >= r_end) break;
+            __half2 y[4];
+            transform(vv[u], r, y);
+            // both roundings of every element; their disagreement is summed on the FMA pipe as squared differences
+            // (zero iff all agree; NaN -- a NaN or infinite element, or the out-of-domain marker -- propagates)
+            float2 dn[4];
+            float2 bad = make_float2(0.f, 0.f);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float2 f = __half22float2(y[j]);
-                bits[2 * j] = (uint8_t)round_reference(f.x, s[2 * j]);
-                bits[2 * j + 1] = (uint8_t)round_reference(f.y, s[2 * j + 1]);
+                const float2 up = __ffma2_rn(f, ru[j], magic);
+                dn[j] = __ffma2_rn(f, rd[j], magic);
+                const float2 d = __fadd2_rn(up, make_float2(-dn[j].x, -dn[j].y));
+                bad = __ffma2_rn(d, d, bad);
             }
+            uint32_t bits[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                bits[2 * j] = __float_as_uint(dn[j].x);
+                bits[2 * j + 1] = __float_as_uint(dn[j].y);
+            }
+            const float bad_sum = bad.x + bad.y;
+            if (!(bad_sum == 0.f)) {
+                if (bad_sum < 64.f) {
+                    // finite: every disagreement is an exact tie (up = dn + 1), resolved to the even neighbour
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 up = __ffma2_rn(__half22float2(y[j]), ru[j], magic);
+                        bits[2 * j] = resolve_tie(__float_as_uint(up.x), bits[2 * j]);
+                        bits[2 * j + 1] = resolve_tie(__float_as_uint(up.y), bits[2 * j + 1]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __half22float2(y[j]);
+                        bits[2 * j] = (uint8_t)round_reference(f.x, s[2 * j]);
+                        bits[2 * j + 1] = (uint8_t)round_reference(f.y, s[2 * j + 1]);
+                    }
+                }
+            }
+            uint2 q;
+            q.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+            q.y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
+            *reinterpret_cast<uint2 *>(obase + (int64_t)r * p.m) = q;
         }
-        uint2 q;
-        q.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
-        q.y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
-        *reinterpret_cast<uint2 *>(obase + (int64_t)r * p.m) = q;
-      }
     }
 }
 
