@@ -24,71 +24,82 @@ constexpr int kLnRowLanes = kLnBlock / (kLnWideCols / 8);   // 4 row lanes per b
 constexpr int kLnChunkRows = 1024;      // the reference's outer loop step (WARP_SZ * WARP_SZ)
 
 // Pass A: the sums of x (if RD_MEAN) and of x * x over one chunk of 1024 rows for a strip of 64 columns.
-// Thread (c8, g): columns 8 c8 .. 8 c8 + 7 of the strip, row block g of the chunk's 32 blocks of 32 rows.
-// The shuffle-down tree over the 32 rows of a block -- x[l] + x[l + 16], then offsets 8, 4, 2, 1 -- is evaluated
-// in four groups of the eight rows l4, l4 + 4, ..., l4 + 28: a group yields the tree's third-level value c[l4],
+// Warp g takes row block g of the chunk's 32 blocks of 32 rows; lane (c8, l4) takes columns 8 c8 .. 8 c8 + 7 of the
+// strip and the eight rows l4, l4 + 4, ..., l4 + 28 of the block.  The shuffle-down tree over the 32 rows of a block
+// -- x[l] + x[l + 16], then offsets 8, 4, 2, 1 -- has the third-level values
 //   c[l4] = ((x[l4] + x[l4+16]) + (x[l4+8] + x[l4+24])) + ((x[l4+4] + x[l4+20]) + (x[l4+12] + x[l4+28])),
-// and the block's sum is (c[0] + c[2]) + (c[1] + c[3]): the same additions, with eight 16-byte loads in flight.
+// which a lane forms from its own rows in two rounds of four 16-byte loads, and the block's sum
+// (c[0] + c[2]) + (c[1] + c[3]) comes from two exchanges between lanes: the same additions as the reference's.
 // sums layout: [quantity (0: x, 1: x*x)][batch][chunk][m] floats.
-constexpr int kLnSumsBlock = 256;       // pass A: 8 column groups x 32 row blocks, one 32-row block per thread
+// Two blocks per SM: 1024 threads of 32 registers for the RMS form (one row block per warp), 512 threads of 64
+// registers when the sums of x are needed too (two row blocks per warp, one after the other).
 template <bool RD_MEAN>
-__global__ void __launch_bounds__(kLnSumsBlock, 2) ln_chunk_sums_kernel(int32_t n, int32_t m, int32_t chunks, const __half *__restrict__ mat,
+struct LnSumsShape {
+    static constexpr int kRowBlocksPerWarp = RD_MEAN ? 2 : 1;
+    static constexpr int kThreads = 1024 / kRowBlocksPerWarp;
+};
+template <bool RD_MEAN>
+__global__ void __launch_bounds__(LnSumsShape<RD_MEAN>::kThreads, 2) ln_chunk_sums_kernel(int32_t n, int32_t m, int32_t chunks, const __half *__restrict__ mat,
                                                                     float *__restrict__ sums) {
     __shared__ __align__(16) float block_sums[2][32][kLnStripCols];
-    const int c8 = threadIdx.x & 7, g = threadIdx.x >> 3;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int c8 = lane & 7, l4 = lane >> 3;
     const int b = blockIdx.z, chunk = blockIdx.y, batch = gridDim.z;
     const int col = blockIdx.x * kLnStripCols + 8 * c8;
     const bool col_ok = col < m;                                   // m is a multiple of 8: a thread's columns are all in or all out
-    {
-        const int r0 = chunk * kLnChunkRows + g * 32;
+#pragma unroll 1
+    for (int gi = 0; gi < LnSumsShape<RD_MEAN>::kRowBlocksPerWarp; ++gi) {
+        const int g = warp * LnSumsShape<RD_MEAN>::kRowBlocksPerWarp + gi;
+        const int r0 = chunk * kLnChunkRows + g * 32 + l4;
         const __half *base = mat + (int64_t)b * n * m + (int64_t)r0 * m + col;
-        float c2[4][8], c1[4][8];
+        float c2[8], c1[8];
+        // round 0: rows l4, l4+16, l4+8, l4+24 -> (x[l4] + x[l4+16]) + (x[l4+8] + x[l4+24]);  round 1: the same, 4 rows on
 #pragma unroll
-        for (int l4 = 0; l4 < 4; ++l4) {
-            uint4 x[8];
+        for (int round = 0; round < 2; ++round) {
+            const int offs[4] = {4 * round, 4 * round + 16, 4 * round + 8, 4 * round + 24};
+            uint4 x[4];
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-                x[k] = (col_ok && r0 + l4 + 4 * k < n) ? __ldg(reinterpret_cast<const uint4 *>(base + (l4 + 4 * k) * m)) : make_uint4(0u, 0u, 0u, 0u);
+            for (int k = 0; k < 4; ++k)
+                x[k] = (col_ok && r0 + offs[k] < n) ? __ldg(reinterpret_cast<const uint4 *>(base + offs[k] * m)) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                float2 f[8];
+                float2 f[4];
 #pragma unroll
-                for (int k = 0; k < 8; ++k) f[k] = __half22float2(reinterpret_cast<const __half2 *>(&x[k])[j]);
-                {
-                    const float a0 = __fadd_rn(__fmul_rn(f[0].x, f[0].x), __fmul_rn(f[4].x, f[4].x));
-                    const float a1 = __fadd_rn(__fmul_rn(f[1].x, f[1].x), __fmul_rn(f[5].x, f[5].x));
-                    const float a2 = __fadd_rn(__fmul_rn(f[2].x, f[2].x), __fmul_rn(f[6].x, f[6].x));
-                    const float a3 = __fadd_rn(__fmul_rn(f[3].x, f[3].x), __fmul_rn(f[7].x, f[7].x));
-                    c2[l4][2 * j] = __fadd_rn(__fadd_rn(a0, a2), __fadd_rn(a1, a3));
-                }
-                {
-                    const float a0 = __fadd_rn(__fmul_rn(f[0].y, f[0].y), __fmul_rn(f[4].y, f[4].y));
-                    const float a1 = __fadd_rn(__fmul_rn(f[1].y, f[1].y), __fmul_rn(f[5].y, f[5].y));
-                    const float a2 = __fadd_rn(__fmul_rn(f[2].y, f[2].y), __fmul_rn(f[6].y, f[6].y));
-                    const float a3 = __fadd_rn(__fmul_rn(f[3].y, f[3].y), __fmul_rn(f[7].y, f[7].y));
-                    c2[l4][2 * j + 1] = __fadd_rn(__fadd_rn(a0, a2), __fadd_rn(a1, a3));
-                }
+                for (int k = 0; k < 4; ++k) f[k] = __half22float2(reinterpret_cast<const __half2 *>(&x[k])[j]);
+                const float qx = __fadd_rn(__fadd_rn(__fmul_rn(f[0].x, f[0].x), __fmul_rn(f[1].x, f[1].x)),
+                                           __fadd_rn(__fmul_rn(f[2].x, f[2].x), __fmul_rn(f[3].x, f[3].x)));
+                const float qy = __fadd_rn(__fadd_rn(__fmul_rn(f[0].y, f[0].y), __fmul_rn(f[1].y, f[1].y)),
+                                           __fadd_rn(__fmul_rn(f[2].y, f[2].y), __fmul_rn(f[3].y, f[3].y)));
+                c2[2 * j] = round == 0 ? qx : __fadd_rn(c2[2 * j], qx);
+                c2[2 * j + 1] = round == 0 ? qy : __fadd_rn(c2[2 * j + 1], qy);
                 if (RD_MEAN) {
-                    c1[l4][2 * j] = __fadd_rn(__fadd_rn(__fadd_rn(f[0].x, f[4].x), __fadd_rn(f[2].x, f[6].x)),
-                                              __fadd_rn(__fadd_rn(f[1].x, f[5].x), __fadd_rn(f[3].x, f[7].x)));
-                    c1[l4][2 * j + 1] = __fadd_rn(__fadd_rn(__fadd_rn(f[0].y, f[4].y), __fadd_rn(f[2].y, f[6].y)),
-                                                  __fadd_rn(__fadd_rn(f[1].y, f[5].y), __fadd_rn(f[3].y, f[7].y)));
+                    const float px = __fadd_rn(__fadd_rn(f[0].x, f[1].x), __fadd_rn(f[2].x, f[3].x));
+                    const float py = __fadd_rn(__fadd_rn(f[0].y, f[1].y), __fadd_rn(f[2].y, f[3].y));
+                    c1[2 * j] = round == 0 ? px : __fadd_rn(c1[2 * j], px);
+                    c1[2 * j + 1] = round == 0 ? py : __fadd_rn(c1[2 * j + 1], py);
                 }
             }
         }
-        float s2[8], s1[8];
+        // (c[0] + c[2]) + (c[1] + c[3]): lanes l4 and l4 ^ 2 first, then l4 ^ 1; float addition commutes, so every lane
+        // of a column group ends with the same bits
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            s2[i] = __fadd_rn(__fadd_rn(c2[0][i], c2[2][i]), __fadd_rn(c2[1][i], c2[3][i]));
-            if (RD_MEAN) s1[i] = __fadd_rn(__fadd_rn(c1[0][i], c1[2][i]), __fadd_rn(c1[1][i], c1[3][i]));
+            c2[i] = __fadd_rn(c2[i], __shfl_xor_sync(0xffffffffu, c2[i], 16));
+            c2[i] = __fadd_rn(c2[i], __shfl_xor_sync(0xffffffffu, c2[i], 8));
+            if (RD_MEAN) {
+                c1[i] = __fadd_rn(c1[i], __shfl_xor_sync(0xffffffffu, c1[i], 16));
+                c1[i] = __fadd_rn(c1[i], __shfl_xor_sync(0xffffffffu, c1[i], 8));
+            }
         }
-        float4 *dst2 = reinterpret_cast<float4 *>(&block_sums[1][g][8 * c8]);
-        dst2[0] = make_float4(s2[0], s2[1], s2[2], s2[3]);
-        dst2[1] = make_float4(s2[4], s2[5], s2[6], s2[7]);
-        if (RD_MEAN) {
-            float4 *dst1 = reinterpret_cast<float4 *>(&block_sums[0][g][8 * c8]);
-            dst1[0] = make_float4(s1[0], s1[1], s1[2], s1[3]);
-            dst1[1] = make_float4(s1[4], s1[5], s1[6], s1[7]);
+        if (l4 == 0) {
+            float4 *dst2 = reinterpret_cast<float4 *>(&block_sums[1][g][8 * c8]);
+            dst2[0] = make_float4(c2[0], c2[1], c2[2], c2[3]);
+            dst2[1] = make_float4(c2[4], c2[5], c2[6], c2[7]);
+            if (RD_MEAN) {
+                float4 *dst1 = reinterpret_cast<float4 *>(&block_sums[0][g][8 * c8]);
+                dst1[0] = make_float4(c1[0], c1[1], c1[2], c1[3]);
+                dst1[1] = make_float4(c1[4], c1[5], c1[6], c1[7]);
+            }
         }
     }
     __syncthreads();
@@ -315,7 +326,7 @@ __global__ void __launch_bounds__(kLnBlock, PASS == 0 ? 3 : 2) ln_quant_kernel(c
 
 template <bool RD_MEAN, bool BIAS>
 int32_t launch_ln_quant(const LnParams &p, int32_t batch, const dim3 &grid_a, const dim3 &grid_bc, float *sums, cudaStream_t stream) {
-    ln_chunk_sums_kernel<RD_MEAN><<<grid_a, kLnSumsBlock, 0, stream>>>(p.n, p.m, p.chunks, p.mat, sums);
+    ln_chunk_sums_kernel<RD_MEAN><<<grid_a, LnSumsShape<RD_MEAN>::kThreads, 0, stream>>>(p.n, p.m, p.chunks, p.mat, sums);
     CPMK_LAUNCH_CHECK();
     ln_quant_kernel<0, RD_MEAN, BIAS><<<grid_bc, kLnBlock, 0, stream>>>(p);
     CPMK_LAUNCH_CHECK();
