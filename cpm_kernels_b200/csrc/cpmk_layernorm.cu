@@ -136,6 +136,7 @@ struct LnParams {
 template <int PASS, bool RD_MEAN, bool BIAS>
 __global__ void __launch_bounds__(kLnBlock, PASS == 0 ? 3 : 2) ln_quant_kernel(const LnParams p) {
     __shared__ __align__(16) __half lane_max[kLnRowLanes][kLnWideCols];
+    __shared__ __align__(16) float col_const[PASS == 0 ? 2 : 5][kLnWideCols];      // 1/std, mean; pass C also: r_up, r_dn, scale
     const int t8 = threadIdx.x & (kLnWideCols / 8 - 1), rl = threadIdx.x / (kLnWideCols / 8);
     const int b = blockIdx.z, split = blockIdx.y, batch = gridDim.z;
     const int col = blockIdx.x * kLnWideCols + 8 * t8;
@@ -143,36 +144,41 @@ __global__ void __launch_bounds__(kLnBlock, PASS == 0 ? 3 : 2) ln_quant_kernel(c
     const int r_begin = split * p.rows_per_split;
     const int r_end = min(p.n, r_begin + p.rows_per_split);
 
-    // statistics of the thread's 8 columns: chunk sums accumulated in order, as the reference's outer loop does
-    float mean[8], rstd[8];
+    // Per-column constants are derived once per block: the four row lanes of a column group split its 8 columns,
+    // two each (columns col + 2 rl, col + 2 rl + 1), and share the results through shared memory.
+    const int my2 = 8 * t8 + 2 * rl;                               // first of the thread's two columns, within the strip
+    // statistics: chunk sums accumulated in order, as the reference's outer loop does
     if (col_ok) {
-        float s1[8], s2[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) s1[i] = s2[i] = 0.f;
+        float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
         for (int c = 0; c < p.chunks; ++c) {
-            const float4 *q2 = reinterpret_cast<const float4 *>(p.sums + (((int64_t)batch + b) * p.chunks + c) * p.m + col);
-            const float4 a = __ldg(q2), d = __ldg(q2 + 1);
-            const float t2[8] = {a.x, a.y, a.z, a.w, d.x, d.y, d.z, d.w};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) s2[i] = __fadd_rn(s2[i], t2[i]);
+            const float2 t2 = __ldg(reinterpret_cast<const float2 *>(p.sums + (((int64_t)batch + b) * p.chunks + c) * p.m + col + 2 * rl));
+            s2.x = __fadd_rn(s2.x, t2.x), s2.y = __fadd_rn(s2.y, t2.y);
             if (RD_MEAN) {
-                const float4 *q1 = reinterpret_cast<const float4 *>(p.sums + ((int64_t)b * p.chunks + c) * p.m + col);
-                const float4 e = __ldg(q1), f = __ldg(q1 + 1);
-                const float t1[8] = {e.x, e.y, e.z, e.w, f.x, f.y, f.z, f.w};
-#pragma unroll
-                for (int i = 0; i < 8; ++i) s1[i] = __fadd_rn(s1[i], t1[i]);
+                const float2 t1 = __ldg(reinterpret_cast<const float2 *>(p.sums + ((int64_t)b * p.chunks + c) * p.m + col + 2 * rl));
+                s1.x = __fadd_rn(s1.x, t1.x), s1.y = __fadd_rn(s1.y, t1.y);
             }
         }
         const float fn = (float)p.n;
+        const float sum2[2] = {s2.x, s2.y}, sum1[2] = {s1.x, s1.y};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            float var = __fdiv_rn(s2[i], fn);
-            mean[i] = 0.f;
+        for (int i = 0; i < 2; ++i) {
+            float var = __fdiv_rn(sum2[i], fn), mu = 0.f;
             if (RD_MEAN) {
-                mean[i] = __fdiv_rn(s1[i], fn);
-                var = __fmaf_rn(-mean[i], mean[i], var);
+                mu = __fdiv_rn(sum1[i], fn);
+                var = __fmaf_rn(-mu, mu, var);
             }
-            rstd[i] = rsqrtf(__fadd_rn(var, p.eps));
+            col_const[0][my2 + i] = rsqrtf(__fadd_rn(var, p.eps));
+            if (RD_MEAN) col_const[1][my2 + i] = mu;
+        }
+    }
+    __syncthreads();
+    float mean[8], rstd[8];
+    {
+        const float4 a = *reinterpret_cast<const float4 *>(&col_const[0][8 * t8]), d = *reinterpret_cast<const float4 *>(&col_const[0][8 * t8 + 4]);
+        rstd[0] = a.x, rstd[1] = a.y, rstd[2] = a.z, rstd[3] = a.w, rstd[4] = d.x, rstd[5] = d.y, rstd[6] = d.z, rstd[7] = d.w;
+        if (RD_MEAN) {
+            const float4 e = *reinterpret_cast<const float4 *>(&col_const[1][8 * t8]), f = *reinterpret_cast<const float4 *>(&col_const[1][8 * t8 + 4]);
+            mean[0] = e.x, mean[1] = e.y, mean[2] = e.z, mean[3] = e.w, mean[4] = f.x, mean[5] = f.y, mean[6] = f.z, mean[7] = f.w;
         }
     }
 
@@ -229,41 +235,43 @@ __global__ void __launch_bounds__(kLnBlock, PASS == 0 ? 3 : 2) ln_quant_kernel(c
         return;
     }
 
-    // PASS 1: fold the maxima of the row ranges, derive the scales, round
-    if (!col_ok) return;
-    __half2 m2[4];
+    // PASS 1: fold the maxima of the row ranges, derive the scales and multipliers (two columns per thread), round
+    if (col_ok) {
+        __half2 mx = __float2half2_rn(0.f);
+        const __half *part = p.amax_partial + (int64_t)b * p.m + col + 2 * rl;
+        for (int sp0 = 0; sp0 < p.splits; sp0 += 8) {              // eight independent loads at a time
+            unsigned v[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) m2[j] = __float2half2_rn(0.f);
-    for (int sp0 = 0; sp0 < p.splits; sp0 += 8) {              // eight independent loads at a time
-        uint4 v[8];
+            for (int u = 0; u < 8; ++u)
+                v[u] = sp0 + u < p.splits ? __ldg(reinterpret_cast<const unsigned *>(part + (int64_t)(sp0 + u) * batch * p.m)) : 0u;
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
-            v[u] = sp0 + u < p.splits ? __ldg(reinterpret_cast<const uint4 *>(p.amax_partial + ((int64_t)(sp0 + u) * batch + b) * p.m + col))
-                                      : make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const __half2 *h = reinterpret_cast<const __half2 *>(&v[u]);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) m2[j] = __hmax2(h[j], m2[j]);
+            for (int u = 0; u < 8; ++u) mx = __hmax2(*reinterpret_cast<const __half2 *>(&v[u]), mx);
         }
+        const float2 a = __half22float2(mx);
+        const float amax[2] = {a.x, a.y};
+        __half sh[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            sh[i] = scale_from_amax(amax[i]);
+            const float sf = __half2float(sh[i]);
+            float up, dn;
+            cpmk_round_prepare(sf, &up, &dn);
+            // a column outside the rule's domain gets a NaN multiplier: its elements then fail the agreement test below
+            if (!(cpmk_scale_in_domain(sf) && cpmk_round_domain_ok(amax[i], up))) up = __int_as_float(0x7fc00000);
+            col_const[2][my2 + i] = up;
+            col_const[3][my2 + i] = dn;
+            col_const[4][my2 + i] = sf;
+        }
+        if (split == 0) *reinterpret_cast<__half2 *>(p.scale + (int64_t)b * p.m + col + 2 * rl) = __halves2half2(sh[0], sh[1]);
     }
-    float s[8];
+    __syncthreads();
+    if (!col_ok) return;
     float2 ru[4], rd[4];
-    __align__(16) __half sh[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        const float2 a = __half22float2(m2[j]);
-        sh[2 * j] = scale_from_amax(a.x);
-        sh[2 * j + 1] = scale_from_amax(a.y);
-        s[2 * j] = __half2float(sh[2 * j]);
-        s[2 * j + 1] = __half2float(sh[2 * j + 1]);
-        cpmk_round_prepare(s[2 * j], &ru[j].x, &rd[j].x);
-        cpmk_round_prepare(s[2 * j + 1], &ru[j].y, &rd[j].y);
-        // a column outside the rule's domain gets a NaN multiplier: its elements then fail the agreement test below
-        if (!(cpmk_scale_in_domain(s[2 * j]) && cpmk_round_domain_ok(a.x, ru[j].x))) ru[j].x = __int_as_float(0x7fc00000);
-        if (!(cpmk_scale_in_domain(s[2 * j + 1]) && cpmk_round_domain_ok(a.y, ru[j].y))) ru[j].y = __int_as_float(0x7fc00000);
+        ru[j] = *reinterpret_cast<const float2 *>(&col_const[2][8 * t8 + 2 * j]);
+        rd[j] = *reinterpret_cast<const float2 *>(&col_const[3][8 * t8 + 2 * j]);
     }
-    if (split == 0 && rl == 0) *reinterpret_cast<uint4 *>(p.scale + (int64_t)b * p.m + col) = *reinterpret_cast<const uint4 *>(sh);
     int8_t *obase = p.out + (int64_t)b * p.n * p.m + col;
     const float2 magic = make_float2(CPMK_ROUND_MAGIC, CPMK_ROUND_MAGIC);
     constexpr int kRowsInFlight = 4;
@@ -311,8 +319,8 @@ __global__ void __launch_bounds__(kLnBlock, PASS == 0 ? 3 : 2) ln_quant_kernel(c
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const float2 f = __half22float2(y[j]);
-                        bits[2 * j] = (uint8_t)round_reference(f.x, s[2 * j]);
-                        bits[2 * j + 1] = (uint8_t)round_reference(f.y, s[2 * j + 1]);
+                        bits[2 * j] = (uint8_t)round_reference(f.x, col_const[4][8 * t8 + 2 * j]);
+                        bits[2 * j + 1] = (uint8_t)round_reference(f.y, col_const[4][8 * t8 + 2 * j + 1]);
                     }
                 }
             }
