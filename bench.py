@@ -3,24 +3,35 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (N = 1): the four CPM-Bee-10B layer linears at M = 4096 tokens (fused QKV 12288x4096, attention-out
-4096x4096, FFN-in 10240x4096, FFN-out 4096x10240), fp16 activations N(0,1) and weights N(0,0.02), seeded
-synthetic data.  One step = one pass over the four linears through the public entry point
-``cpm_kernels_b200.torch.bmm(x, False, W, True, int8=True)``, which -- like the reference's bmm -- quantises
-BOTH operands on every call (per-row absmax scale + int8 rounding), runs the int8 GEMM and dequantises to fp16:
-two kernels per linear (both operands quantised in one launch, then the GEMM), eight per step.  ``value`` counts 2*M*N*K operations of the four GEMMs over the whole
-step time (quantisation passes included), inputs resident in HBM.  ``e2e`` is the same step driven from pinned
-host buffers: activations copied host->device and fp16 outputs device->host inside the timed region.
+Workload: the four CPM-Bee-10B layer linears at M = 4096 tokens (fused QKV 12288x4096, attention-out 4096x4096, FFN-in
+10240x4096, FFN-out 4096x10240), fp16 activations N(0,1) and weights N(0,0.02), seeded synthetic data.  One step = one
+pass over the four linears; like the reference's bmm, every call quantises BOTH operands (per-row absmax scale + int8
+rounding), runs the int8 GEMM and dequantises to fp16: two kernels per linear, eight per step.  ``value`` counts
+2*M*N*K operations of the four GEMMs over the whole step time (quantisation passes included), inputs resident in HBM.
 
-N > 1 (torchrun, one rank per GPU): the same linears column-parallel -- each rank holds N/g rows of every weight,
-quantises its shard, computes its output slice, and the slices are all-gathered over NCCL ("strong" scaling).
+N = 1: the public entry point ``cpm_kernels_b200.torch.bmm(x, False, W, True, int8=True)``.
+N > 1 (torchrun, one rank per GPU): the same linears column-parallel ("strong" scaling) -- each rank holds N/g rows of
+every weight, computes its output columns, and the GEMM's epilogue stores them into every rank's full-width result over
+NVLink (``cpm_kernels_b200.sharded``); after the timed region every rank recomputes the unsharded linears and compares
+bit for bit (``parity``).
+
+``e2e`` drives the same step from pinned host buffers, copies inside the timed region.  At N > 1 every rank owns M/g
+tokens end to end: it uploads its rows, quantises them once (the quantising kernel stores the int8 codes into every
+rank's buffer), and downloads its rows of the results.
+
+Beside them in the same line: ``roofline`` (the GEMM kernel alone, CUDA events around its launches), ``cfg5`` (the 48-layer
+stack at M = 16384: GEMM-phase rate, end-to-end rate with the exchange, NVLink GB/s), ``sustained`` (the step looped for
+two seconds with the clock sampled), ``reference_cuda`` (the reference's own six-launch CUDA pipeline, timed in the same
+process on the same tensors), ``cpu_baseline`` (the reference's test formula on the host cores, the whole workload),
+``gemv`` (decode GEMV GB/s) and ``other_configs``.
 
 ``--impl reference`` times the reference's own arithmetic on the host CPU: the torch expressions its unit tests
-hold the kernels to (oracle/test_formula.py), on a bounded sample of the same workload, with all host threads.
+hold the kernels to (oracle/test_formula.py), on the same workload, with all host threads.
 """
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -115,48 +126,75 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
-# CPU baseline: the reference's test formula on host cores (bounded sample)
+# DRAM traffic of the dominant kernel, from the tracked record of the profiler capture it came from
 # ------------------------------------------------------------------------------------------------
-CPU_SAMPLE_TOKENS = 1024
+TRAFFIC_RECORD = os.path.join(ROOT, "profiles", "gemm_i8_tc2_kernel_cpm-bee-linears_M4096.dram_traffic.txt")
 
 
-def cpu_baseline(repeats: int = 2) -> dict:
+def read_dram_traffic() -> dict:
+    """``{"bytes_per_launch": mean over the four GEMM launches, "per_shape": {...}, "captured": ..., "source": file}`` from
+    the record beside the profile summary; ``None`` values when the record is missing or does not parse (never a
+    built-in number)."""
+    out = {"bytes_per_launch": None, "per_shape": None, "captured": None, "source": os.path.relpath(TRAFFIC_RECORD, ROOT)}
+    try:
+        fields = {}
+        for line in open(TRAFFIC_RECORD):
+            if ":" in line and not line.lstrip().startswith("#"):
+                key, val = line.split(":", 1)
+                fields[key.strip()] = val.strip()
+        per = {}
+        for item in fields["dram_bytes_per_launch"].split():
+            name, val = item.split("=")
+            per[name] = float(val)
+        if sorted(per) == sorted(name for name, _, _ in SHAPES):
+            out["per_shape"] = per
+            out["bytes_per_launch"] = sum(per.values()) / len(per)
+            out["captured"] = fields.get("captured")
+    except Exception:
+        pass
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline: the reference's test formula on host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_baseline(passes: int = 2, tokens: int | None = None) -> dict:
+    """The four linears at ``tokens`` (default: the workload's) through the reference's test formula in torch CPU
+    fp32 on all host cores; one warm-up pass, then the MEAN of ``passes`` passes (the statistic of the measured arm)."""
     import torch
     from oracle import test_formula
+    tokens = M_TOKENS if tokens is None else tokens
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     g = torch.Generator(device="cpu").manual_seed(0)
-    best = None
-    ops = total_ops(CPU_SAMPLE_TOKENS)
     data = []
     for _, n, k in SHAPES:
-        x = torch.randn((1, CPU_SAMPLE_TOKENS, k), generator=g).half()
+        x = torch.randn((1, tokens, k), generator=g).half()
         w = (torch.randn((1, n, k), generator=g) * 0.02).half()
         data.append((x, w))
-    for _ in range(repeats + 1):                      # first pass is the warm-up
+    times = []
+    for _ in range(passes + 1):                       # first pass is the warm-up
         t0 = time.perf_counter()
         for x, w in data:
             test_formula.real_bmm(x, False, w, True, True)
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    return {"value": ops / best / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": "the same four linears at M=%d tokens (1/%d of the workload), reference test formula "
-                      "(tests/test_gemm.py:8-41) in torch CPU fp32, best of %d passes, %.2f s per pass" %
-                      (CPU_SAMPLE_TOKENS, M_TOKENS // CPU_SAMPLE_TOKENS, repeats, best),
-            "seconds_per_pass": best}
+        times.append(time.perf_counter() - t0)
+    mean = sum(times[1:]) / len(times[1:])
+    return {"value": total_ops(tokens) / mean / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": "the whole workload: the same four linears at M=%d tokens, reference test formula (tests/test_gemm.py:8-41) "
+                      "in torch CPU fp32, mean of %d passes after one warm-up, %.2f s per pass" % (tokens, passes, mean),
+            "seconds_per_pass": mean, "tokens": tokens}
 
 
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 3))
-    base = cpu_baseline(repeats=steps)
+    base = cpu_baseline(passes=max(1, min(args.steps, 3)), tokens=M_TOKENS)
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": base["seconds_per_pass"] * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample_tokens": CPU_SAMPLE_TOKENS},
+        "config": {"workload": workload_name(), "tokens": M_TOKENS},
         "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -164,188 +202,271 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
+def workload_name() -> str:
+    return WORKLOAD if M_TOKENS == 4096 else WORKLOAD + " [REDUCED to %d tokens: profiling case, not a bench value]" % M_TOKENS
+
+
 # ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
+class Run:
+    """Process-wide state of one benchmark run: device, ranks, streams, timing helpers."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist, self.args = torch, dist, args
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        self.saved_stdout = None
+        if self.world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            # libraries print banners on stdout when a communicator is created: keep stdout for the one JSON line
+            sys.stdout.flush()
+            self.saved_stdout = os.dup(1)
+            os.dup2(2, 1)
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.stream = torch.cuda.current_stream()
+        self.peaks = measured_peaks()
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, value: float) -> float:
+        if self.world == 1:
+            return float(value)
+        t = self.torch.tensor([value], device=self.dev, dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(self, value: int) -> int:
+        if self.world == 1:
+            return int(value)
+        t = self.torch.tensor([value], device=self.dev, dtype=self.torch.int64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return int(t.item())
+
+    def timed(self, fn, iters: int, warm: int = 0) -> float:
+        """Milliseconds per call of ``fn`` over ``iters`` calls: CUDA events on the main stream between two rank
+        barriers, max over ranks."""
+        for _ in range(warm):
+            fn()
+        e0, e1 = self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        e0.record(self.stream)
+        for _ in range(iters):
+            fn()
+        e1.record(self.stream)
+        self.barrier()
+        return self.max_over_ranks(e0.elapsed_time(e1) / iters)
+
+    def emit(self, line: dict):
+        if self.saved_stdout is not None:
+            sys.stdout.flush()
+            os.dup2(self.saved_stdout, 1)
+            os.close(self.saved_stdout)
+            self.saved_stdout = None
+        print(json.dumps(line), flush=True)
+
+
+class Lanes:
+    """The linears of the synthetic stack are independent, so they are spread over several streams: while one linear's
+    GEMM drains its output over NVLink, the others' quantisation passes and GEMMs run beside it (the scattering GEMM's
+    persistent grid leaves part of the SMs free for that)."""
+
+    def __init__(self, run: Run, n_lanes: int, sm_margin: int):
+        from cpm_kernels_b200.library import cpmk
+        self.run, self.cpmk, self.sm_margin = run, cpmk, sm_margin
+        self.side = [run.torch.cuda.Stream() for _ in range(max(0, n_lanes - 1))]
+
+    def __len__(self):
+        return len(self.side) + 1
+
+    def fork(self):
+        for s in self.side:
+            s.wait_stream(self.run.stream)
+        if self.side:
+            self.cpmk.set_gemm_sm_margin(self.sm_margin)
+
+    def on(self, i: int):
+        lane = i % len(self)
+        return self.run.torch.cuda.stream(self.side[lane - 1]) if lane else contextlib.nullcontext()
+
+    def join(self):
+        for s in self.side:
+            self.run.stream.wait_stream(s)
+        if self.side:
+            self.cpmk.set_gemm_sm_margin(-1)
+
+
+def cfg2_tensors(run: Run, want_full_weights: bool = False):
+    """Activations (1, M, K) for the four linears, on every rank, and either this rank's rows of each weight or (for
+    the parity check) the full weights: the same device generator sequence in both cases."""
+    torch = run.torch
+    from cpm_kernels_b200.sharded import shard_bounds
+    gen = torch.Generator(device=run.dev).manual_seed(0)
+    xs, ws = [], []
+    for _, n, k in SHAPES:
+        assert n % run.world == 0
+        x = torch.randn((1, M_TOKENS, k), generator=gen, device=run.dev).half()
+        w_full = (torch.randn((1, n, k), generator=gen, device=run.dev) * 0.02).half()
+        if want_full_weights:
+            ws.append(w_full)
+        else:
+            xs.append(x)
+            lo, hi = shard_bounds(n, run.world, run.rank)
+            ws.append(w_full[:, lo:hi, :].contiguous())
+        del w_full
+    return xs, ws, gen
+
+
+def count_mismatches(torch, got, want) -> int:
+    return int((got.view(torch.int16) != want.view(torch.int16)).sum().item())
+
+
 def run_ours(args) -> None:
-    import torch
-    import torch.distributed as dist
+    run = Run(args)
+    torch, dist = run.torch, run.dist
     import cpm_kernels_b200.torch as ct
     import cpm_kernels_b200.kernels as ck
     from cpm_kernels_b200.library import cpmk
-    from cpm_kernels_b200.sharded import shard_bounds
+    from cpm_kernels_b200.sharded import (ColumnParallelInt8Linear, FusedColumnParallelInt8Linear, SymmetricArena, ExchangeBuffers)
+    from cpm_kernels_b200.torch.gemm import quantize, gemm_and_scale
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    saved_stdout = None
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # libraries print banners on stdout when a communicator is created: keep stdout for the one JSON line
-        sys.stdout.flush()
-        saved_stdout = os.dup(1)
-        os.dup2(2, 1)
-        dist.init_process_group("nccl", device_id=dev)
+    world, rank, dev, stream, peaks = run.world, run.rank, run.dev, run.stream, run.peaks
     cpmk.check_device()
-    peaks = measured_peaks()
+    xs, ws, gen = cfg2_tensors(run)
+    warmup = max(args.warmup, 3)
 
-    # ---- data: activations replicated, weights sharded along N (rank r holds rows [r*N/g, (r+1)*N/g)) ----
-    gen = torch.Generator(device=dev).manual_seed(0)
-    xs, ws, outs, gathered = [], [], [], []
-    for _, n, k in SHAPES:
-        assert n % world == 0
-        xs.append(torch.randn((1, M_TOKENS, k), generator=gen, device=dev).half())
-        w_full = (torch.randn((1, n, k), generator=gen, device=dev) * 0.02).half()
-        lo, hi = shard_bounds(n, world, rank)
-        ws.append(w_full[:, lo:hi, :].contiguous())
-        del w_full
-        if world > 1:
-            gathered.append(torch.empty((world, M_TOKENS, n // world), dtype=torch.half, device=dev))
-    stream = torch.cuda.current_stream()
-    comm_stream = torch.cuda.Stream() if world > 1 else None
-    from cpm_kernels_b200.sharded import ColumnParallelInt8Linear, FusedColumnParallelInt8Linear
-    layers = [ColumnParallelInt8Linear(w) for w in ws] if world > 1 else None
-    # preferred exchange: the GEMM epilogue stores each rank's output slice into every rank's full-width output
-    # (peer-mapped symmetric memory); falls back to an NCCL all-gather beside the GEMM if that cannot be set up
-    fused_layers, exchange, fused_two_streams = None, "none", False
-    fused_margin = os.environ.get("CPMK_BENCH_FUSED_SM_MARGIN", "32")
-    n_side = max(1, int(os.environ.get("CPMK_BENCH_FUSED_STREAMS", "4")) - 1)
-    side_streams = ([comm_stream] + [torch.cuda.Stream() for _ in range(n_side - 1)]) if world > 1 else []
+    # ---- N > 1: peer-mapped buffers and the layers whose GEMM epilogue is the all-gather ----
+    arena = layers = lanes = None
+    nccl_layers, gathered, comm_stream = None, [], None
+    exchange = "none"
+    want_cfg5 = not args.kernels_only and not args.no_cfg5 and M_TOKENS == 4096
     if world > 1:
-        exchange = "nccl all_gather_into_tensor on a side stream"
-        if args.exchange in ("fused", "fused1"):
-            try:
-                fused_layers = [FusedColumnParallelInt8Linear(w) for w in ws]
-                for fl in fused_layers:
-                    fl._buffer(M_TOKENS)
-                exchange = "fused: GEMM epilogue TMA-stores its slice into every rank's output over NVLink"
-            except Exception as e:                       # noqa: BLE001
-                sys.stderr.write("fused exchange unavailable (%s); using the NCCL all-gather\n" % (e,))
-                fused_layers = None
-        if fused_layers is None:
-            # the collective's kernels run beside the persistent GEMM grid: leave them a few SMs
-            os.environ.setdefault("CPMK_GEMM_SM_MARGIN", "16")
-        elif args.exchange == "fused":
-            fused_two_streams = True
-            exchange += "; the linears run on %d streams, scatter GEMM grids leave %s SMs free" % (n_side + 1, fused_margin)
+        nbytes = sum(ExchangeBuffers.nbytes(M_TOKENS, k, n) for _, n, k in SHAPES)
+        if want_cfg5:
+            nbytes += sum(ExchangeBuffers.nbytes(CFG5_TOKENS, k, n) for _, n, k in SHAPES)
+        arena = SymmetricArena(nbytes + (1 << 20), dev)
+        bufs = [ExchangeBuffers(arena, M_TOKENS, k, n) for _, n, k in SHAPES]
+        layers = [FusedColumnParallelInt8Linear(w, buffers=b) for w, b in zip(ws, bufs)]
+        n_lanes = int(os.environ.get("CPMK_BENCH_FUSED_STREAMS", "4")) if args.exchange != "fused1" else 1
+        lanes = Lanes(run, n_lanes, int(os.environ.get("CPMK_BENCH_FUSED_SM_MARGIN", "32")))
+        exchange = ("fused: the GEMM epilogue TMA-stores its output columns into every rank's full-width result over NVLink; activations present "
+                    "on every rank; linears on %d streams, scattering GEMM grids leave %d SMs free; one rank barrier per step; results alternate "
+                    "between two buffers" % (len(lanes), lanes.sm_margin))
+        if args.exchange == "nccl":
+            nccl_layers = [ColumnParallelInt8Linear(w) for w in ws]
+            gathered = [torch.empty((world, M_TOKENS, n // world), dtype=torch.half, device=dev) for _, n, _ in SHAPES]
+            comm_stream = torch.cuda.Stream()
+            os.environ.setdefault("CPMK_GEMM_SM_MARGIN", "16")       # the collective's kernels run beside the persistent GEMM grid
+            exchange = "nccl all_gather_into_tensor on a side stream"
 
-    gemm_events = []
+    step_no = [0]
 
-    def step(record_gemm: bool = False, gather: bool = True):
-        """The four linears through the public API.  With record_gemm, CUDA events bracket each GEMM launch."""
-        results = []
-        if fused_layers is not None and gather and not record_gemm:
-            # The linears of the synthetic stack are independent, so they are spread over several streams: while one
-            # linear's GEMM drains its output over NVLink, the others' quantisation passes and GEMMs run beside it
-            # (the scatter GEMM's persistent grid leaves part of the SMs free for that: CPMK_GEMM_SM_MARGIN).
-            if fused_two_streams:
-                for s2 in side_streams:
-                    s2.wait_stream(stream)
-                cpmk.set_gemm_sm_margin(int(fused_margin))
-            for i, (fl, x) in enumerate(zip(fused_layers, xs)):
-                lane = i % (len(side_streams) + 1) if fused_two_streams else 0
-                if lane:
-                    with torch.cuda.stream(side_streams[lane - 1]):
-                        results.append(fl(x))
-                else:
-                    results.append(fl(x))
-            if fused_two_streams:
-                for s2 in side_streams:
-                    stream.wait_stream(s2)
-                cpmk.set_gemm_sm_margin(-1)
-            return results
-        for i, (x, w) in enumerate(zip(xs, ws)):
-            if record_gemm:
-                # same three launches as ct.bmm, spelled out so that events can bracket the GEMM kernel alone
-                from cpm_kernels_b200.torch.gemm import quantize, gemm_and_scale
-                sa, qa = quantize(x, False)
-                sb, qb = quantize(w, False)
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                y = gemm_and_scale(qa, sa, qb, sb, False, True)
-                e1.record(stream)
-                gemm_events.append((i, e0, e1))
-            else:
+    def step(only_local: bool = False):
+        """One pass over the four linears.  N = 1: the public bmm.  N > 1: one library call per linear (quantise both
+        operands + scattering GEMM), one rank barrier per step.  only_local: the same without the exchange."""
+        if world == 1:
+            return [ct.bmm(x, False, w, True, int8=True) for x, w in zip(xs, ws)]
+        if nccl_layers is not None:
+            out = []
+            for i, (x, w) in enumerate(zip(xs, ws)):
                 y = ct.bmm(x, False, w, True, int8=True)
-            if world > 1 and gather:
-                ev = torch.cuda.Event()
-                ev.record(stream)
-                with torch.cuda.stream(comm_stream):
-                    comm_stream.wait_event(ev)
-                    layers[i].gather(y, out=gathered[i])
-                y.record_stream(comm_stream)
-            results.append(y)
-        if world > 1 and gather:
-            stream.wait_stream(comm_stream)
-        return results
+                if not only_local:
+                    ev = torch.cuda.Event()
+                    ev.record(stream)
+                    with torch.cuda.stream(comm_stream):
+                        comm_stream.wait_event(ev)
+                        nccl_layers[i].gather(y, out=gathered[i])
+                    y.record_stream(comm_stream)
+                out.append(y)
+            if not only_local:
+                stream.wait_stream(comm_stream)
+            return out
+        slot = step_no[0] & 1
+        step_no[0] += 1
+        lanes.fork()
+        out = []
+        for i, (layer, x) in enumerate(zip(layers, xs)):
+            with lanes.on(i):
+                out.append(layer.launch(x, slot, only_local))
+        lanes.join()
+        if not only_local:
+            arena.barrier(1)
+        return out
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(warmup):
         step()
-    barrier()
+    run.barrier()
     assert cpmk.last_gemm_path() == 1, "the tensor-core GEMM kernel was not selected"
 
-    sampler = ClockSampler(local_rank)
+    # ---- timed region: exactly K steps, device time, max over ranks ----
+    sampler = ClockSampler(run.local_rank)
     if rank == 0:
         sampler.start()
-    # ---- timed region: exactly K steps, device time, max over ranks ----
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record(stream)
+    ms_per_step = run.timed(step, args.steps)
+    value = total_ops() / (ms_per_step * 1e-3) / 1e12
+
+    # ---- the GEMM kernel alone: events around each GEMM launch of the same step (at N > 1 with the scatter to every rank
+    #      active, on one stream, one barrier per step) ----
+    gemm_events = []
+
+    def step_recorded():
+        slot = step_no[0] & 1
+        step_no[0] += 1
+        for i, (x, w) in enumerate(zip(xs, ws)):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if world == 1 or nccl_layers is not None:
+                sa, qa = quantize(x, False)
+                sb, qb = quantize(w, False)
+                e0.record(stream)
+                gemm_and_scale(qa, sa, qb, sb, False, True)
+                e1.record(stream)
+            else:
+                layer, buf = layers[i], layers[i].buffers
+                ck.gemm_quantize_rows_pair(1, M_TOKENS, x.data_ptr(), buf.sx[slot].data_ptr(), buf.qx[slot].data_ptr(), 1, layer.n_local,
+                                           w.data_ptr(), layer.scale_w.data_ptr(), layer.q_w.data_ptr(), layer.k, stream.cuda_stream)
+                e0.record(stream)
+                layer.gemm(M_TOKENS, slot)
+                e1.record(stream)
+            gemm_events.append((i, e0, e1))
+        if layers is not None and nccl_layers is None:
+            arena.barrier(1)
+
     for _ in range(args.steps):
-        step()
-    e1.record(stream)
-    barrier()
-    ms_total = e0.elapsed_time(e1)
-    # ---- same region again with events around each GEMM launch: per-kernel duration for the roofline
-    #      (without the all-gather, whose copy kernels would otherwise share the SMs with the GEMM being timed) ----
-    for _ in range(args.steps):
-        step(record_gemm=True, gather=False)
-    barrier()
+        step_recorded()
+    run.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+
     phases = None
     if world > 1:
-        # compute phase alone (no exchange), to separate GEMM-phase scaling from the NVLink-bound gather
-        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        p0.record(stream)
-        for _ in range(args.steps):
-            step(gather=False)
-        p1.record(stream)
-        barrier()
-        t = torch.tensor([p0.elapsed_time(p1) / args.steps], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_compute = float(t.item())
+        ms_compute = run.timed(lambda: step(only_local=True), args.steps, warm=1)
         gather_bytes = sum(2 * M_TOKENS * n for _, n, _ in SHAPES) * (world - 1) // world
         phases = {"compute_only_ms_per_step": ms_compute, "compute_only_tops": total_ops() / (ms_compute * 1e-3) / 1e12,
                   "allgather_bytes_received_per_rank_per_step": gather_bytes,
+                  "nvlink_ingress_GBps_per_rank": gather_bytes / (ms_per_step * 1e-3) / 1e9, "nvlink_nominal_GBps": 900.0,
                   "note": "the all-gather of fp16 outputs moves (g-1)/g * 2*M*N bytes into every rank per linear and bounds the step for g >= 2"}
-    clocks = sampler.stop() if rank == 0 else None
-    if world > 1:
-        t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_per_step = ms_total / args.steps
-    value = total_ops() / (ms_per_step * 1e-3) / 1e12
 
     per_shape_ms = {}
     for i, a, b in gemm_events:
         per_shape_ms.setdefault(i, []).append(a.elapsed_time(b))
     gemm_ms = sum(statistics.mean(v) for v in per_shape_ms.values())
-    gemm_ops = total_ops() / world
-    gemm_tops = gemm_ops / (gemm_ms * 1e-3) / 1e12
+    gemm_tops = total_ops() / world / (gemm_ms * 1e-3) / 1e12
     peak_tops = 2.0 * peaks["bf16_tflops"]
+    traffic = read_dram_traffic()
     roofline = {
         "bound": "tensor", "achieved": gemm_tops, "peak": peak_tops, "unit": "TOPS", "frac": gemm_tops / peak_tops,
-        # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of these four launches at N = 1
-        # (profiles/gemm_i8_tc2_kernel_cpm-bee-linears_M4096.md): 131.0 / 36.8 / 104.9 / 133.2 MB, mean of the four
-        "traffic": 101.5e6 if (world == 1 and M_TOKENS == 4096) else None,
+        "traffic": traffic["bytes_per_launch"] if (world == 1 and M_TOKENS == 4096) else None,
+        "traffic_record": {k: traffic[k] for k in ("source", "captured", "per_shape")},
         "kernel": "gemm_i8_tc2_kernel<dequant> (tcgen05.mma cta_group::2 kind::i8, 256x256 tiles per CTA pair)",
+        "timed": "CUDA events around each GEMM launch of the step" + ("" if world == 1 else
+                 ("; exchange on: the epilogue stores to all %d ranks, one stream" % world if nccl_layers is None else "; exchange off (NCCL gathers afterwards)")),
         "peak_note": "2 x %s dense bf16 %s TFLOP/s (burst; no int8 figure is measured on this pool); nominal dense int8 is 4500 TOPS: frac_nominal below"
                      % (peaks["source"], peaks["bf16_tflops"]),
         "frac_nominal": gemm_tops / 4500.0,
@@ -353,110 +474,57 @@ def run_ours(args) -> None:
                            for i, v in sorted(per_shape_ms.items())},
     }
 
+    # ---- parity of the sharded path, outside the timed region: every rank recomputes the unsharded linears locally and
+    #      compares its full-width results (which the peers' epilogues wrote) bit for bit ----
+    parity = {"checked": False, "note": "one GPU: nothing is exchanged; parity is the GPU test suite's job"}
+    if world > 1 and nccl_layers is None:
+        _, w_full, _ = cfg2_tensors(run, want_full_weights=True)
+        ys = step()
+        run.barrier()
+        bad = 0
+        for i in range(len(SHAPES)):
+            want = ct.bmm(xs[i], False, w_full[i], True, int8=True)
+            bad += count_mismatches(torch, ys[i], want)
+            del want
+        parity = {"checked": True, "mismatches": run.sum_over_ranks(bad), "elements_compared_per_rank": sum(M_TOKENS * n for _, n, _ in SHAPES),
+                  "what": "full-width y of the four linears on every rank (activations present in full) against the unsharded bmm computed locally"}
+
     # ---- e2e: pinned host activations in, fp16 outputs out, every step ----
     e2e = None
     if not args.kernels_only:
-        host_x = [x.cpu().pin_memory() for x in xs]
-        host_y = [torch.empty((1, M_TOKENS, w.shape[1]), dtype=torch.half).pin_memory() for w in ws]
-        h2d = sum(t.numel() * 2 for t in host_x)
-        d2h = sum(t.numel() * 2 for t in host_y)
-        copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
-        # two sets of device input buffers: the uploads of step s+1 run while step s still computes and downloads
-        # (PCIe is full duplex), and wait only for the compute of step s-1, which read the set they overwrite
-        dev_x = [[torch.empty_like(x) for x in xs] for _ in range(2)]
-        consumed = [None, None]                      # per buffer set: event after the last GEMM that read it
-        step_no = [0]
-
-        def e2e_step():
-            # three-stage pipeline over the four linears: upload(i+1) || compute(i) || download(i-1)
-            cur = step_no[0] & 1
-            step_no[0] += 1
-            ups = []
-            with torch.cuda.stream(copy_in):
-                if consumed[cur] is not None:
-                    copy_in.wait_event(consumed[cur])
+        if world == 1 or nccl_layers is not None:
+            e2e = measure_e2e_single(run, xs, ws, ct)
+        else:
+            e2e = measure_e2e_sharded(run, xs, layers, lanes, arena)
+            if parity.get("checked"):
+                # the e2e path is the other form of the layer (row-sharded activations, codes gathered by the quantiser's stores)
+                bad = 0
+                lo, hi = rank * (M_TOKENS // world), (rank + 1) * (M_TOKENS // world)
                 for i in range(len(SHAPES)):
-                    dev_x[cur][i].copy_(host_x[i], non_blocking=True)
-                    ev = torch.cuda.Event()
-                    ev.record(copy_in)
-                    ups.append(ev)
-            for i in range(len(SHAPES)):
-                stream.wait_event(ups[i])
-                y = ct.bmm(dev_x[cur][i], False, ws[i], True, int8=True)
-                done = torch.cuda.Event()
-                done.record(stream)
-                with torch.cuda.stream(copy_out):
-                    copy_out.wait_event(done)
-                    host_y[i].copy_(y, non_blocking=True)
-                y.record_stream(copy_out)
-            consumed[cur] = done
+                    want = ct.bmm(xs[i], False, w_full[i], True, int8=True)[:, lo:hi, :].cpu()
+                    bad += count_mismatches(torch, e2e["_host_y"][i], want)
+                parity["e2e_mismatches"] = run.sum_over_ranks(bad)
+                parity["e2e_what"] = "each rank's downloaded rows of y (row-sharded activations, int8 codes all-gathered by the quantising kernel) against the unsharded bmm"
+            e2e.pop("_host_y", None)
+    if world > 1 and nccl_layers is None:
+        del w_full
 
-        for _ in range(2):
-            e2e_step()
-        barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        n_e2e = max(3, min(args.steps, 10))
-        a.record(stream)
-        copy_in.wait_event(a)                         # nothing of the timed steps starts before the first event
-        for _ in range(n_e2e):
-            e2e_step()
-        stream.wait_stream(copy_out)                  # the last step's results have reached the host
-        b.record(stream)
-        barrier()
-        ms_e2e = a.elapsed_time(b) / n_e2e
-        if world > 1:
-            t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms_e2e = float(t.item())
-        e2e = {"value": total_ops() / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": ms_e2e,
-               "note": "activations uploaded from pinned host memory and this rank's fp16 outputs downloaded every step, "
-                       "copies pipelined against compute on separate streams; weights stay resident"}
-        del host_x, host_y, dev_x
-
-    # ---- secondary metric of the path: decode GEMV HBM GB/s (weight 10240x4096 and its transpose, batch 1) ----
-    gemv = None
+    # ---- N = 1 extras: sustained run, the reference's CUDA pipeline, decode GEMV, the other configurations ----
+    sustained = reference_cuda = gemv = other = None
+    if rank == 0 and world == 1 and not args.kernels_only:
+        sustained = measure_sustained(run, step, xs, ws, ms_per_step)
+        reference_cuda = measure_reference_cuda(run, xs, ws, ct, ms_per_step, roofline["per_shape_tops"])
     if rank == 0 and not args.kernels_only:
-        gemv = {}
-        gs = torch.cuda.Stream()                         # capture stream; warmed up first so that the library's
-        s = gs.cuda_stream                               # per-stream workspace exists before capture begins
-        for batch in (1, 4, 16):
-            nbuf = max(1, 4 // batch)                    # at least 4 x 84 MB of weights rotate: larger than L2
-            mats = [(torch.randn((batch, 10240, 4096), generator=gen, device=dev) * 0.02).half() for _ in range(nbuf)]
-            vec_in = torch.randn((batch, 4096), generator=gen, device=dev).half()
-            y_rows = torch.empty((batch, 10240), dtype=torch.half, device=dev)
-            # the transposed weight [4096, 10240] = (dim_in, dim_out): the same buffers, read with the other shape
-            for name, fn in (("gemv_fp16", lambda j: ck.gemv_fp16(batch, 10240, 4096, mats[j].data_ptr(), vec_in.data_ptr(), y_rows.data_ptr(), s)),
-                             ("gemv_fp16_transpose", lambda j: ck.gemv_fp16_transpose(batch, 10240, 4096, mats[j].data_ptr(), vec_in.data_ptr(), y_rows.data_ptr(), s))):
-                gs.wait_stream(stream)
-                with torch.cuda.stream(gs):
-                    for j in range(nbuf):
-                        fn(j)
-                gs.synchronize()
-                reps = max(2, 20 // (nbuf * batch))
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=gs):
-                    for j in range(nbuf * reps):
-                        fn(j % nbuf)
-                graph.replay()
-                torch.cuda.synchronize()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                graph.replay()
-                b.record()
-                torch.cuda.synchronize()
-                sec = a.elapsed_time(b) * 1e-3 / (nbuf * reps)
-                bytes_alg = batch * (2 * 10240 * 4096 + 2 * (10240 + 4096))
-                gemv["%s_batch%d" % (name, batch)] = {"GBps": bytes_alg / sec / 1e9, "us": sec * 1e6,
-                                                     "frac_of_hbm_peak": bytes_alg / sec / 1e9 / peaks["hbm_gbs"]}
-            del mats
-        mats = None
-        del mats
-
-    # ---- the other configurations of the path: attention-score bmm, fp16 bmm, quantisation passes, GELU ----
-    other = None
+        gemv = measure_gemv(run, gen, ck)
     if rank == 0 and world == 1 and not args.kernels_only:
         other = measure_other_configs(("attention", "prequantised", "transposed", "fp16", "passes"), dev, gen, stream, peaks, xs, ws)
+
+    # ---- configuration 5: the 48-layer stack at M = 16384 ----
+    cfg5 = None
+    if want_cfg5 and nccl_layers is None:
+        del xs, ws
+        torch.cuda.empty_cache()
+        cfg5 = measure_cfg5(run, arena, lanes, ct)
 
     status = cpmk.read_status()
     if world > 1:
@@ -467,24 +535,385 @@ def run_ours(args) -> None:
         return
     base = cpu_baseline() if (world == 1 and not args.kernels_only) else None
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": WORKLOAD if M_TOKENS == 4096 else WORKLOAD + " [REDUCED to %d tokens: profiling case, not a bench value]" % M_TOKENS, "tokens": M_TOKENS, "parallelism": "column-parallel x%d; exchange = %s" % (world, exchange) if world > 1 else "single GPU",
+        "config": {"workload": workload_name(), "tokens": M_TOKENS,
+                   "parallelism": "column-parallel x%d; exchange = %s" % (world, exchange) if world > 1 else "single GPU",
                    "l2": "per-step working set (fp16 weights 302 MB + activations 134 MB + outputs 252 MB) exceeds the 126 MB L2; no explicit flush",
                    "weights": "re-quantised on every call, as the reference's bmm does"},
-        "roofline": roofline, "e2e": e2e, "gpu_launches": 8 * args.steps, "clocks": clocks,
+        "roofline": roofline, "e2e": e2e, "gpu_launches": 8 * args.steps, "clocks": clocks, "parity": parity,
+        "cfg5": cfg5, "sustained": sustained, "reference_cuda": reference_cuda,
         "gemv": gemv, "other_configs": other, "phases": phases, "device_status_word": status,
         "peaks": {k: peaks.get(k) for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained", "source")},
     }
     if base is not None:
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
-    if saved_stdout is not None:
-        sys.stdout.flush()
-        os.dup2(saved_stdout, 1)
-        os.close(saved_stdout)
-    print(json.dumps(line), flush=True)
+    run.emit(line)
     if world > 1:
         dist.destroy_process_group()
+
+
+def measure_e2e_single(run: Run, xs, ws, ct) -> dict:
+    """One GPU (or the NCCL variant): the public bmm from pinned host activations to pinned host results, three-stage
+    pipeline upload(i+1) || compute(i) || download(i-1)."""
+    torch, stream, args = run.torch, run.stream, run.args
+    host_x = [x.cpu().pin_memory() for x in xs]
+    host_y = [torch.empty((1, M_TOKENS, w.shape[1]), dtype=torch.half).pin_memory() for w in ws]
+    h2d = sum(t.numel() * 2 for t in host_x)
+    d2h = sum(t.numel() * 2 for t in host_y)
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    # two sets of device input buffers: the uploads of step s+1 run while step s still computes and downloads
+    # (PCIe is full duplex), and wait only for the compute of step s-1, which read the set they overwrite
+    dev_x = [[torch.empty_like(x) for x in xs] for _ in range(2)]
+    consumed = [None, None]                      # per buffer set: event after the last GEMM that read it
+    step_no = [0]
+
+    def e2e_step():
+        cur = step_no[0] & 1
+        step_no[0] += 1
+        ups = []
+        with torch.cuda.stream(copy_in):
+            if consumed[cur] is not None:
+                copy_in.wait_event(consumed[cur])
+            for i in range(len(SHAPES)):
+                dev_x[cur][i].copy_(host_x[i], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copy_in)
+                ups.append(ev)
+        done = None
+        for i in range(len(SHAPES)):
+            stream.wait_event(ups[i])
+            y = ct.bmm(dev_x[cur][i], False, ws[i], True, int8=True)
+            done = torch.cuda.Event()
+            done.record(stream)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(done)
+                host_y[i].copy_(y, non_blocking=True)
+            y.record_stream(copy_out)
+        consumed[cur] = done
+
+    for _ in range(2):
+        e2e_step()
+    run.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n_e2e = max(3, min(args.steps, 10))
+    a.record(stream)
+    copy_in.wait_event(a)                         # nothing of the timed steps starts before the first event
+    for _ in range(n_e2e):
+        e2e_step()
+    stream.wait_stream(copy_out)                  # the last step's results have reached the host
+    b.record(stream)
+    run.barrier()
+    ms_e2e = run.max_over_ranks(a.elapsed_time(b) / n_e2e)
+    return {"value": total_ops() / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d * run.world, "d2h_bytes_per_step": d2h * run.world,
+            "ms_per_step": ms_e2e, "steps": n_e2e,
+            "note": "activations uploaded from pinned host memory and fp16 outputs downloaded every step, copies pipelined against compute on "
+                    "separate streams; weights stay resident"}
+
+
+def measure_e2e_sharded(run: Run, xs, layers, lanes, arena) -> dict:
+    """N > 1.  Every rank owns M/g tokens end to end: it uploads only its rows of the activations, quantises them once
+    -- the quantising kernel stores codes and scales into every rank's code buffer over NVLink, 1 byte per element --
+    runs its columns of the four GEMMs on the gathered codes (epilogue stores into every rank's y), and downloads its
+    M/g rows of the full-width results.  Per step: 4 uploads, 4 quantise launches, barrier, 4 GEMM launches, barrier,
+    4 downloads; two buffer sets, so upload(s+1) || compute(s) || download(s-1)."""
+    torch, stream, args, world, rank = run.torch, run.stream, run.args, run.world, run.rank
+    rows = M_TOKENS // world
+    lo, hi = rank * rows, (rank + 1) * rows
+    host_x = [x[:, lo:hi, :].contiguous().cpu().pin_memory() for x in xs]
+    host_y = [torch.empty((1, rows, layer.n_total), dtype=torch.half).pin_memory() for layer in layers]
+    h2d = sum(t.numel() * 2 for t in host_x)
+    d2h = sum(t.numel() * 2 for t in host_y)
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    dev_x = [[torch.empty((1, rows, x.size(2)), dtype=torch.half, device=run.dev) for x in xs] for _ in range(2)]
+    consumed = [None, None]                      # per set: the quantisation that read dev_x[set] has run
+    downloaded = [None, None]                    # per set: the download that read y[set] has run
+    step_no = [0]
+
+    def e2e_step():
+        cur = step_no[0] & 1
+        step_no[0] += 1
+        ups = []
+        with torch.cuda.stream(copy_in):
+            if consumed[cur] is not None:
+                copy_in.wait_event(consumed[cur])
+            for i in range(len(SHAPES)):
+                dev_x[cur][i].copy_(host_x[i], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copy_in)
+                ups.append(ev)
+        for i, layer in enumerate(layers):
+            stream.wait_event(ups[i])
+            layer.quantize_shard(dev_x[cur][i], cur, M_TOKENS)
+        consumed[cur] = torch.cuda.Event()
+        consumed[cur].record(stream)
+        if downloaded[cur] is not None:
+            stream.wait_event(downloaded[cur])    # peers overwrite y[cur] after the next barrier: our download of it must be over
+        arena.barrier(0)                          # every rank's codes have landed; every rank is done with y[cur]
+        lanes.fork()
+        ys = []
+        for i, layer in enumerate(layers):
+            with lanes.on(i):
+                ys.append(layer.gemm(M_TOKENS, cur))
+        lanes.join()
+        arena.barrier(1)                          # every rank's output columns have landed
+        done = torch.cuda.Event()
+        done.record(stream)
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(done)
+            for i in range(len(SHAPES)):
+                host_y[i].copy_(ys[i][:, lo:hi, :], non_blocking=True)
+            downloaded[cur] = torch.cuda.Event()
+            downloaded[cur].record(copy_out)
+
+    for _ in range(2):
+        e2e_step()
+    run.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n_e2e = max(3, min(args.steps, 10))
+    a.record(stream)
+    copy_in.wait_event(a)
+    for _ in range(n_e2e):
+        e2e_step()
+    stream.wait_stream(copy_out)
+    b.record(stream)
+    run.barrier()
+    ms_e2e = run.max_over_ranks(a.elapsed_time(b) / n_e2e)
+    codes_in = sum(M_TOKENS * x.size(2) for x in xs) * (world - 1) // world
+    return {"value": total_ops() / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+            "h2d_bytes_per_step_per_rank": h2d, "d2h_bytes_per_step_per_rank": d2h, "ms_per_step": ms_e2e, "steps": n_e2e,
+            "int8_code_bytes_received_per_rank_per_step": codes_in,
+            "note": "every rank uploads its M/g rows of the activations from pinned host memory, quantises them once (the quantising kernel stores "
+                    "codes and scales into every rank's buffer over NVLink), computes its columns on the gathered codes (epilogue stores into every "
+                    "rank's y) and downloads its M/g rows of the full-width results; byte counts are whole-job totals; weights stay resident",
+            "_host_y": host_y}
+
+
+def measure_sustained(run: Run, step, xs, ws, ms_per_step: float) -> dict:
+    """The same step looped for a little over two seconds with the SM clock sampled: what the part settles at under its
+    power limit, against the sustained bf16 figure of the peaks file.  Also the GEMM launches alone, operands quantised once."""
+    torch, stream, peaks = run.torch, run.stream, run.peaks
+    from cpm_kernels_b200.torch.gemm import quantize, gemm_and_scale
+    out = {}
+    peak = 2.0 * peaks.get("bf16_tflops_sustained", 0.0) if peaks.get("bf16_tflops_sustained") else None
+
+    def loop(fn, ms_guess, name, ops):
+        n = max(50, int(2200.0 / max(ms_guess, 1e-3)))
+        sampler = ClockSampler(run.local_rank)
+        sampler.start()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record(stream)
+        for _ in range(n):
+            fn()
+        b.record(stream)
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+        ms = a.elapsed_time(b) / n
+        tops = ops / (ms * 1e-3) / 1e12
+        out[name] = {"TOPS": tops, "ms_per_step": ms, "steps": n, "seconds": ms * n * 1e-3, "clocks": clocks,
+                     "frac_of_sustained_peak": tops / peak if peak else None}
+
+    loop(step, ms_per_step, "step", total_ops())
+    quantised = [(quantize(x, False), quantize(w, False)) for x, w in zip(xs, ws)]
+
+    def gemms():
+        for (sa, qa), (sb, qb) in quantised:
+            gemm_and_scale(qa, sa, qb, sb, False, True)
+    loop(gemms, ms_per_step * 0.75, "gemm_only", total_ops())
+    out["peak"] = peak
+    out["peak_note"] = "2 x %s bf16_tflops_sustained (%s TFLOP/s: a seconds-long cuBLAS bf16 loop under the power cap)" % (peaks["source"], peaks.get("bf16_tflops_sustained"))
+    return out
+
+
+def measure_reference_cuda(run: Run, xs, ws, ct, our_ms_per_step: float, our_gemm_tops: dict) -> dict:
+    """The reference's own CUDA pipeline on the same tensors in the same process with the same event loop: its six
+    launches per linear (cpm_kernels/torch/gemm.py:86-113: calc_scale, round for both operands, cublasLt int8 GEMM,
+    gemm_scale), its kernels compiled unmodified for sm_100 (oracle/_ref), its cublasLt call sequence
+    (cpm_kernels/kernels/gemm.py:127-186) replayed by oracle/ref_cuda.py, its allocations per call.  Checker code:
+    nothing of it is on the product path."""
+    torch, stream = run.torch, run.stream
+    try:
+        from oracle import ref_cuda
+        if not ref_cuda.available():
+            return {"unavailable": "oracle/_ref/*.fatbin are not built (no reference checkout where build() ran)"}
+        rk, lt = ref_cuda.ReferenceKernels(), ref_cuda.ReferenceCublasLt()
+    except Exception as e:                                  # noqa: BLE001
+        return {"unavailable": "reference device code could not be loaded: %s" % (e,)}
+
+    def linear(x, w):
+        # torch/gemm.py:98-104 with the operand swap of :45-52
+        sa = rk.gemm_calc_scale(x)
+        qa = rk.gemm_round(x, sa)
+        sb = rk.gemm_calc_scale(w)
+        qb = rk.gemm_round(w, sb)
+        n, k, m = w.size(1), w.size(2), x.size(1)
+        acc = torch.empty((1, m, n), dtype=torch.int32, device=x.device)
+        lt.gemm_int8(n, k, m, 1, 1, True, False, qb, qa, acc)
+        return rk.gemm_scale(acc, sa, sb, True, True), (qa, qb, acc)
+
+    def ref_step():
+        for x, w in zip(xs, ws):
+            linear(x, w)
+    try:
+        ms_step = run.timed(ref_step, 5, warm=2)
+        gemm_tops, identical = {}, {}
+        for (name, n, k), x, w in zip(SHAPES, xs, ws):
+            y_ref, (qa, qb, acc) = linear(x, w)
+            identical[name] = bool(torch.equal(y_ref.view(torch.int16), ct.bmm(x, False, w, True, int8=True).view(torch.int16)))
+            ms = run.timed(lambda: lt.gemm_int8(n, k, x.size(1), 1, 1, True, False, qb, qa, acc), 10, warm=2)
+            gemm_tops[name] = 2.0 * x.size(1) * n * k / (ms * 1e-3) / 1e12
+            del y_ref, qa, qb, acc
+    except Exception as e:                                  # noqa: BLE001
+        return {"unavailable": "the reference pipeline failed on this device: %s" % (e,)}
+    return {"ms_per_step": ms_step, "TOPS": total_ops() / (ms_step * 1e-3) / 1e12, "launches_per_step": 24,
+            "speedup_of_this_repo_whole_step": ms_step / our_ms_per_step,
+            "cublaslt_gemm_only_tops": gemm_tops, "this_repo_gemm_only_tops": our_gemm_tops,
+            "gemm_only_ratio": {k: our_gemm_tops[k] / gemm_tops[k] for k in gemm_tops},
+            "outputs_bit_identical_to_this_repo": identical,
+            "what": "reference kernels (cuda/gemm.cu, unmodified, sm_100) + its cublasLt int8 call sequence (int32 result, then cu_gemm_scale), "
+                    "same tensors, same process; the GEMM-only figures time the cublasLt call alone (host descriptor churn included, as in the reference)"}
+
+
+def measure_gemv(run: Run, gen, ck) -> dict:
+    """Decode GEMV HBM GB/s (weight 10240 x 4096 and its transpose; batch 1, 4, 16 with per-batch matrices), inside a
+    CUDA graph over rotating weights larger than L2."""
+    torch, dev, stream, peaks = run.torch, run.dev, run.stream, run.peaks
+    gemv = {}
+    gs = torch.cuda.Stream()                         # capture stream; warmed up first so that the library's
+    s = gs.cuda_stream                               # per-stream workspace exists before capture begins
+    for batch in (1, 4, 16):
+        nbuf = max(1, 4 // batch)                    # at least 4 x 84 MB of weights rotate: larger than L2
+        mats = [(torch.randn((batch, 10240, 4096), generator=gen, device=dev) * 0.02).half() for _ in range(nbuf)]
+        vec_in = torch.randn((batch, 4096), generator=gen, device=dev).half()
+        y_rows = torch.empty((batch, 10240), dtype=torch.half, device=dev)
+        # the transposed weight [4096, 10240] = (dim_in, dim_out): the same buffers, read with the other shape
+        for name, fn in (("gemv_fp16", lambda j: ck.gemv_fp16(batch, 10240, 4096, mats[j].data_ptr(), vec_in.data_ptr(), y_rows.data_ptr(), s)),
+                         ("gemv_fp16_transpose", lambda j: ck.gemv_fp16_transpose(batch, 10240, 4096, mats[j].data_ptr(), vec_in.data_ptr(), y_rows.data_ptr(), s))):
+            gs.wait_stream(stream)
+            with torch.cuda.stream(gs):
+                for j in range(nbuf):
+                    fn(j)
+            gs.synchronize()
+            reps = max(2, 20 // (nbuf * batch))
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=gs):
+                for j in range(nbuf * reps):
+                    fn(j % nbuf)
+            graph.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            sec = a.elapsed_time(b) * 1e-3 / (nbuf * reps)
+            bytes_alg = batch * (2 * 10240 * 4096 + 2 * (10240 + 4096))
+            gemv["%s_batch%d" % (name, batch)] = {"GBps": bytes_alg / sec / 1e9, "us": sec * 1e6,
+                                                 "frac_of_hbm_peak": bytes_alg / sec / 1e9 / peaks["hbm_gbs"]}
+        del mats
+    return gemv
+
+
+# ------------------------------------------------------------------------------------------------
+# configuration 5: the full 48-layer CPM-Bee-10B linear stack at M = 16384 tokens, weights seeded per layer,
+# column-parallel across the ranks
+# ------------------------------------------------------------------------------------------------
+CFG5_TOKENS = 16384
+CFG5_LAYERS = 48
+CFG5_BLOCKS = 8          # every weight is generated in 8 row blocks, so that a rank's shard does not depend on how many ranks there are
+
+
+def cfg5_weight_rows(run: Run, layer: int, shape: int, blocks) -> "torch.Tensor":
+    """Rows of weight (layer, shape) made of the given row blocks: fp16 (1, len(blocks) * N / 8, K), N(0, 0.02)."""
+    torch = run.torch
+    _, n, k = SHAPES[shape]
+    parts = []
+    for j in blocks:
+        g = torch.Generator(device=run.dev).manual_seed(5_000_000 + (layer * len(SHAPES) + shape) * CFG5_BLOCKS + j)
+        parts.append((torch.randn((n // CFG5_BLOCKS, k), generator=g, device=run.dev) * 0.02).half())
+    return torch.cat(parts).unsqueeze(0).contiguous()
+
+
+def measure_cfg5(run: Run, arena, lanes, ct) -> dict:
+    torch, dev, world, rank, stream = run.torch, run.dev, run.world, run.rank, run.stream
+    from cpm_kernels_b200.sharded import FusedColumnParallelInt8Linear, SymmetricArena, ExchangeBuffers
+    n_layers = int(os.environ.get("CPMK_BENCH_CFG5_LAYERS", str(CFG5_LAYERS)))
+    steps = 2
+    if arena is None:
+        arena = SymmetricArena(sum(ExchangeBuffers.nbytes(CFG5_TOKENS, k, n) for _, n, k in SHAPES) + (1 << 20), dev)
+    if lanes is None:
+        lanes = Lanes(run, 1, 0)
+    gen = torch.Generator(device=dev).manual_seed(5)
+    xs = [torch.randn((1, CFG5_TOKENS, k), generator=gen, device=dev).half() for _, _, k in SHAPES]
+    bufs = [ExchangeBuffers(arena, CFG5_TOKENS, k, n) for _, n, k in SHAPES]
+    scratch = [(torch.empty((1, n // world, k), dtype=torch.int8, device=dev), torch.empty((1, n // world), dtype=torch.half, device=dev))
+               for _, n, k in SHAPES]
+    per = CFG5_BLOCKS // world
+    my_blocks = range(rank * per, (rank + 1) * per)
+    layers = [[FusedColumnParallelInt8Linear(cfg5_weight_rows(run, l, i, my_blocks), buffers=bufs[i], weight_scratch=scratch[i])
+               for i in range(len(SHAPES))] for l in range(n_layers)]
+    weight_bytes = sum(w.weight.numel() * 2 for row in layers for w in row)
+
+    def stack(only_local: bool):
+        for l, row in enumerate(layers):
+            lanes.fork()
+            for i, layer in enumerate(row):
+                with lanes.on(i):
+                    layer.launch(xs[i], l & 1, only_local)
+            lanes.join()
+            if not only_local:
+                arena.barrier(1)                 # one rank barrier per layer: the layer's outputs are complete on every rank
+
+    ops = total_ops(CFG5_TOKENS) * n_layers
+    ms_e2e = run.timed(lambda: stack(False), steps, warm=1)
+    ms_phase = run.timed(lambda: stack(True), steps, warm=1) if world > 1 else ms_e2e
+    out = {"workload": "%d-layer CPM-Bee-10B linear stack, M=%d tokens, int8, weights N(0, 0.02) seeded per layer (fp16, %.1f GB resident per rank, "
+                       "re-quantised on every call), column-parallel x%d; one step = %d linears" % (n_layers, CFG5_TOKENS, weight_bytes / 1e9, world, n_layers * len(SHAPES)),
+           "steps": steps, "end_to_end_with_exchange": {"ms_per_step": ms_e2e, "TOPS": ops / (ms_e2e * 1e-3) / 1e12},
+           "gemm_phase": {"ms_per_step": ms_phase, "TOPS": ops / (ms_phase * 1e-3) / 1e12,
+                          "what": "the same launches (quantise activations and weight rows, GEMM + dequantisation) with each rank storing into its own result only: no NVLink traffic, no barrier"}}
+    if world > 1:
+        # one GPU's rate on the unsharded problem, measured here on layer 0's full weights (every rank measures; rank 0's figure is used)
+        w_full = [cfg5_weight_rows(run, 0, i, range(CFG5_BLOCKS)) for i in range(len(SHAPES))]
+
+        def single():
+            for x, w in zip(xs, w_full):
+                ct.bmm(x, False, w, True, int8=True)
+        single()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(3):
+            single()
+        b.record(stream)
+        torch.cuda.synchronize()
+        single_tops = total_ops(CFG5_TOKENS) / (a.elapsed_time(b) / 3 * 1e-3) / 1e12
+        out["gemm_phase"]["one_gpu_unsharded_TOPS"] = single_tops
+        out["gemm_phase"]["efficiency"] = out["gemm_phase"]["TOPS"] / (world * single_tops)
+        out["end_to_end_with_exchange"]["speedup_over_one_gpu"] = out["end_to_end_with_exchange"]["TOPS"] / single_tops
+        ingress = sum(2 * CFG5_TOKENS * n for _, n, _ in SHAPES) * (world - 1) // world * n_layers
+        out["nvlink"] = {"bytes_received_per_rank_per_step": ingress, "achieved_GBps_per_rank": ingress / (ms_e2e * 1e-3) / 1e9, "nominal_GBps": 900.0,
+                         "frac_of_nominal": ingress / (ms_e2e * 1e-3) / 1e9 / 900.0,
+                         "note": "bytes that must enter every GPU ((g-1)/g of the fp16 outputs) over the end-to-end step time"}
+        # parity on the first and the last layer: every rank's full-width results against the unsharded bmm computed locally
+        bad, compared = 0, 0
+        for l in sorted({0, n_layers - 1}):
+            if l != 0:
+                w_full = [cfg5_weight_rows(run, l, i, range(CFG5_BLOCKS)) for i in range(len(SHAPES))]
+            for i, layer in enumerate(layers[l]):
+                y = layer.forward(xs[i], sync_before=True, slot=0)
+                run.barrier()
+                want = ct.bmm(xs[i], False, w_full[i], True, int8=True)
+                bad += count_mismatches(torch, y, want)
+                compared += want.numel()
+                del want
+        out["parity"] = {"checked": True, "mismatches": run.sum_over_ranks(bad), "elements_compared_per_rank": compared,
+                         "what": "layers 0 and %d, four linears each, every rank's full-width y against the unsharded bmm computed locally" % (n_layers - 1)}
+        del w_full
+    del layers, xs, bufs, scratch
+    torch.cuda.empty_cache()
+    return out
 
 
 def measure_other_configs(cases, dev, gen, stream, peaks, xs=None, ws=None, iters=12):
@@ -614,7 +1043,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--exchange", default="fused", choices=["fused", "fused1", "nccl"],
-                    help="N > 1: how the output slices reach every rank (fused = stored by the GEMM epilogue, linears on two alternating streams; fused1 = the same on one stream; nccl = all-gather)")
+                    help="N > 1: how the output slices reach every rank (fused = stored by the GEMM epilogue, linears on several streams; fused1 = the same on one stream; nccl = all-gather)")
+    ap.add_argument("--no-cfg5", action="store_true", help="skip the 48-layer stack at M = 16384 (shorter run)")
     ap.add_argument("--tokens", type=int, default=M_TOKENS,
                     help="tokens per step; anything but the default is a reduced case for profiler captures, not a bench value")
     ap.add_argument("--kernels-only", action="store_true",

@@ -19,6 +19,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
     "-shared", "-Xcompiler", "-fPIC",
+    "--threads", "0",                      # one compilation per source file in parallel
 ]
 
 

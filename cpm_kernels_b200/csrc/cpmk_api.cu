@@ -49,6 +49,9 @@ int32_t current_device_info(DeviceInfo *info) {
     return CPMK_OK;
 }
 
+// At most this many (stream) workspaces per device; a slot is given back with cpmk_release_workspace.
+constexpr size_t kMaxWorkspacesPerDevice = 256;
+
 int32_t get_workspace(cudaStream_t stream, Workspace *ws) {
     int dev = 0;
     CPMK_CUDA_TRY(cudaGetDevice(&dev));
@@ -56,8 +59,11 @@ int32_t get_workspace(cudaStream_t stream, Workspace *ws) {
     auto key = std::make_pair(dev, stream);
     auto it = g_workspaces.find(key);
     if (it == g_workspaces.end()) {
-        if (g_workspaces.size() >= 64) {
-            set_error("more than 64 (device, stream) pairs asked for a cpmk workspace");
+        size_t on_device = 0;
+        for (auto &kv : g_workspaces) on_device += kv.first.first == dev ? 1 : 0;
+        if (on_device >= kMaxWorkspacesPerDevice) {
+            set_error("more than %zu streams of device %d asked for a cpmk workspace; release those of destroyed streams with "
+                      "cpmk_release_workspace", kMaxWorkspacesPerDevice, dev);
             return CPMK_ENOMEM;
         }
         Workspace w;
@@ -73,6 +79,17 @@ int32_t get_workspace(cudaStream_t stream, Workspace *ws) {
         it = g_workspaces.emplace(key, w).first;
     }
     *ws = it->second;
+    return CPMK_OK;
+}
+
+// Reads the status word of one workspace; when a kernel recorded a failure there, clears the word AND the ticket
+// region: a kernel that gave up a wait leaves without taking its ticket, so the counters it shares with later calls
+// are no longer at zero.  The caller holds g_mutex and has synchronised the work that uses the workspace.
+static int32_t collect_status(const Workspace &w, uint32_t *word_out) {
+    uint32_t word = 0;
+    CPMK_CUDA_TRY(cudaMemcpy(&word, w.status(), sizeof(word), cudaMemcpyDeviceToHost));
+    if (word != 0) CPMK_CUDA_TRY(cudaMemset(w.base, 0, Workspace::kScratchOffset));
+    *word_out = word;
     return CPMK_OK;
 }
 
@@ -104,13 +121,43 @@ int32_t cpmk_read_status(uint32_t *status_out) {
     for (auto &kv : cpmk::g_workspaces) {
         if (kv.first.first != dev) continue;
         uint32_t word = 0;
-        CPMK_CUDA_TRY(cudaMemcpy(&word, kv.second.status(), sizeof(word), cudaMemcpyDeviceToHost));
-        if (word != 0) {
-            if (worst == 0) worst = word;
-            CPMK_CUDA_TRY(cudaMemset(kv.second.status(), 0, sizeof(word)));
-        }
+        const int32_t rc = cpmk::collect_status(kv.second, &word);
+        if (rc) return rc;
+        if (word != 0 && worst == 0) worst = word;
     }
     *status_out = worst;
+    return CPMK_OK;
+}
+
+int32_t cpmk_check_stream(cpmk_stream_t stream) {
+    int dev = 0;
+    CPMK_CUDA_TRY(cudaGetDevice(&dev));
+    CPMK_CUDA_TRY(cudaStreamSynchronize(cpmk::as_stream(stream)));
+    std::lock_guard<std::mutex> lock(cpmk::g_mutex);
+    auto it = cpmk::g_workspaces.find(std::make_pair(dev, cpmk::as_stream(stream)));
+    if (it == cpmk::g_workspaces.end()) return CPMK_OK;          // no kernel with a bounded wait ran on this stream
+    uint32_t word = 0;
+    const int32_t rc = cpmk::collect_status(it->second, &word);
+    if (rc) return rc;
+    if (word != 0) {
+        cpmk::set_error("a kernel on this stream gave up a bounded wait (code 0x%x); its output is incomplete", word);
+        return CPMK_EDEVICE;
+    }
+    return CPMK_OK;
+}
+
+int32_t cpmk_release_workspace(cpmk_stream_t stream) {
+    int dev = 0;
+    CPMK_CUDA_TRY(cudaGetDevice(&dev));
+    cpmk::Workspace w;
+    {
+        std::lock_guard<std::mutex> lock(cpmk::g_mutex);
+        auto it = cpmk::g_workspaces.find(std::make_pair(dev, cpmk::as_stream(stream)));
+        if (it == cpmk::g_workspaces.end()) return CPMK_OK;
+        w = it->second;
+        cpmk::g_workspaces.erase(it);
+    }
+    CPMK_CUDA_TRY(cudaFree(w.base));                             // waits for the device to finish with the memory
     return CPMK_OK;
 }
 

@@ -3,13 +3,16 @@
 // Replaces the cublasLtMatmul call of cpm_kernels/kernels/gemm.py:127-186 (and, when fused, the
 // cu_gemm_scale pass of cuda/gemm.cu:37-57 that follows it in cpm_kernels/torch/gemm.py:40-64).
 //
-// Two kernels:
-//   * gemm_i8_tc_kernel  -- tcgen05.mma kind::i8, accumulators in tensor memory, operands staged in
-//     shared memory by TMA through a 4-stage mbarrier pipeline, one persistent CTA per SM with
-//     warp-specialised roles (TMA producer / MMA issuer / 4 epilogue warps) and two accumulator
-//     buffers so that the epilogue of tile i overlaps the main loop of tile i+1.  It handles the
-//     layout in which both operands are contiguous along k (aT && !bT: the nn.Linear case).
+// Three kernels:
+//   * gemm_i8_tc2_kernel -- the main one: a cluster of two CTAs computes a 256 x 256 output tile with
+//     tcgen05.mma.cta_group::2.kind::i8, accumulators in tensor memory (two per CTA, so the epilogue of tile i overlaps
+//     the main loop of tile i+1), operands staged by TMA through a 5-stage mbarrier ring, persistent grid with
+//     warp-specialised roles (TMA producer / MMA issuer / 8 epilogue warps), output through swizzled shared-memory
+//     staging tiles and TMA stores (to one or several destinations).  Takes all four storage orders of the operands.
+//   * gemm_i8_tc_kernel  -- one CTA per 128 x 256 tile (cta_group::1, 4 stages, 4 epilogue warps, register epilogue),
+//     for outputs of at most 128 rows with both operands contiguous along k.
 //   * gemm_i8_simt_kernel -- dp4a, any layout, any size that the interface admits.
+// gemm_f16_tc2_kernel is the first kernel's pipeline with kind::f16 (the int8=False branch of bmm).
 //
 // Every device-side wait is bounded: when one runs out the CTA records a code in the status word,
 // raises its abort flag, lets copies in flight land, frees its tensor memory and returns.
@@ -19,6 +22,7 @@
 
 #include <atomic>
 #include <mutex>
+#include <unordered_map>
 
 #include "cpmk_common.cuh"
 #include "cpmk_ptx.cuh"
@@ -889,28 +893,34 @@ EncodeTiledFn get_encode_tiled() {
     return fn;
 }
 
-// Encoding a tensor map costs a microsecond or two of host time and a GEMM needs three; callers reuse the same
-// buffers call after call (weights, and whatever the framework's caching allocator hands back), so the last few
-// encodings are kept per thread, keyed by everything that went into them.
+// Encoding a tensor map costs a microsecond or two of host time and a GEMM needs three or more; callers reuse the same
+// buffers call after call (weights, and whatever the framework's caching allocator hands back), so encodings are kept
+// per thread in a hash table keyed by everything that went into them.  A model of 48 layers with four weights each,
+// activations, outputs and one output map per peer GPU stays well inside kMapCacheEntries; when the table is full it
+// is emptied and refills.
 struct MapKey {
     const void *ptr;
     int32_t a, b, c, kind;
     bool operator==(const MapKey &o) const { return ptr == o.ptr && a == o.a && b == o.b && c == o.c && kind == o.kind; }
 };
+struct MapKeyHash {
+    size_t operator()(const MapKey &k) const {
+        uint64_t h = reinterpret_cast<uintptr_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+        h ^= ((uint64_t)(uint32_t)k.a << 32 | (uint32_t)k.b) * 0xC2B2AE3D27D4EB4Full;
+        h ^= ((uint64_t)(uint32_t)k.c << 32 | (uint32_t)k.kind) * 0x165667B19E3779F9ull;
+        return (size_t)(h ^ (h >> 29));
+    }
+};
+constexpr size_t kMapCacheEntries = 4096;
 struct MapCache {
-    static constexpr int kEntries = 32;
-    MapKey keys[kEntries];
-    CUtensorMap maps[kEntries];
-    int used = 0, next = 0;
+    std::unordered_map<MapKey, CUtensorMap, MapKeyHash> table;
     const CUtensorMap *find(const MapKey &k) const {
-        for (int i = 0; i < used; ++i)
-            if (keys[i] == k) return &maps[i];
-        return nullptr;
+        auto it = table.find(k);
+        return it == table.end() ? nullptr : &it->second;
     }
     void put(const MapKey &k, const CUtensorMap &m) {
-        const int slot = used < kEntries ? used++ : (next++ % kEntries);
-        keys[slot] = k;
-        maps[slot] = m;
+        if (table.size() >= kMapCacheEntries) table.clear();
+        table.emplace(k, m);
     }
 };
 thread_local MapCache g_map_cache;
@@ -1135,7 +1145,7 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
             const bool enc_q = q_mn ? encode_operand_mn(&tmap_q, A, m, k, batchA) : encode_operand(&tmap_q, A, m, k, batchA, kHalfBN);
             if (total < (int64_t(1) << 31) && enc_p && enc_q) {
                 prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.total_tiles = (int32_t)total;
-            set_tile_divisors(&prm);
+                set_tile_divisors(&prm);
                 const int pairs = (int)(total < max_pairs ? total : max_pairs);
                 const dim3 grid(2 * pairs);
                 OutMaps tmap_o;
@@ -1148,7 +1158,7 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
                     set_error("scattered output needs a row pitch that is a multiple of 16 bytes and 16-byte aligned destinations");
                     return CPMK_EINVAL;
                 }
-if (!p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, false, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+                if (!p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, false, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
                 else if (!p_mn && q_mn) gemm_i8_tc2_kernel<DEQUANT, false, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
                 else if (p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, true, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
                 else gemm_i8_tc2_kernel<DEQUANT, true, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
@@ -1296,7 +1306,7 @@ int32_t launch_gemm_f16(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t
             set_tile_divisors(&prm);
             const int pairs = (int)(total < max_pairs ? total : max_pairs);
             const dim3 grid(2 * pairs);
-if (!p_mn && !q_mn) gemm_f16_tc2_kernel<false, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+            if (!p_mn && !q_mn) gemm_f16_tc2_kernel<false, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
             else if (!p_mn && q_mn) gemm_f16_tc2_kernel<false, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
             else if (p_mn && !q_mn) gemm_f16_tc2_kernel<true, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
             else gemm_f16_tc2_kernel<true, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);

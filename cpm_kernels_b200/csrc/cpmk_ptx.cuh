@@ -38,7 +38,9 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 
 // Waits for the phase of `bar` with the given parity.  Returns false when the CTA is aborting or the
 // wait exceeded its limit (in which case it raises the abort flag and records `code`).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint32_t *status, uint32_t code) {
+// `limit_ns`: how long the wait may last (default: kWaitLimitNs).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint32_t *status, uint32_t code,
+                                          uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
     for (uint32_t spin = 1;; ++spin) {
@@ -47,7 +49,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) {
+            else if (now - t0 > limit_ns) {
                 *abort_flag = 1u;
                 atomicCAS(status, 0u, code);
                 return false;

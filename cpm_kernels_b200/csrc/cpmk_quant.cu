@@ -35,19 +35,31 @@ struct SecondOperand {
     int8_t *out;
     unsigned first_block;
 };
-template <int NV, int MODE, bool FULL, bool PAIR = false>
+// MULTI: the scales and codes of the FIRST operand are written to `n` destinations instead of one (this GPU's buffer
+// and its peers', reached through peer-mapped addresses): a rank that holds a slice of the activations' rows quantises
+// it once and the stores themselves distribute the result -- the all-gather of the codes costs no second kernel and no
+// second read.  Only stores cross the link.
+constexpr int kMaxQuantDst = 8;
+struct MultiDst {
+    int32_t n;
+    int8_t *codes[kMaxQuantDst];      // element (0, 0) of these rows in each destination
+    __half *scale[kMaxQuantDst];
+};
+template <int NV, int MODE, bool FULL, bool PAIR = false, bool MULTI = false>
 __global__ void __launch_bounds__(kBlock, NV <= 4 ? 6 : 4) quant_rows_kernel(int64_t rows, int32_t m, int group, const __half *__restrict__ mat,
                                                             __half *__restrict__ scale, int8_t *__restrict__ out,
-                                                            const SecondOperand second = SecondOperand()) {
+                                                            const SecondOperand second = SecondOperand(), const MultiDst multi = MultiDst()) {
     __shared__ float warp_max[kBlock / 32];
     const int tid = threadIdx.x;
     unsigned block = blockIdx.x;
+    bool multi_here = MULTI;
     if (PAIR && block >= second.first_block) {
         block -= second.first_block;
         rows = second.rows;
         mat = second.mat;
         scale = second.scale;
         out = second.out;
+        multi_here = false;
     }
     // group is a power of two: shifts, not divisions (a division's latency would sit in front of the first load)
     const int group_log2 = 31 - __clz(group);
@@ -84,13 +96,39 @@ __global__ void __launch_bounds__(kBlock, NV <= 4 ? 6 : 4) quant_rows_kernel(int
             for (int w = 1; w < (group >> 5); ++w) amax = fmaxf(amax, warp_max[first_warp + w]);
         }
         const __half sh = scale_from_amax(amax);
-        if (row_ok && lane_in_row == 0) scale[row] = sh;
+        if (row_ok && lane_in_row == 0) {
+            if (MULTI && multi_here) {
+#pragma unroll
+                for (int d = 0; d < kMaxQuantDst; ++d)
+                    if (d < multi.n) multi.scale[d][row] = sh;
+            } else {
+                scale[row] = sh;
+            }
+        }
         s = __half2float(sh);
     }
     if (MODE == 1) return;
     float r_up, r_dn;
     cpmk_round_prepare(s, &r_up, &r_dn);
     if (!(cpmk_scale_in_domain(s) && cpmk_round_domain_ok(local_max, r_up))) r_up = __int_as_float(0x7fc00000);
+    if (MULTI && multi_here) {
+        uint2 q[NV];
+#pragma unroll
+        for (int j = 0; j < NV; ++j) q[j] = round8_one_scale(v[j], s, r_up, r_dn);
+        const int64_t offset = (row_ok ? row : 0) * (int64_t)m;
+#pragma unroll
+        for (int d = 0; d < kMaxQuantDst; ++d) {
+            if (d < multi.n) {
+                uint2 *dst = reinterpret_cast<uint2 *>(multi.codes[d] + offset);
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    const int idx = lane_in_row + j * group;
+                    if (FULL || (row_ok && idx < nvec)) dst[idx] = q[j];
+                }
+            }
+        }
+        return;
+    }
     uint2 *dst = reinterpret_cast<uint2 *>(out + (row_ok ? row : 0) * (int64_t)m);
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
@@ -679,15 +717,21 @@ int32_t launch_quant_rows(int32_t batch, int32_t n, int32_t m, const void *mat, 
 }
 
 // Fused scale + round of two operands with rows of the same length in one launch (see SecondOperand).
+// `multi`: when given, the first operand's scales and codes go to its destinations (see MultiDst) and the second
+// operand may be empty (rows1 == 0).
 int32_t launch_quant_rows_pair(int64_t rows0, const void *mat0, void *scale0, void *out0, int64_t rows1, const void *mat1, void *scale1,
-                               void *out1, int32_t m, cudaStream_t stream, bool *done) {
+                               void *out1, int32_t m, cudaStream_t stream, bool *done, const MultiDst *multi = nullptr) {
     *done = false;
     DeviceInfo info;
     int32_t rc = current_device_info(&info);
     if (rc) return rc;
-    if (rows0 <= 0 || rows1 <= 0 || m <= 0) return CPMK_OK;
-    const bool vec_ok = (m % 8 == 0) && m <= 256 * 8 * 8 && aligned16(mat0) && aligned16(mat1) && (reinterpret_cast<uintptr_t>(out0) & 7u) == 0 &&
-                        (reinterpret_cast<uintptr_t>(out1) & 7u) == 0;
+    if (rows0 <= 0 || (rows1 <= 0 && !multi) || rows1 < 0 || m <= 0) return CPMK_OK;
+    bool vec_ok = (m % 8 == 0) && m <= 256 * 8 * 8 && aligned16(mat0) && (rows1 == 0 || (aligned16(mat1) && (reinterpret_cast<uintptr_t>(out1) & 7u) == 0));
+    if (multi) {
+        for (int d = 0; d < multi->n; ++d) vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(multi->codes[d]) & 7u) == 0;
+    } else {
+        vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(out0) & 7u) == 0;
+    }
     if (!vec_ok) return CPMK_OK;
     const int nvec = m / 8;
     int group = 8;
@@ -710,7 +754,10 @@ int32_t launch_quant_rows_pair(int64_t rows0, const void *mat0, void *scale0, vo
     int8_t *dst = static_cast<int8_t *>(out0);
 #define CPMK_LAUNCH_ROWS_PAIR(NVT)                                                                                               \
     do {                                                                                                                         \
-        if (full) quant_rows_kernel<NVT, 0, true, true><<<grid, kBlock, 0, stream>>>(rows0, m, group, src, sc, dst, second);     \
+        if (multi) {                                                                                                             \
+            if (full) quant_rows_kernel<NVT, 0, true, true, true><<<grid, kBlock, 0, stream>>>(rows0, m, group, src, sc, dst, second, *multi);  \
+            else quant_rows_kernel<NVT, 0, false, true, true><<<grid, kBlock, 0, stream>>>(rows0, m, group, src, sc, dst, second, *multi);      \
+        } else if (full) quant_rows_kernel<NVT, 0, true, true><<<grid, kBlock, 0, stream>>>(rows0, m, group, src, sc, dst, second);     \
         else quant_rows_kernel<NVT, 0, false, true><<<grid, kBlock, 0, stream>>>(rows0, m, group, src, sc, dst, second);         \
     } while (0)
     if (nv <= 1) CPMK_LAUNCH_ROWS_PAIR(1);
@@ -908,6 +955,32 @@ int32_t cpmk_quantize_rows_pair(int32_t batch0, int32_t n0, const void *mat0, vo
     rc = launch_quant_rows<0>(batch0, n0, m, mat0, scale_out0, q_out0, as_stream(stream));
     if (rc) return rc;
     return launch_quant_rows<0>(batch1, n1, m, mat1, scale_out1, q_out1, as_stream(stream));
+}
+
+int32_t cpmk_quantize_rows_pair_scatter(int32_t n0, const void *mat0, int32_t n_dst, void *const *scale_dst0, void *const *q_dst0,
+                                        int32_t n1, const void *mat1, void *scale_out1, void *q_out1, int32_t m, cpmk_stream_t stream) {
+    int32_t rc = check_shape(1, n0, m);
+    if (rc) return rc;
+    rc = check_shape(1, n1, m);
+    if (rc) return rc;
+    CPMK_REQUIRE(n_dst >= 1 && n_dst <= kMaxQuantDst, "number of destinations must be 1..%d (got %d)", kMaxQuantDst, n_dst);
+    CPMK_REQUIRE(scale_dst0 && q_dst0, "null destination list");
+    if (n0 == 0 && n1 == 0) return CPMK_OK;
+    CPMK_REQUIRE(n0 > 0 && m > 0, "the scattered operand must not be empty (n0=%d m=%d)", n0, m);
+    CPMK_REQUIRE(mat0 && (n1 == 0 || (mat1 && scale_out1 && q_out1)), "null tensor pointer");
+    MultiDst multi;
+    multi.n = n_dst;
+    for (int d = 0; d < kMaxQuantDst; ++d) {
+        multi.codes[d] = d < n_dst ? static_cast<int8_t *>(q_dst0[d]) : nullptr;
+        multi.scale[d] = d < n_dst ? static_cast<__half *>(scale_dst0[d]) : nullptr;
+        if (d < n_dst) CPMK_REQUIRE(multi.codes[d] && multi.scale[d], "destination %d is null", d);
+    }
+    bool done = false;
+    rc = launch_quant_rows_pair(n0, mat0, nullptr, nullptr, n1, mat1, scale_out1, q_out1, m, as_stream(stream), &done, &multi);
+    if (rc) return rc;
+    CPMK_REQUIRE(done, "scattered quantisation needs rows of a multiple of 8 and at most 16384 elements, a 16-byte aligned operand and "
+                       "8-byte aligned destinations (m=%d)", m);
+    return CPMK_OK;
 }
 
 int32_t cpmk_gemm_calc_scale_transpose(int32_t batch, int32_t n, int32_t m, const void *inp, void *out, cpmk_stream_t stream) {

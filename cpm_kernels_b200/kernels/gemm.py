@@ -194,6 +194,36 @@ def gemm_int8_scale_scatter(m: int, k: int, n: int,
     import ctypes
     assert m % 4 == 0 and n % 4 == 0 and k % 4 == 0
     assert batchA == batchB or batchA == 1 or batchB == 1
-    arr = (ctypes.c_void_p * len(dst))(*dst)
+    arr = dst if not isinstance(dst, (list, tuple)) else (ctypes.c_void_p * len(dst))(*dst)
     cpmk.call("cpmk_gemm_int8_dequant_scatter", m, k, n, batchA, batchB, int(bool(aT)), int(bool(bT)), A, B, scale_x, scale_y,
               int(bool(broad_cast_x)), int(bool(broad_cast_y)), len(dst), arr, dst_row_pitch, stream_arg(stream))
+
+
+def gemm_quantize_rows_pair_scatter(n0: int, mat0: DevicePointer,
+                                    scale_dst0: list,       # where the scales (n0) of these rows go in each destination
+                                    q_dst0: list,           # where the codes (n0, m) of these rows go in each destination
+                                    n1: int, mat1: DevicePointer, scale1: DevicePointer, out1: DevicePointer,
+                                    m: int, stream: CUDAStream):
+    """gemm_quantize_rows_pair whose first operand is written to several destinations (this GPU's code buffer and its
+    peers'): the all-gather of row-sharded int8 activations, done by the stores of the quantisation pass.  ``n1`` may
+    be 0 (no second operand).  No counterpart in the reference."""
+    import ctypes
+    assert len(scale_dst0) == len(q_dst0) and 1 <= len(q_dst0) <= 8
+    sarr = (ctypes.c_void_p * len(scale_dst0))(*scale_dst0)
+    qarr = (ctypes.c_void_p * len(q_dst0))(*q_dst0)
+    cpmk.call("cpmk_quantize_rows_pair_scatter", n0, mat0, len(q_dst0), sarr, qarr, n1, mat1, scale1, out1, m, stream_arg(stream))
+
+
+def linear_int8_scatter(tokens: int, k: int, n_local: int,
+                        x: DevicePointer,          # (tokens, k)    fp16
+                        w: DevicePointer,          # (n_local, k)   fp16: this rank's rows of the weight
+                        scale_x: DevicePointer, q_x: DevicePointer, scale_w: DevicePointer, q_w: DevicePointer,   # written
+                        dst,                       # ctypes array of device addresses, or a list of them
+                        dst_row_pitch: int, stream: CUDAStream):
+    """One column-parallel int8 linear in one call: quantise x and w (one launch), GEMM + dequantisation stored to every
+    destination (one launch).  Every buffer is the caller's.  torch/gemm.py:86-113 for the sharded layout."""
+    import ctypes
+    if isinstance(dst, (list, tuple)):
+        dst = (ctypes.c_void_p * len(dst))(*dst)
+    cpmk.call("cpmk_linear_int8_scatter", tokens, k, n_local, x, w, scale_x, q_x, scale_w, q_w, len(dst), dst, dst_row_pitch,
+              stream_arg(stream))

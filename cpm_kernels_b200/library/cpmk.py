@@ -26,6 +26,11 @@ _p = c_void_p
 SIGNATURES = {
     "cpmk_check_device": [POINTER(c_int32)],
     "cpmk_read_status": [POINTER(c_uint32)],
+    "cpmk_check_stream": [_p],
+    "cpmk_release_workspace": [_p],
+    "cpmk_selftest_bounded_wait": [c_uint32, _p],
+    "cpmk_quantize_rows_pair_scatter": [_i, _p, _i, POINTER(c_void_p), POINTER(c_void_p), _i, _p, _p, _p, _i, _p],
+    "cpmk_linear_int8_scatter": [_i, _i, _i, _p, _p, _p, _p, _p, _p, _i, POINTER(c_void_p), ctypes.c_int64, _p],
     "cpmk_gemm_calc_scale": [_i, _i, _i, _p, _p, _p],
     "cpmk_gemm_calc_scale_transpose": [_i, _i, _i, _p, _p, _p],
     "cpmk_gemm_round": [_i, _i, _i, _p, _p, _p, _p],
@@ -95,6 +100,16 @@ def read_status() -> int:
     word = c_uint32(0)
     check_status(lib.cpmk_read_status(ctypes.byref(word)), "cpmk_read_status")
     return word.value
+
+
+def check_stream(stream) -> None:
+    """Wait for ``stream``; raise RuntimeError (status CPMK_EDEVICE) if a kernel on it gave up a bounded wait."""
+    call("cpmk_check_stream", stream)
+
+
+def release_workspace(stream) -> None:
+    """Free the library's workspace of (current device, ``stream``); call before destroying the stream."""
+    call("cpmk_release_workspace", stream)
 
 
 def set_gemm_sm_margin(sms: int) -> None:

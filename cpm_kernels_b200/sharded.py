@@ -1,15 +1,23 @@
 """Column-parallel (N-sharded) int8 linear over ``torch.distributed``.
 
 The reference has no multi-GPU code; its linear layer shards naturally along the output features: rank r holds
-rows [r*N/g, (r+1)*N/g) of the weight W (N, K), the activations x (M, K) are replicated, and because both
-quantisations are per row (x rows along K, W rows along K) every rank's slice of y = x W^T is bit-identical to
-the same slice of the unsharded result.  The only exchange is an all-gather of the fp16 output slices.
+rows [r*N/g, (r+1)*N/g) of the weight W (N, K), and because both quantisations are per row (x rows along K, W rows
+along K) every rank's slice of y = x W^T is bit-identical to the same slice of the unsharded result.  Two exchanges
+exist, both done by the stores of this package's own kernels into peer-mapped (symmetric) memory:
 
-One process per GPU; the process group is the caller's (NCCL on GPUs; gloo works for the host logic).
+* the all-gather of the fp16 outputs: the GEMM's epilogue stores its N/g columns into every rank's full-width y;
+* (optional) the all-gather of the int8 activations: a rank that holds only rows [r*M/g, (r+1)*M/g) of x quantises
+  them once and the quantising kernel stores codes and scales into every rank's full code buffer -- 1 byte per element
+  over NVLink instead of every rank loading (or uploading) the whole fp16 tensor.
+
+One process per GPU; the process group is the caller's (NCCL on GPUs; gloo works for the host logic of the
+NCCL-gather layer).
 """
 from __future__ import annotations
 
-from typing import Callable, Optional, Tuple
+import ctypes
+import math
+from typing import Callable, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -30,7 +38,7 @@ def _default_compute(x: torch.Tensor, w_shard: torch.Tensor) -> torch.Tensor:
 
 
 class ColumnParallelInt8Linear:
-    """y = int8_linear(x, W) with W sharded along N.
+    """y = int8_linear(x, W) with W sharded along N and an NCCL all-gather of the output slices.
 
     ``weight_shard``: this rank's rows of W, fp16 (1, N/g, K), contiguous.
     ``compute``: the local linear; defaults to this package's CUDA ``bmm(x, False, w, True, int8=True)``.  Tests of the
@@ -73,57 +81,208 @@ class ColumnParallelInt8Linear:
     __call__ = forward
 
 
-class FusedColumnParallelInt8Linear:
-    """The same layer with the all-gather done by the GEMM: every rank's epilogue stores its N/g output columns straight
-    into columns [r*N/g, (r+1)*N/g) of every rank's full-width, token-major y (TMA stores over NVLink into peer-mapped
-    symmetric memory), so there is no gather kernel, no second read of the slice and no re-layout pass.
+# ------------------------------------------------------------------------------------------------
+# peer-mapped buffers
+# ------------------------------------------------------------------------------------------------
+def _align(x: int, a: int = 256) -> int:
+    return (x + a - 1) // a * a
 
-    ``y`` lives in symmetric memory owned by the layer (one buffer per token count, reused call after call): the caller
-    must be done reading the previous result on every rank before calling again, or pass ``sync_before=True``.
-    CUDA only (there is no host form of peer-mapped stores); NCCL process group for the rendezvous.
+
+class SymmetricArena:
+    """One symmetric-memory allocation per rank (same size on every rank), carved into buffers that sit at the same
+    offset on every rank, so that a peer's copy of a buffer is ``base[peer] + offset``.  One rendezvous for everything
+    instead of one per tensor.  With a single rank (or no process group) it is ordinary device memory and the barrier
+    does nothing, so the same layer code runs on one GPU."""
+
+    def __init__(self, nbytes: int, device: torch.device, group: Optional[dist.ProcessGroup] = None):
+        self.distributed = dist.is_available() and dist.is_initialized()
+        self.group = (group if group is not None else dist.group.WORLD) if self.distributed else None
+        self.world = dist.get_world_size(self.group) if self.distributed else 1
+        self.rank = dist.get_rank(self.group) if self.distributed else 0
+        self.nbytes = _align(max(int(nbytes), 256))
+        self.used = 0
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+            self.handle = symm_mem.rendezvous(self.buf, self.group)
+            self.base = [int(self.handle.buffer_ptrs[p]) for p in range(self.world)]
+        else:
+            self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+            self.handle = None
+            self.base = [self.buf.data_ptr()]
+
+    def carve(self, shape, dtype: torch.dtype) -> Tuple[torch.Tensor, int]:
+        """A (local tensor, offset) pair; the peers' copies are at ``peer_ptr(p, offset)``."""
+        n = math.prod(shape) * torch.empty((), dtype=dtype).element_size()
+        off = self.used
+        if off + n > self.nbytes:
+            raise RuntimeError("symmetric arena of %d bytes is full (%d used, %d asked)" % (self.nbytes, off, n))
+        self.used = _align(off + n)
+        return self.buf[off:off + n].view(dtype).view(shape), off
+
+    def peer_ptr(self, peer: int, offset: int) -> int:
+        return self.base[peer] + offset
+
+    def barrier(self, channel: int = 0) -> None:
+        """Every rank's work enqueued so far on its current stream (stores into peers included) has completed when the
+        stream passes this point on any rank."""
+        if self.handle is not None:
+            self.handle.barrier(channel=channel)
+
+
+class ExchangeBuffers:
+    """The peer-mapped buffers of one linear shape (tokens, K) -> (tokens, N): per slot the full-width fp16 output
+    y (1, tokens, N), the gathered int8 activations qx (1, tokens, K) and their scales sx (1, tokens).  Two slots let
+    step s+1 be written while step s is still being read."""
+
+    def __init__(self, arena: SymmetricArena, tokens: int, k: int, n_total: int, slots: int = 2):
+        self.arena, self.tokens, self.k, self.n_total, self.slots = arena, tokens, k, n_total, slots
+        self.y, self.qx, self.sx = [], [], []
+        self.y_off, self.qx_off, self.sx_off = [], [], []
+        for _ in range(slots):
+            t, off = arena.carve((1, tokens, n_total), torch.half)
+            self.y.append(t)
+            self.y_off.append(off)
+            t, off = arena.carve((1, tokens, k), torch.int8)
+            self.qx.append(t)
+            self.qx_off.append(off)
+            t, off = arena.carve((1, tokens), torch.half)
+            self.sx.append(t)
+            self.sx_off.append(off)
+
+    @staticmethod
+    def nbytes(tokens: int, k: int, n_total: int, slots: int = 2) -> int:
+        return slots * (_align(2 * tokens * n_total) + _align(tokens * k) + _align(2 * tokens))
+
+
+def _peer_order(rank: int, world: int) -> List[int]:
+    """Destinations in the order rank+1, rank+2, ..., rank: at any moment the ranks store to different peers instead of
+    all converging on rank 0 first."""
+    return [(rank + 1 + i) % world for i in range(world)]
+
+
+class FusedColumnParallelInt8Linear:
+    """The column-parallel layer with the all-gather done by the GEMM: every rank's epilogue stores its N/g output
+    columns straight into columns [r*N/g, (r+1)*N/g) of every rank's full-width, token-major y (TMA stores over NVLink
+    into peer-mapped memory), so there is no gather kernel, no second read of the slice and no re-layout pass.
+
+    ``weight_shard``: this rank's rows of W, fp16 (1, N/g, K).  ``buffers``: the peer-mapped buffers of this shape
+    (shared by all layers of the shape); without them the layer allocates its own on first use -- a collective call.
+    ``weight_scratch``: (codes int8 (1, N/g, K), scales fp16 (1, N/g)) for the quantised weight; layers of one shape may
+    share it, because the weight is re-quantised on every call as the reference's ``bmm`` does.
+
+    Two forms of the forward pass:
+      * ``forward(x)``: x (1, tokens, K) is present in full on every rank; one library call quantises x and the weight
+        rows and runs the scattering GEMM; one barrier afterwards.
+      * ``quantize_shard(x_rows)`` + barrier + ``gemm()`` + barrier (``forward_sharded``): each rank holds only its
+        tokens/g rows of x; the quantising kernel distributes codes and scales to every rank.
+    ``y`` lives in the buffers' slot: the caller must be done reading a slot on every rank before it is written again
+    (alternate slots, or pass ``sync_before=True``).  CUDA only.
     """
 
-    def __init__(self, weight_shard: torch.Tensor, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, weight_shard: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
+                 buffers: Optional[ExchangeBuffers] = None, weight_scratch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
         assert weight_shard.ndim == 3 and weight_shard.size(0) == 1 and weight_shard.is_contiguous() and weight_shard.is_cuda
+        assert weight_shard.dtype == torch.half
         self.weight = weight_shard
-        self.group = group if group is not None else dist.group.WORLD
-        self.world = dist.get_world_size(self.group)
-        self.rank = dist.get_rank(self.group)
-        self._buffers = {}
+        self.distributed = dist.is_available() and dist.is_initialized()
+        self.group = (group if group is not None else dist.group.WORLD) if self.distributed else None
+        self.world = dist.get_world_size(self.group) if self.distributed else 1
+        self.rank = dist.get_rank(self.group) if self.distributed else 0
+        self.n_local, self.k = weight_shard.size(1), weight_shard.size(2)
+        self.n_total = self.n_local * self.world
+        self.buffers = buffers
+        if weight_scratch is None:
+            weight_scratch = (torch.empty(weight_shard.shape, dtype=torch.int8, device=weight_shard.device),
+                              torch.empty((1, self.n_local), dtype=torch.half, device=weight_shard.device))
+        self.q_w, self.scale_w = weight_scratch
+        assert self.q_w.shape == weight_shard.shape and self.q_w.dtype == torch.int8
+        self._own = {}
+        self._dst_cache = {}
 
-    def _buffer(self, m_tokens: int):
-        import torch.distributed._symmetric_memory as symm_mem
-        if m_tokens not in self._buffers:
-            n_total = self.weight.size(1) * self.world
-            y = symm_mem.empty((1, m_tokens, n_total), dtype=torch.half, device=self.weight.device)
-            handle = symm_mem.rendezvous(y, self.group)
-            self._buffers[m_tokens] = (y, handle)
-        return self._buffers[m_tokens]
+    # ---- buffers and destination lists ----
+    def _buffers_for(self, tokens: int) -> ExchangeBuffers:
+        if self.buffers is not None:
+            assert self.buffers.tokens == tokens and self.buffers.k == self.k and self.buffers.n_total == self.n_total
+            return self.buffers
+        if tokens not in self._own:
+            arena = SymmetricArena(ExchangeBuffers.nbytes(tokens, self.k, self.n_total), self.weight.device, self.group)
+            self._own[tokens] = ExchangeBuffers(arena, tokens, self.k, self.n_total)
+        return self._own[tokens]
 
-    def forward(self, x: torch.Tensor, sync_before: bool = False) -> torch.Tensor:
-        from .kernels import gemm_int8_scale_scatter, gemm_quantize_rows_pair
-        assert x.ndim == 3 and x.size(0) == 1 and x.is_contiguous() and x.is_cuda
-        m_tokens, k = x.size(1), x.size(2)
-        n_local = self.weight.size(1)
-        n_total = n_local * self.world
-        y, handle = self._buffer(m_tokens)
-        # activations and this rank's weight rows in one launch (both are stored with K contiguous)
-        dev = x.device
-        scale_x = torch.empty((1, m_tokens), dtype=torch.half, device=dev)
-        q_x = torch.empty(x.shape, dtype=torch.int8, device=dev)
-        scale_w = torch.empty((1, n_local), dtype=torch.half, device=dev)
-        q_w = torch.empty(self.weight.shape, dtype=torch.int8, device=dev)
-        with torch.cuda.device(dev):
-            gemm_quantize_rows_pair(1, m_tokens, x.data_ptr(), scale_x.data_ptr(), q_x.data_ptr(), 1, n_local, self.weight.data_ptr(),
-                                    scale_w.data_ptr(), q_w.data_ptr(), k, torch.cuda.current_stream().cuda_stream)
-        if sync_before:
-            handle.barrier(channel=0)
-        dst = [int(handle.buffer_ptrs[p]) + 2 * self.rank * n_local for p in range(self.world)]
+    def _dsts(self, buf: ExchangeBuffers, slot: int, only_local: bool = False):
+        """(y destinations, code destinations, scale destinations) of this rank's contribution, as ctypes arrays."""
+        key = (id(buf), slot, only_local)
+        if key not in self._dst_cache:
+            arena = buf.arena
+            peers = [self.rank] if only_local else _peer_order(self.rank, self.world)
+            rows = buf.tokens // self.world
+            y = [arena.peer_ptr(p, buf.y_off[slot]) + 2 * self.rank * self.n_local for p in peers]
+            qx = [arena.peer_ptr(p, buf.qx_off[slot]) + self.rank * rows * self.k for p in peers]
+            sx = [arena.peer_ptr(p, buf.sx_off[slot]) + 2 * self.rank * rows for p in peers]
+            self._dst_cache[key] = tuple((ctypes.c_void_p * len(v))(*v) for v in (y, qx, sx))
+        return self._dst_cache[key]
+
+    @staticmethod
+    def _stream() -> int:
+        return torch.cuda.current_stream().cuda_stream
+
+    # ---- x present in full on every rank ----
+    def launch(self, x: torch.Tensor, slot: int = 0, only_local: bool = False) -> torch.Tensor:
+        """Quantise x and the weight rows, run the scattering GEMM (two launches, one library call); no barrier.
+        ``only_local``: store this rank's columns into its own y only (the compute phase without the exchange)."""
+        from .kernels import linear_int8_scatter
+        assert x.ndim == 3 and x.size(0) == 1 and x.is_contiguous() and x.is_cuda and x.dtype == torch.half and x.size(2) == self.k
+        tokens = x.size(1)
+        buf = self._buffers_for(tokens)
+        y_dst, _, _ = self._dsts(buf, slot, only_local)
         with torch.cuda.device(x.device):
-            # kernel-level (m, k, n) = (N_local, K, M): A = weights, B = activations, out rows = tokens
-            gemm_int8_scale_scatter(n_local, k, m_tokens, 1, 1, True, False, q_w.data_ptr(), q_x.data_ptr(), scale_x.data_ptr(),
-                                    scale_w.data_ptr(), True, True, dst, n_total, torch.cuda.current_stream().cuda_stream)
-        handle.barrier(channel=1)          # every rank's stores have landed before anyone reads y
+            linear_int8_scatter(tokens, self.k, self.n_local, x.data_ptr(), self.weight.data_ptr(), buf.sx[slot].data_ptr(),
+                                buf.qx[slot].data_ptr(), self.scale_w.data_ptr(), self.q_w.data_ptr(), y_dst, self.n_total, self._stream())
+        return buf.y[slot]
+
+    def forward(self, x: torch.Tensor, sync_before: bool = False, slot: int = 0) -> torch.Tensor:
+        buf = self._buffers_for(x.size(1))
+        if sync_before:
+            buf.arena.barrier(0)           # every rank is done reading the slot's previous contents
+        y = self.launch(x, slot)
+        buf.arena.barrier(1)               # every rank's stores have landed before anyone reads y
         return y
 
     __call__ = forward
+
+    # ---- x sharded by rows ----
+    def quantize_shard(self, x_rows: torch.Tensor, slot: int = 0, tokens: Optional[int] = None) -> None:
+        """x_rows (1, tokens/g, K): this rank's rows [r*tokens/g, (r+1)*tokens/g) of the activations.  One launch
+        quantises them into every rank's code buffer (at that row offset) and this rank's weight rows into its scratch.
+        A barrier must follow before ``gemm`` reads the gathered codes."""
+        from .kernels import gemm_quantize_rows_pair_scatter
+        assert x_rows.ndim == 3 and x_rows.size(0) == 1 and x_rows.is_contiguous() and x_rows.is_cuda and x_rows.dtype == torch.half
+        rows = x_rows.size(1)
+        tokens = rows * self.world if tokens is None else tokens
+        assert rows * self.world == tokens and x_rows.size(2) == self.k
+        buf = self._buffers_for(tokens)
+        _, q_dst, s_dst = self._dsts(buf, slot)
+        with torch.cuda.device(x_rows.device):
+            gemm_quantize_rows_pair_scatter(rows, x_rows.data_ptr(), s_dst, q_dst, self.n_local, self.weight.data_ptr(),
+                                            self.scale_w.data_ptr(), self.q_w.data_ptr(), self.k, self._stream())
+
+    def gemm(self, tokens: int, slot: int = 0, only_local: bool = False) -> torch.Tensor:
+        """The scattering GEMM on the slot's gathered codes and this rank's quantised weight rows."""
+        from .kernels import gemm_int8_scale_scatter
+        buf = self._buffers_for(tokens)
+        y_dst, _, _ = self._dsts(buf, slot, only_local)
+        with torch.cuda.device(self.weight.device):
+            # kernel-level (m, k, n) = (N_local, K, tokens): A = weight codes, B = activation codes, output rows = tokens
+            gemm_int8_scale_scatter(self.n_local, self.k, tokens, 1, 1, True, False, self.q_w.data_ptr(), buf.qx[slot].data_ptr(),
+                                    buf.sx[slot].data_ptr(), self.scale_w.data_ptr(), True, True, y_dst, self.n_total, self._stream())
+        return buf.y[slot]
+
+    def forward_sharded(self, x_rows: torch.Tensor, slot: int = 0) -> torch.Tensor:
+        tokens = x_rows.size(1) * self.world
+        buf = self._buffers_for(tokens)
+        self.quantize_shard(x_rows, slot, tokens)
+        buf.arena.barrier(0)               # every rank's codes and scales have landed
+        y = self.gemm(tokens, slot)
+        buf.arena.barrier(1)               # every rank's output columns have landed
+        return y

@@ -47,6 +47,25 @@ int32_t cpmk_check_device(int32_t *arch_out);
  * GEMM has no user-visible waits). */
 int32_t cpmk_read_status(uint32_t *status_out);
 
+/* Waits for `stream`, then reports whether a kernel that ran on it gave up a bounded wait: CPMK_EDEVICE (with the
+ * kernel's code in cpmk_last_error) if so, CPMK_OK otherwise.  After a failure the status word and the library's
+ * ticket counters of that stream are cleared, so later calls on the stream work again; what the failed kernel should
+ * have written is undefined.  Unlike cpmk_read_status it synchronises one stream, not the device.  No counterpart
+ * in the reference. */
+int32_t cpmk_check_stream(cpmk_stream_t stream);
+
+/* Frees the library's workspace of (current device, stream): call it before destroying a stream that ran calls which
+ * use the workspace (int8 / fp16 GEMM, column quantisation, transposed GEMV, layer norm), so that a process that
+ * creates and destroys streams does not accumulate 16 MiB per stream.  Waits for the device.  At most 256 streams per
+ * device hold a workspace at a time (CPMK_ENOMEM beyond).  No counterpart in the reference. */
+int32_t cpmk_release_workspace(cpmk_stream_t stream);
+
+/* Self-test of the give-up path of the library's device-side waits: a one-block kernel waits up to `limit_us`
+ * microseconds (1..100000) on a barrier on which nothing arrives.  Returns CPMK_OK when the wait ran out, the kernel
+ * recorded its code (0x901) in the stream's status word and returned; the next cpmk_check_stream on that stream
+ * then returns CPMK_EDEVICE once.  Synchronises the stream.  No counterpart in the reference. */
+int32_t cpmk_selftest_bounded_wait(uint32_t limit_us, cpmk_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Quantisation passes (cuda/gemm.cu)
  * ------------------------------------------------------------------------------------------ */
@@ -76,6 +95,18 @@ int32_t cpmk_quantize_rows(int32_t batch, int32_t n, int32_t m, const void *mat,
 int32_t cpmk_quantize_rows_pair(int32_t batch0, int32_t n0, const void *mat0, void *scale_out0, void *q_out0,
                                 int32_t batch1, int32_t n1, const void *mat1, void *scale_out1, void *q_out1,
                                 int32_t m, cpmk_stream_t stream);
+
+/* cpmk_quantize_rows_pair whose FIRST operand (n0, m) is written to `n_dst` (1..8) destinations: scale_dst0[i] and
+ * q_dst0[i] are where the scales (n0) and codes (n0, m) of these rows go in destination i -- this GPU's buffers and
+ * its peers', mapped into this process.  Rank r of g holds rows [r*M/g, (r+1)*M/g) of the activations, quantises them
+ * once, and the stores of the quantising kernel place them at that row offset of every rank's full code buffer: the
+ * all-gather of the int8 activations (1 byte per element over NVLink instead of g uploads of 2 bytes per element)
+ * happens inside the quantisation pass.  Per-row quantisation makes the gathered codes and scales identical to those
+ * of the unsharded tensor.  The second operand (n1, m) -- this rank's weight rows -- is quantised into local buffers
+ * by the same launch; n1 may be 0.  m must be a multiple of 8 and at most 16384; otherwise CPMK_EINVAL.
+ * The caller synchronises the ranks.  No counterpart in the reference (it has no multi-GPU code). */
+int32_t cpmk_quantize_rows_pair_scatter(int32_t n0, const void *mat0, int32_t n_dst, void *const *scale_dst0, void *const *q_dst0,
+                                        int32_t n1, const void *mat1, void *scale_out1, void *q_out1, int32_t m, cpmk_stream_t stream);
 
 /* Fused gemm_calc_scale_transpose + gemm_round_transpose (same call sites, transposed operand):
  * writes scale_out (batch, m) and q_out (batch, n, m).  Uses the library workspace. */
@@ -129,6 +160,14 @@ int32_t cpmk_gemm_int8_dequant_scatter(int32_t m, int32_t k, int32_t n, int32_t 
                                        const void *A, const void *B, const void *scale_x, const void *scale_y,
                                        int32_t broad_cast_x, int32_t broad_cast_y, int32_t n_dst, void *const *dst,
                                        int64_t dst_row_pitch, cpmk_stream_t stream);
+
+/* One column-parallel int8 linear in one call, all buffers the caller's: cpmk_quantize_rows_pair on the activations
+ * x (tokens, k) and this rank's weight rows w (n_local, k), then cpmk_gemm_int8_dequant_scatter of the product into
+ * `n_dst` destinations (y[:, r*n_local : (r+1)*n_local] of every rank).  scale_x (tokens), q_x (tokens, k), scale_w
+ * (n_local), q_w (n_local, k) receive the quantised operands (what cpm_kernels/torch/gemm.py:107-112 saves for
+ * backward).  Replaces the six launches and six allocations of cpm_kernels/torch/gemm.py:86-113 for this layout. */
+int32_t cpmk_linear_int8_scatter(int32_t tokens, int32_t k, int32_t n_local, const void *x, const void *w, void *scale_x, void *q_x,
+                                 void *scale_w, void *q_w, int32_t n_dst, void *const *dst, int64_t dst_row_pitch, cpmk_stream_t stream);
 
 /* Layer norm over the MIDDLE axis of mat (batch, n, m) fp16, per-row affine, and quantisation along that same axis,
  * without storing the intermediate tensors: what cpm_kernels runs as four kernels between a layer norm and the int8

@@ -304,8 +304,15 @@ def bmm_int8(A: np.ndarray, aT: bool, B: np.ndarray, bT: bool):
 def build_c_oracle() -> str:
     """Compile oracle/quant_linear.c (and, where a reference checkout is present, the reference's
     own device code into oracle/_ref/) with oracle/Makefile; return the path of the C library."""
-    subprocess.run(["make", "-s", "-C", _HERE, "all"], check=True, stdout=subprocess.DEVNULL)
+    subprocess.run(["make", "-s", "-C", _HERE, "all", "REFERENCE_DIR=" + reference_dir()], check=True, stdout=subprocess.DEVNULL)
     return os.path.join(_HERE, "_build", "libquant_linear_oracle.so")
+
+
+def reference_dir() -> str:
+    """Where a cpm_kernels checkout is looked for: $CPM_KERNELS_REFERENCE_DIR, else a directory named ``reference``
+    beside this repository.  Empty when there is none (the prebuilt oracle/_ref files are then used as they are)."""
+    cand = os.environ.get("CPM_KERNELS_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.exists(os.path.join(cand, "cuda", "gemm.cu")) else ""
 
 
 def _c_oracle_path() -> str:

@@ -25,7 +25,8 @@ def close(got_fp16, want_f64):
 
 
 ROWS = [(16, 2222, 128), (1, 10240, 4096), (4, 1024, 4096), (3, 37, 24), (2, 9, 4100), (1, 5, 30), (2, 8, 7),
-        (3, 1000, 1032), (2, 2371, 6400)]                          # streaming kernel: ragged row groups, longest rows it takes
+        (3, 1000, 1032), (2, 2371, 6400),
+        (4, 10240, 4096), (16, 10240, 4096)]                       # configuration 3 with per-batch matrices at full size                          # streaming kernel: ragged row groups, longest rows it takes
 
 
 @pytest.mark.parametrize("batch,dim_out,dim_in", ROWS)
@@ -45,7 +46,8 @@ def test_gemv_fp16(G, batch, dim_out, dim_in):
 
 
 COLS = [(16, 128, 2222), (1, 10240, 4096), (1, 4096, 10240), (4, 1024, 4096), (3, 40, 24), (2, 12, 9), (2, 264, 100),
-        (4, 4096, 2048), (8, 2056, 1000), (16, 10240, 1024)]      # the last three take the shared-memory streaming kernel
+        (4, 4096, 2048), (8, 2056, 1000), (16, 10240, 1024),
+        (4, 10240, 4096), (16, 10240, 4096), (4, 4096, 10240)]      # the last three take the shared-memory streaming kernel
 
 
 @pytest.mark.parametrize("batch,dim_out,dim_in", COLS)

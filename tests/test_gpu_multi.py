@@ -1,5 +1,7 @@
 """Multi-GPU parity (needs at least two GPUs; skipped otherwise): the column-parallel layer with an NCCL all-gather and the
-layer whose GEMM epilogue scatters its output slice to every rank, both against the unsharded oracle, bit for bit."""
+layer whose kernels do the exchanges themselves (GEMM epilogue scatters the output columns; the quantiser scatters the
+int8 codes of row-sharded activations), all against the unsharded oracle, bit for bit.  tests/dist_gpu_worker.py is the
+per-rank program.  (bench.py --gpus N repeats the comparison on its own tensors after its timed region.)"""
 import os
 import socket
 import subprocess
@@ -20,11 +22,21 @@ def _free_port():
     return port
 
 
-@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_sharded_layers_on_two_gpus():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+def _run_workers(nproc):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc), "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "dist_gpu_worker.py")]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
+    for rank in range(nproc):
+        assert "rank %d ok" % rank in r.stdout
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_layers_on_two_gpus():
+    _run_workers(2)
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 4, reason="needs four GPUs")
+def test_sharded_layers_on_all_gpus():
+    _run_workers(8 if torch.cuda.device_count() >= 8 else 4)

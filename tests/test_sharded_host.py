@@ -34,6 +34,39 @@ def test_shard_bounds():
     assert shard_bounds(4096, 1, 0) == (0, 4096)
 
 
+def test_peer_order_spreads_the_first_destination():
+    """Rank r stores to r+1, r+2, ..., r: no two ranks start on the same peer, and every rank ends on itself."""
+    from cpm_kernels_b200.sharded import _peer_order
+    for world in (1, 2, 4, 8):
+        orders = [_peer_order(r, world) for r in range(world)]
+        for r, o in enumerate(orders):
+            assert sorted(o) == list(range(world)) and o[-1] == r
+        for step in range(world):
+            assert len({o[step] for o in orders}) == world
+
+
+def test_arena_carves_aligned_buffers_at_rank_independent_offsets():
+    """One rank, host memory: the carving arithmetic (what makes `base[peer] + offset` valid on every rank)."""
+    import torch
+    from cpm_kernels_b200.sharded import ExchangeBuffers, SymmetricArena
+    need = ExchangeBuffers.nbytes(48, 64, 96)
+    arena = SymmetricArena(need, torch.device("cpu"))
+    assert arena.world == 1 and arena.rank == 0
+    buf = ExchangeBuffers(arena, 48, 64, 96)
+    assert arena.used <= arena.nbytes == need
+    offs = buf.y_off + buf.qx_off + buf.sx_off
+    assert all(o % 256 == 0 for o in offs) and len(set(offs)) == 6
+    assert buf.y[1].shape == (1, 48, 96) and buf.y[1].dtype == torch.half and buf.qx[0].dtype == torch.int8
+    assert buf.y[1].data_ptr() == arena.peer_ptr(0, buf.y_off[1])
+    arena.barrier(0)                                           # one rank: nothing to wait for
+    try:
+        arena.carve((1 << 20,), torch.half)
+    except RuntimeError as e:
+        assert "full" in str(e)
+    else:
+        raise AssertionError("an over-full arena must refuse")
+
+
 def test_reference_arm_under_torchrun_prints_one_line():
     """bench.py --impl reference with two ranks: rank 0 alone runs and prints; the other exits 0 without work."""
     import json
