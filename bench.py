@@ -274,34 +274,83 @@ class Run:
         print(json.dumps(line), flush=True)
 
 
-class Lanes:
-    """The linears of the synthetic stack are independent, so they are spread over several streams: while one linear's
-    GEMM drains its output over NVLink, the others' quantisation passes and GEMMs run beside it (the scattering GEMM's
-    persistent grid leaves part of the SMs free for that)."""
+SLOTS = 3          # result buffers per linear shape that the sharded steps rotate through
 
-    def __init__(self, run: Run, n_lanes: int, sm_margin: int):
+
+class Lanes:
+    """How the sharded steps are issued.  The linears of the synthetic stack are independent, so linear i runs on lane
+    (stream) i % n: while one linear's GEMM drains its output over NVLink, the others' quantisation passes and GEMMs run
+    beside it (the scattering GEMM's persistent grid leaves `sm_margin` SMs free for that).  The main stream only joins
+    the lanes and runs the rank barrier of each step.  Steps are pipelined: step s writes result buffer s % 3, whose
+    previous contents (step s-3) every rank has finished with once the barrier of step s-2 has passed, so the lanes of
+    step s wait for THAT barrier, not for the latest one -- the link keeps draining step s-1 while step s computes."""
+
+    def __init__(self, run: Run, n_lanes: int, sm_margin: int, arena):
         from cpm_kernels_b200.library import cpmk
-        self.run, self.cpmk, self.sm_margin = run, cpmk, sm_margin
-        self.side = [run.torch.cuda.Stream() for _ in range(max(0, n_lanes - 1))]
+        torch = run.torch
+        self.run, self.cpmk, self.arena = run, cpmk, arena
+        self.sm_margin = sm_margin if n_lanes > 1 else 0
+        self.streams = [torch.cuda.Stream() for _ in range(max(1, n_lanes))]
+        for s in self.streams:
+            s.wait_stream(run.stream)
+        self.count = 0                       # steps issued so far
+        self.passed = {}                     # step -> event recorded on the main stream after that step's barrier
+        self.margin(True)
 
     def __len__(self):
-        return len(self.side) + 1
+        return len(self.streams)
 
-    def fork(self):
-        for s in self.side:
+    def margin(self, on: bool):
+        self.cpmk.set_gemm_sm_margin(self.sm_margin if on and self.sm_margin > 0 else -1)
+
+    def slot(self) -> int:
+        return self.count % SLOTS
+
+    def run_step(self, work, barrier: bool = True):
+        """work: one callable per linear, called as work[i](slot) under lane i's stream.  Returns their results."""
+        torch, main = self.run.torch, self.run.stream
+        slot, gate = self.slot(), self.passed.get(self.count - (SLOTS - 1))
+        out = [None] * len(work)
+        used = set()
+        for i, fn in enumerate(work):
+            lane = self.streams[i % len(self.streams)]
+            with torch.cuda.stream(lane):
+                if gate is not None and lane not in used:
+                    lane.wait_event(gate)
+                used.add(lane)
+                out[i] = fn(slot)
+        for lane in used:
+            main.wait_stream(lane)
+        if barrier:
+            self.arena.barrier(1)            # every rank's stores of this step have landed
+            ev = torch.cuda.Event()
+            ev.record(main)
+            self.passed[self.count] = ev
+            self.passed.pop(self.count - SLOTS, None)
+        self.count += 1
+        return out
+
+    def run_after_main(self, work):
+        """work[i]() under lane i's stream, all lanes ordered after the main stream's work so far; the main stream
+        then waits for the lanes (no barrier, no pipelining)."""
+        torch, main = self.run.torch, self.run.stream
+        out, used = [None] * len(work), set()
+        for i, fn in enumerate(work):
+            lane = self.streams[i % len(self.streams)]
+            with torch.cuda.stream(lane):
+                if lane not in used:
+                    lane.wait_stream(main)
+                used.add(lane)
+                out[i] = fn()
+        for lane in used:
+            main.wait_stream(lane)
+        return out
+
+    def drain(self):
+        """Order the lanes after everything issued so far on the main stream (used between measurements)."""
+        for s in self.streams:
             s.wait_stream(self.run.stream)
-        if self.side:
-            self.cpmk.set_gemm_sm_margin(self.sm_margin)
-
-    def on(self, i: int):
-        lane = i % len(self)
-        return self.run.torch.cuda.stream(self.side[lane - 1]) if lane else contextlib.nullcontext()
-
-    def join(self):
-        for s in self.side:
-            self.run.stream.wait_stream(s)
-        if self.side:
-            self.cpmk.set_gemm_sm_margin(-1)
+        self.passed.clear()
 
 
 def cfg2_tensors(run: Run, want_full_weights: bool = False):
@@ -349,25 +398,23 @@ def run_ours(args) -> None:
     exchange = "none"
     want_cfg5 = not args.kernels_only and not args.no_cfg5 and M_TOKENS == 4096
     if world > 1:
-        nbytes = sum(ExchangeBuffers.nbytes(M_TOKENS, k, n) for _, n, k in SHAPES)
+        nbytes = sum(ExchangeBuffers.nbytes(M_TOKENS, k, n, SLOTS) for _, n, k in SHAPES)
         if want_cfg5:
-            nbytes += sum(ExchangeBuffers.nbytes(CFG5_TOKENS, k, n) for _, n, k in SHAPES)
+            nbytes += sum(ExchangeBuffers.nbytes(CFG5_TOKENS, k, n, SLOTS) for _, n, k in SHAPES)
         arena = SymmetricArena(nbytes + (1 << 20), dev)
-        bufs = [ExchangeBuffers(arena, M_TOKENS, k, n) for _, n, k in SHAPES]
+        bufs = [ExchangeBuffers(arena, M_TOKENS, k, n, SLOTS) for _, n, k in SHAPES]
         layers = [FusedColumnParallelInt8Linear(w, buffers=b) for w, b in zip(ws, bufs)]
         n_lanes = int(os.environ.get("CPMK_BENCH_FUSED_STREAMS", "4")) if args.exchange != "fused1" else 1
-        lanes = Lanes(run, n_lanes, int(os.environ.get("CPMK_BENCH_FUSED_SM_MARGIN", "32")))
+        lanes = Lanes(run, n_lanes, int(os.environ.get("CPMK_BENCH_FUSED_SM_MARGIN", "32")), arena)
         exchange = ("fused: the GEMM epilogue TMA-stores its output columns into every rank's full-width result over NVLink; activations present "
-                    "on every rank; linears on %d streams, scattering GEMM grids leave %d SMs free; one rank barrier per step; results alternate "
-                    "between two buffers" % (len(lanes), lanes.sm_margin))
+                    "on every rank; linears on %d streams, scattering GEMM grids leave %d SMs free; one rank barrier per step; results rotate "
+                    "through %d buffers, so a step's exchange drains while the next step computes" % (len(lanes), lanes.sm_margin, SLOTS))
         if args.exchange == "nccl":
             nccl_layers = [ColumnParallelInt8Linear(w) for w in ws]
             gathered = [torch.empty((world, M_TOKENS, n // world), dtype=torch.half, device=dev) for _, n, _ in SHAPES]
             comm_stream = torch.cuda.Stream()
             os.environ.setdefault("CPMK_GEMM_SM_MARGIN", "16")       # the collective's kernels run beside the persistent GEMM grid
             exchange = "nccl all_gather_into_tensor on a side stream"
-
-    step_no = [0]
 
     def step(only_local: bool = False):
         """One pass over the four linears.  N = 1: the public bmm.  N > 1: one library call per linear (quantise both
@@ -389,17 +436,8 @@ def run_ours(args) -> None:
             if not only_local:
                 stream.wait_stream(comm_stream)
             return out
-        slot = step_no[0] & 1
-        step_no[0] += 1
-        lanes.fork()
-        out = []
-        for i, (layer, x) in enumerate(zip(layers, xs)):
-            with lanes.on(i):
-                out.append(layer.launch(x, slot, only_local))
-        lanes.join()
-        if not only_local:
-            arena.barrier(1)
-        return out
+        return lanes.run_step([(lambda slot, layer=layer, x=x: layer.launch(x, slot, only_local)) for layer, x in zip(layers, xs)],
+                              barrier=not only_local)
 
     for _ in range(warmup):
         step()
@@ -418,8 +456,7 @@ def run_ours(args) -> None:
     gemm_events = []
 
     def step_recorded():
-        slot = step_no[0] & 1
-        step_no[0] += 1
+        slot = 0
         for i, (x, w) in enumerate(zip(xs, ws)):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             if world == 1 or nccl_layers is not None:
@@ -439,9 +476,15 @@ def run_ours(args) -> None:
         if layers is not None and nccl_layers is None:
             arena.barrier(1)
 
+    if lanes is not None:
+        run.barrier()
+        lanes.margin(False)
     for _ in range(args.steps):
         step_recorded()
     run.barrier()
+    if lanes is not None:
+        lanes.drain()
+        lanes.margin(True)
     clocks = sampler.stop() if rank == 0 else None
 
     phases = None
@@ -650,12 +693,7 @@ def measure_e2e_sharded(run: Run, xs, layers, lanes, arena) -> dict:
         if downloaded[cur] is not None:
             stream.wait_event(downloaded[cur])    # peers overwrite y[cur] after the next barrier: our download of it must be over
         arena.barrier(0)                          # every rank's codes have landed; every rank is done with y[cur]
-        lanes.fork()
-        ys = []
-        for i, layer in enumerate(layers):
-            with lanes.on(i):
-                ys.append(layer.gemm(M_TOKENS, cur))
-        lanes.join()
+        ys = lanes.run_after_main([(lambda layer=layer: layer.gemm(M_TOKENS, cur)) for layer in layers])
         arena.barrier(1)                          # every rank's output columns have landed
         done = torch.cuda.Event()
         done.record(stream)
@@ -841,12 +879,12 @@ def measure_cfg5(run: Run, arena, lanes, ct) -> dict:
     n_layers = int(os.environ.get("CPMK_BENCH_CFG5_LAYERS", str(CFG5_LAYERS)))
     steps = 2
     if arena is None:
-        arena = SymmetricArena(sum(ExchangeBuffers.nbytes(CFG5_TOKENS, k, n) for _, n, k in SHAPES) + (1 << 20), dev)
+        arena = SymmetricArena(sum(ExchangeBuffers.nbytes(CFG5_TOKENS, k, n, SLOTS) for _, n, k in SHAPES) + (1 << 20), dev)
     if lanes is None:
-        lanes = Lanes(run, 1, 0)
+        lanes = Lanes(run, 1, 0, arena)
     gen = torch.Generator(device=dev).manual_seed(5)
     xs = [torch.randn((1, CFG5_TOKENS, k), generator=gen, device=dev).half() for _, _, k in SHAPES]
-    bufs = [ExchangeBuffers(arena, CFG5_TOKENS, k, n) for _, n, k in SHAPES]
+    bufs = [ExchangeBuffers(arena, CFG5_TOKENS, k, n, SLOTS) for _, n, k in SHAPES]
     scratch = [(torch.empty((1, n // world, k), dtype=torch.int8, device=dev), torch.empty((1, n // world), dtype=torch.half, device=dev))
                for _, n, k in SHAPES]
     per = CFG5_BLOCKS // world
@@ -856,14 +894,10 @@ def measure_cfg5(run: Run, arena, lanes, ct) -> dict:
     weight_bytes = sum(w.weight.numel() * 2 for row in layers for w in row)
 
     def stack(only_local: bool):
-        for l, row in enumerate(layers):
-            lanes.fork()
-            for i, layer in enumerate(row):
-                with lanes.on(i):
-                    layer.launch(xs[i], l & 1, only_local)
-            lanes.join()
-            if not only_local:
-                arena.barrier(1)                 # one rank barrier per layer: the layer's outputs are complete on every rank
+        # one rank barrier per layer (the layer's outputs are complete on every rank), pipelined as in the main step
+        for row in layers:
+            lanes.run_step([(lambda slot, layer=layer, x=x: layer.launch(x, slot, only_local)) for layer, x in zip(row, xs)],
+                           barrier=not only_local)
 
     ops = total_ops(CFG5_TOKENS) * n_layers
     ms_e2e = run.timed(lambda: stack(False), steps, warm=1)
@@ -880,6 +914,8 @@ def measure_cfg5(run: Run, arena, lanes, ct) -> dict:
         def single():
             for x, w in zip(xs, w_full):
                 ct.bmm(x, False, w, True, int8=True)
+        run.barrier()
+        lanes.margin(False)
         single()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -888,6 +924,7 @@ def measure_cfg5(run: Run, arena, lanes, ct) -> dict:
             single()
         b.record(stream)
         torch.cuda.synchronize()
+        lanes.margin(True)
         single_tops = total_ops(CFG5_TOKENS) / (a.elapsed_time(b) / 3 * 1e-3) / 1e12
         out["gemm_phase"]["one_gpu_unsharded_TOPS"] = single_tops
         out["gemm_phase"]["efficiency"] = out["gemm_phase"]["TOPS"] / (world * single_tops)

@@ -52,6 +52,7 @@ constexpr uint32_t kErrProducerWait = 0x101;
 constexpr uint32_t kErrMmaWaitFull = 0x102;
 constexpr uint32_t kErrMmaWaitTmem = 0x103;
 constexpr uint32_t kErrEpilogueWait = 0x104;
+constexpr uint32_t kErrForwardWaitTile = 0x105;
 
 struct GemmParams {
     int32_t R, C, K;              // out is (batch, R, C); reduction length K
@@ -65,6 +66,10 @@ struct GemmParams {
     int32_t bcast_r, bcast_c;
     int32_t tma_store;            // the two-CTA kernel writes its output with TMA stores (needs 16-byte row pitch)
     int32_t n_dst;                // number of destinations each output tile is stored to (1, or one per GPU when scattering)
+    int32_t send_pairs;           // > 0: the last `send_pairs` CTA pairs of the grid forward finished tiles from destination 0 to the others
+    uint32_t *flags;              // send_pairs > 0: one counter per (pair tile, CTA of the pair), zero at launch; 8 = all epilogue warps have stored
+    __half *fwd_dst[8];           // send_pairs > 0: element (0, 0, 0) of every destination (0: this GPU's own, where the computing CTAs store)
+    int64_t out_ld;               // row pitch of the destinations in elements
     uint32_t *status;
     // tile index -> (batch, column block, row block) without integer division: multipliers and shifts for
     // tiles_r * tiles_c and for tiles_r (set_tile_divisors)
@@ -600,6 +605,84 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const O
     if (staged > 0) flush();
 }
 
+// ------------------------------------------------------------------------------------------------
+// Forwarding CTAs.  When the output goes to several GPUs, stores that cross NVLink are slow to drain: issued by the
+// CTAs that compute, they sit in the same per-SM TMA queue as the operand loads and in the same staging tiles the
+// epilogue wants back, and the main loop ends up waiting for the link (measured: GEMM time = compute + transfer).
+// So the computing CTAs store only to destination 0 -- this GPU's own buffer -- and signal each finished 128 x 256
+// CTA tile through a counter; the last `send_pairs` CTA pairs of the same grid do nothing but wait for those counters
+// and copy finished tiles from destination 0 (out of L2, where they were just written) to every other destination.
+// The copy uses ordinary 16-byte loads and stores, a whole 512-byte tile row per warp instruction: TMA stores to a
+// peer were measured to hold up the TMA loads queued behind them on the same SM, plain stores do not.  A couple of
+// dozen SMs saturate the link; the others compute at full speed, and transfer and arithmetic overlap tile by tile
+// inside one kernel.  Only stores cross the link (no load touches a peer's memory, nothing is multicast).  The wait
+// for a tile is bounded.
+// ------------------------------------------------------------------------------------------------
+constexpr int kFwdRows = kBM / kEpiWarps2;              // rows of a CTA tile per forwarding warp: 16
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void forward_tiles(const GemmParams &prm, int send_pair, uint32_t rank) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp < 2) return;                                // as many forwarding warps as there are epilogue warps
+    const int w = warp - 2;
+    const int64_t ld = prm.out_ld;
+    for (int tile = send_pair; tile < prm.total_tiles; tile += prm.send_pairs) {
+        int b, c_blk, r_blk;
+        tile_coords(prm, tile, b, c_blk, r_blk);
+        const int row0 = r_blk * (2 * kBM) + (int)rank * kBM + w * kFwdRows;
+        const int col = c_blk * kBN + lane * 8;           // this lane's eight columns (16 bytes) of every row
+        if (row0 >= prm.R) continue;                      // uniform across the warp
+        // lane 0 waits until all eight epilogue warps of the computing CTA have stored their part of the tile
+        int ok = 1;
+        if (lane == 0) {
+            const uint32_t *flag = prm.flags + ((size_t)tile * 2 + rank);
+            uint64_t t0 = 0;
+            for (uint32_t spin = 0; ld_acquire_gpu(flag) < (uint32_t)kEpiWarps2; ++spin) {
+                __nanosleep(64);
+                if ((spin & 0x3ffu) == 0x3ffu) {
+                    const uint64_t now = global_timer_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > kWaitLimitNs) {
+                        atomicCAS(prm.status, 0u, kErrForwardWaitTile);
+                        ok = 0;
+                        break;
+                    }
+                }
+            }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);             // (also orders the other lanes' loads after lane 0's acquire)
+        if (!ok) return;
+        const bool col_ok = col < prm.C;                  // C % 8 == 0: the eight columns are in or out together
+        const int64_t offset = ((int64_t)b * prm.R + row0) * ld + col;
+        const __half *src = prm.fwd_dst[0] + offset;
+#pragma unroll
+        for (int part = 0; part < kFwdRows / 8; ++part) {
+            uint4 v[8];
+            bool in[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int r = part * 8 + i;
+                in[i] = col_ok && row0 + r < prm.R;
+                v[i] = in[i] ? __ldcg(reinterpret_cast<const uint4 *>(src + r * ld)) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int d = 1; d < kMaxDst; ++d) {
+                if (d < prm.n_dst) {
+                    __half *dst = prm.fwd_dst[d] + offset;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (in[i]) *reinterpret_cast<uint4 *>(dst + (part * 8 + i) * ld) = v[i];
+                }
+            }
+        }
+    }
+}
+
 // P_MN / Q_MN: the row / column operand is stored with its rows contiguous (k is the slow axis) instead of k:
 // the reference's bT / !aT layouts.  Their tensor maps then have (rows, k, batch) extents and 128 x kBK boxes, the
 // shared-memory tiles are MN-major, and bits 15 / 16 of the instruction descriptor say so.
@@ -626,6 +709,12 @@ __device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CU
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_cta_rank();
     const bool leader = rank == 0;
+    // the last send_pairs pairs of the grid forward finished tiles to the other destinations instead of computing
+    const int pair = blockIdx.x >> 1, num_pairs = (gridDim.x >> 1) - prm.send_pairs;
+    if (prm.send_pairs > 0 && pair >= num_pairs) {
+        forward_tiles(prm, pair - num_pairs, rank);
+        return;
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -646,8 +735,6 @@ __device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CU
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const int tiles_per_batch = prm.tiles_r * prm.tiles_c;   // in 256 x 256 pair tiles
 
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
@@ -745,6 +832,14 @@ __device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CU
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(tmem_empty_bar + 8 * acc, 0));
+            if (prm.send_pairs > 0 && lane == 0) {
+                // tell the forwarding CTAs that this warp's part of the tile is in destination 0: its stores have completed
+                // (not merely been read out of shared memory), then a release at GPU scope, then the count
+                bulk_wait_all();
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+                __threadfence();
+                atomicAdd(prm.flags + ((size_t)tile * 2 + rank), 1u);
+            }
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
         }
@@ -999,6 +1094,8 @@ bool encode_output_raw(CUtensorMap *map, void *ptr, int32_t R, int32_t C, int64_
 }
 
 std::atomic<int> g_sm_margin{-1};
+std::atomic<int> g_forward_sms{-1};
+constexpr size_t kFlagBytes = 1u << 20;                 // tile counters of the forwarding CTAs: the last MiB of the workspace
 thread_local int32_t g_last_path = 0;
 thread_local int32_t g_last_variant = 0;
 
@@ -1121,6 +1218,10 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
         prm.scale_r = static_cast<const __half *>(scale_x); prm.scale_c = static_cast<const __half *>(scale_y);
         prm.bcast_r = bx; prm.bcast_c = by;
         prm.tma_store = 0;
+        prm.send_pairs = 0;
+        prm.flags = nullptr;
+        prm.out_ld = 0;
+        for (int d = 0; d < 8; ++d) prm.fwd_dst[d] = nullptr;
         prm.status = ws.status();
         rc = prepare_tc_kernels(info.device);
         if (rc) return rc;
@@ -1146,8 +1247,30 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
             if (total < (int64_t(1) << 31) && enc_p && enc_q) {
                 prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.total_tiles = (int32_t)total;
                 set_tile_divisors(&prm);
-                const int pairs = (int)(total < max_pairs ? total : max_pairs);
-                const dim3 grid(2 * pairs);
+                // Several destinations: part of the grid can forward finished tiles from destination 0 to the others (see
+                // forward_tiles).  CPMK_GEMM_FORWARD_SMS / cpmk_set_gemm_forward_sms: how many SMs do that (default 0: none,
+                // every computing CTA stores to all destinations itself).
+                int send_pairs = 0;
+                if (scatter && n_dst > 1) {
+                    int sms = g_forward_sms.load(std::memory_order_relaxed);
+                    if (sms < 0) {
+                        const char *fe = getenv("CPMK_GEMM_FORWARD_SMS");
+                        sms = fe ? atoi(fe) : 0;
+                    }
+                    const int want = (sms + 1) / 2;
+                    if (want > 0 && max_pairs - want >= 8 && (size_t)total * 2 * sizeof(uint32_t) <= kFlagBytes) send_pairs = want;
+                }
+                const int compute_cap = max_pairs - send_pairs;
+                const int pairs = (int)(total < compute_cap ? total : compute_cap);
+                const dim3 grid(2 * (pairs + send_pairs));
+                prm.send_pairs = send_pairs;
+                prm.flags = nullptr;
+                if (send_pairs > 0) {
+                    for (int d = 0; d < kMaxDst; ++d) prm.fwd_dst[d] = d < n_dst ? static_cast<__half *>(dsts[d]) : nullptr;
+                    prm.out_ld = dst_ld;
+                    prm.flags = reinterpret_cast<uint32_t *>(ws.base + Workspace::kBytes - kFlagBytes);
+                    CPMK_CUDA_TRY(cudaMemsetAsync(prm.flags, 0, (size_t)total * 2 * sizeof(uint32_t), stream));
+                }
                 OutMaps tmap_o;
                 memset(&tmap_o, 0, sizeof(tmap_o));
                 prm.n_dst = scatter ? n_dst : 1;
@@ -1377,6 +1500,11 @@ int32_t cpmk_gemm_fp16(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t 
 
 int32_t cpmk_set_gemm_sm_margin(int32_t sms) {
     g_sm_margin.store(sms < 0 ? -1 : sms, std::memory_order_relaxed);
+    return CPMK_OK;
+}
+
+int32_t cpmk_set_gemm_forward_sms(int32_t sms) {
+    g_forward_sms.store(sms < 0 ? -1 : sms, std::memory_order_relaxed);
     return CPMK_OK;
 }
 

@@ -48,6 +48,7 @@ SIGNATURES = {
     "cpmk_quantize_rows_pair": [_i, _i, _p, _p, _p, _i, _i, _p, _p, _p, _i, _p],
     "cpmk_layernorm_quantize_cols": [_i, _i, _i, _p, ctypes.c_float, _i, _p, _p, _p, _p, _p],
     "cpmk_set_gemm_sm_margin": [_i],
+    "cpmk_set_gemm_forward_sms": [_i],
     "cpmk_gelu_forward": [_i, _i, _p, _p, _p],
     "cpmk_transpose": [_i, _i, _i, _p, _p, _p],
     "cpmk_gemm_int8_dequant_gelu": [_i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p, _p],
@@ -115,6 +116,11 @@ def release_workspace(stream) -> None:
 def set_gemm_sm_margin(sms: int) -> None:
     """Keep the persistent GEMM grid off ``sms`` SMs (0: use all; negative: follow CPMK_GEMM_SM_MARGIN)."""
     call("cpmk_set_gemm_sm_margin", int(sms))
+
+
+def set_gemm_forward_sms(sms: int) -> None:
+    """How many SMs of a scattering GEMM forward finished tiles to the other destinations (0: none; negative: default)."""
+    call("cpmk_set_gemm_forward_sms", int(sms))
 
 
 def last_gemm_variant() -> int:

@@ -156,9 +156,10 @@ class ExchangeBuffers:
 
 
 def _peer_order(rank: int, world: int) -> List[int]:
-    """Destinations in the order rank+1, rank+2, ..., rank: at any moment the ranks store to different peers instead of
-    all converging on rank 0 first."""
-    return [(rank + 1 + i) % world for i in range(world)]
+    """Destinations in the order rank, rank+1, rank+2, ...: the rank's own buffer first (the scattering GEMM computes into
+    destination 0 and forwards from there), then the peers starting with its neighbour, so that at any moment the ranks
+    store to different peers instead of all converging on rank 0."""
+    return [(rank + i) % world for i in range(world)]
 
 
 class FusedColumnParallelInt8Linear:

@@ -155,6 +155,9 @@ int32_t cpmk_gemm_int8_dequant(int32_t m, int32_t k, int32_t n, int32_t batchA, 
  * cpm_kernels' callers would run after a column-parallel linear happens inside the GEMM's epilogue (TMA stores over
  * NVLink), without a second pass over the slice.  No counterpart in the reference (it has no multi-GPU code).
  * Needs the tensor-core kernel (extents and pointers multiples of 16 bytes); otherwise CPMK_EINVAL.
+ * dst[0] should be the destination in THIS GPU's memory: when forwarding is switched on (cpmk_set_gemm_forward_sms) the
+ * computing CTAs store only there, and a few CTAs of the same grid copy each finished tile from dst[0] to the other
+ * destinations (stores over NVLink only).
  * The caller synchronises the ranks (all stores of a call are complete when the call's kernel has finished). */
 int32_t cpmk_gemm_int8_dequant_scatter(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT,
                                        const void *A, const void *B, const void *scale_x, const void *scale_y,
@@ -212,6 +215,13 @@ int32_t cpmk_gemm_fp16(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t 
  * 0 = use every SM; a negative value returns the choice to the environment variable CPMK_GEMM_SM_MARGIN.
  * No counterpart in the reference (cublasLt picks its own grid). */
 int32_t cpmk_set_gemm_sm_margin(int32_t sms);
+
+/* How many SMs of a scattering GEMM (cpmk_gemm_int8_dequant_scatter with more than one destination) forward finished
+ * output tiles from destination 0 to the other destinations instead of computing, from now on (process-wide).
+ * 0 = none: every computing CTA stores to all destinations itself; a negative value returns the choice to the
+ * environment variable CPMK_GEMM_FORWARD_SMS, and without it to the default (0).
+ * No counterpart in the reference. */
+int32_t cpmk_set_gemm_forward_sms(int32_t sms);
 
 /* Which GEMM kernel the last cpmk_gemm_int8* / cpmk_gemm_fp16 call on this thread selected:
  * 1 = tcgen05 tensor-core kernel, 2 = generic SIMT kernel.  For tests and the benchmark. */

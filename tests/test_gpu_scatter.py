@@ -97,3 +97,35 @@ def test_linear_scatter_to_two_local_destinations():
         assert (got[:, col0:col0 + n_local].view(np.uint16) == want.view(np.uint16)).all()
         assert (got[:, :col0] == 5.0).all() and (got[:, col0 + n_local:] == 5.0).all()
     assert cpmk.read_status() == 0
+
+
+@pytest.mark.parametrize("tokens,k,n_local,n_dst", [(4096, 1024, 1536, 4), (1000, 512, 520, 3), (256, 4096, 256, 8), (2048, 10240, 512, 2)])
+def test_forwarding_ctas_equal_direct_stores(tokens, k, n_local, n_dst):
+    """With more than one destination a few CTAs of the GEMM's grid forward finished tiles from destination 0 to the
+    others.  Every destination must receive exactly what the direct form (every computing CTA stores everywhere) and the
+    oracle give, for many tiles per forwarding CTA, ragged edges, and fewer tiles than forwarding CTAs."""
+    x = randn_fp16((1, tokens, k), 27)
+    w = randn_fp16((1, n_local, k), 28, 0.02)
+    xd, wd = x.cuda(), w.cuda()
+    n_total = n_local * n_dst
+    sx = torch.empty((tokens,), dtype=torch.half, device="cuda")
+    qx = torch.empty((tokens, k), dtype=torch.int8, device="cuda")
+    sw = torch.empty((n_local,), dtype=torch.half, device="cuda")
+    qw = torch.empty((n_local, k), dtype=torch.int8, device="cuda")
+    want = ql.bmm_int8(np16(x), False, np16(w), True)["out"][0].view(np.uint16)
+    try:
+        for forward_sms in (0, 16, 6):
+            cpmk.set_gemm_forward_sms(forward_sms)
+            for rep in range(2):                                                  # twice: the tile counters start from zero each call
+                ys = [torch.full((tokens, n_total), 5.0, dtype=torch.half, device="cuda") for _ in range(n_dst)]
+                ck.linear_int8_scatter(tokens, k, n_local, xd.data_ptr(), wd.data_ptr(), sx.data_ptr(), qx.data_ptr(), sw.data_ptr(), qw.data_ptr(),
+                                       [y.data_ptr() + 2 * n_local * d for d, y in enumerate(ys)], n_total, _s())
+                torch.cuda.synchronize()
+                for d, y in enumerate(ys):
+                    got = y.cpu().numpy()
+                    assert (got[:, n_local * d:n_local * (d + 1)].view(np.uint16) == want).all(), (forward_sms, rep, d)
+                    got[:, n_local * d:n_local * (d + 1)] = 5.0
+                    assert (got == 5.0).all()                                      # nothing else is touched
+            assert cpmk.read_status() == 0
+    finally:
+        cpmk.set_gemm_forward_sms(-1)

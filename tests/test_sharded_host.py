@@ -35,12 +35,12 @@ def test_shard_bounds():
 
 
 def test_peer_order_spreads_the_first_destination():
-    """Rank r stores to r+1, r+2, ..., r: no two ranks start on the same peer, and every rank ends on itself."""
+    """Rank r stores to r, r+1, r+2, ...: its own buffer first, and at every position the ranks address different peers."""
     from cpm_kernels_b200.sharded import _peer_order
     for world in (1, 2, 4, 8):
         orders = [_peer_order(r, world) for r in range(world)]
         for r, o in enumerate(orders):
-            assert sorted(o) == list(range(world)) and o[-1] == r
+            assert sorted(o) == list(range(world)) and o[0] == r
         for step in range(world):
             assert len({o[step] for o in orders}) == world
 
