@@ -394,6 +394,7 @@ def run_ours(args) -> None:
 
     # ---- N > 1: peer-mapped buffers and the layers whose GEMM epilogue is the all-gather ----
     arena = layers = lanes = None
+    use_multicast = False
     nccl_layers, gathered, comm_stream = None, [], None
     exchange = "none"
     want_cfg5 = not args.kernels_only and not args.no_cfg5 and M_TOKENS == 4096
@@ -409,6 +410,10 @@ def run_ours(args) -> None:
         exchange = ("fused: the GEMM epilogue TMA-stores its output columns into every rank's full-width result over NVLink; activations present "
                     "on every rank; linears on %d streams, scattering GEMM grids leave %d SMs free; one rank barrier per step; results rotate "
                     "through %d buffers, so a step's exchange drains while the next step computes" % (len(lanes), lanes.sm_margin, SLOTS))
+        use_multicast = args.exchange == "multicast" and arena.multicast_base != 0
+        if use_multicast:
+            exchange = exchange.replace("fused: the GEMM epilogue TMA-stores its output columns into every rank's full-width result over NVLink",
+                                        "multicast: forwarding CTAs of the GEMM's grid send each finished tile once, with multimem stores that the NVLink switch replicates into every rank's result")
         if args.exchange == "nccl":
             nccl_layers = [ColumnParallelInt8Linear(w) for w in ws]
             gathered = [torch.empty((world, M_TOKENS, n // world), dtype=torch.half, device=dev) for _, n, _ in SHAPES]
@@ -436,7 +441,7 @@ def run_ours(args) -> None:
             if not only_local:
                 stream.wait_stream(comm_stream)
             return out
-        return lanes.run_step([(lambda slot, layer=layer, x=x: layer.launch(x, slot, only_local)) for layer, x in zip(layers, xs)],
+        return lanes.run_step([(lambda slot, layer=layer, x=x: layer.launch(x, slot, only_local, multicast=use_multicast)) for layer, x in zip(layers, xs)],
                               barrier=not only_local)
 
     for _ in range(warmup):
@@ -813,42 +818,57 @@ def measure_reference_cuda(run: Run, xs, ws, ct, our_ms_per_step: float, our_gem
                     "same tensors, same process; the GEMM-only figures time the cublasLt call alone (host descriptor churn included, as in the reference)"}
 
 
-def measure_gemv(run: Run, gen, ck) -> dict:
+def measure_gemv(run: Run, gen, ck, batches=(1, 4, 16)) -> dict:
     """Decode GEMV HBM GB/s (weight 10240 x 4096 and its transpose; batch 1, 4, 16 with per-batch matrices), inside a
-    CUDA graph over rotating weights larger than L2."""
+    CUDA graph over rotating weights larger than L2; and, for one matrix, what merely reading it costs (read_floor)."""
     torch, dev, stream, peaks = run.torch, run.dev, run.stream, run.peaks
+    from cpm_kernels_b200.library import cpmk
     gemv = {}
     gs = torch.cuda.Stream()                         # capture stream; warmed up first so that the library's
     s = gs.cuda_stream                               # per-stream workspace exists before capture begins
-    for batch in (1, 4, 16):
+
+    def graph_time(fn, nbuf, launches):
+        """Seconds per launch of fn(j) (j = buffer index), `launches` launches replayed from one CUDA graph."""
+        gs.wait_stream(stream)
+        with torch.cuda.stream(gs):
+            for j in range(nbuf):
+                fn(j)
+        gs.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=gs):
+            for j in range(launches):
+                fn(j % nbuf)
+        graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1e-3 / launches
+
+    for batch in batches:
         nbuf = max(1, 4 // batch)                    # at least 4 x 84 MB of weights rotate: larger than L2
         mats = [(torch.randn((batch, 10240, 4096), generator=gen, device=dev) * 0.02).half() for _ in range(nbuf)]
         vec_in = torch.randn((batch, 4096), generator=gen, device=dev).half()
         y_rows = torch.empty((batch, 10240), dtype=torch.half, device=dev)
+        launches = nbuf * max(2, 20 // (nbuf * batch))
+        bytes_alg = batch * (2 * 10240 * 4096 + 2 * (10240 + 4096))
         # the transposed weight [4096, 10240] = (dim_in, dim_out): the same buffers, read with the other shape
         for name, fn in (("gemv_fp16", lambda j: ck.gemv_fp16(batch, 10240, 4096, mats[j].data_ptr(), vec_in.data_ptr(), y_rows.data_ptr(), s)),
                          ("gemv_fp16_transpose", lambda j: ck.gemv_fp16_transpose(batch, 10240, 4096, mats[j].data_ptr(), vec_in.data_ptr(), y_rows.data_ptr(), s))):
-            gs.wait_stream(stream)
-            with torch.cuda.stream(gs):
-                for j in range(nbuf):
-                    fn(j)
-            gs.synchronize()
-            reps = max(2, 20 // (nbuf * batch))
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=gs):
-                for j in range(nbuf * reps):
-                    fn(j % nbuf)
-            graph.replay()
-            torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            graph.replay()
-            b.record()
-            torch.cuda.synchronize()
-            sec = a.elapsed_time(b) * 1e-3 / (nbuf * reps)
-            bytes_alg = batch * (2 * 10240 * 4096 + 2 * (10240 + 4096))
+            sec = graph_time(fn, nbuf, launches)
             gemv["%s_batch%d" % (name, batch)] = {"GBps": bytes_alg / sec / 1e9, "us": sec * 1e6,
                                                  "frac_of_hbm_peak": bytes_alg / sec / 1e9 / peaks["hbm_gbs"]}
+        if batch == 1:
+            # the same 84 MB matrices merely read, by a plain grid-stride kernel and by the row GEMV's own copy pipeline
+            floor = {}
+            for mode, name in ((0, "plain_read"), (1, "row_gemv_pipeline_without_arithmetic")):
+                sec = graph_time(lambda j: cpmk.call("cpmk_probe_read", mode, 10240, 4096, mats[j].data_ptr(), y_rows.data_ptr(), s), nbuf, launches)
+                floor[name] = {"us": sec * 1e6, "GBps": 2 * 10240 * 4096 / sec / 1e9}
+            gemv["read_floor_batch1"] = floor
+            for name in ("gemv_fp16_batch1", "gemv_fp16_transpose_batch1"):
+                gemv[name]["vs_plain_read"] = floor["plain_read"]["us"] / gemv[name]["us"]
         del mats
     return gemv
 
@@ -1064,6 +1084,14 @@ def run_case(args):
     dev = torch.device("cuda", 0)
     cpmk.check_device()
     gen = torch.Generator(device=dev).manual_seed(0)
+    if args.case == "gemv":
+        import cpm_kernels_b200.kernels as ck
+        class _R:                                        # the few members measure_gemv uses
+            pass
+        r = _R()
+        r.torch, r.dev, r.stream, r.peaks = torch, dev, torch.cuda.current_stream(), measured_peaks()
+        print(json.dumps({"case": "gemv", "result": measure_gemv(r, gen, ck, batches=(1,))}), flush=True)
+        return
     xs = ws = None
     if args.case == "fp16":
         xs = [torch.randn((1, M_TOKENS, k), generator=gen, device=dev).half() for _, n, k in SHAPES]
@@ -1079,14 +1107,15 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--exchange", default="fused", choices=["fused", "fused1", "nccl"],
-                    help="N > 1: how the output slices reach every rank (fused = stored by the GEMM epilogue, linears on several streams; fused1 = the same on one stream; nccl = all-gather)")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "fused1", "multicast", "nccl"],
+                    help="N > 1: how the output slices reach every rank (fused = stored by the GEMM's own CTAs, linears on several streams; fused1 = the same on one "
+                         "stream; multicast = forwarded once per GPU through the NVLink switch's multicast mapping; nccl = all-gather)")
     ap.add_argument("--no-cfg5", action="store_true", help="skip the 48-layer stack at M = 16384 (shorter run)")
     ap.add_argument("--tokens", type=int, default=M_TOKENS,
                     help="tokens per step; anything but the default is a reduced case for profiler captures, not a bench value")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the e2e, GEMV and CPU-baseline legs (profiler captures of the step's kernels)")
-    ap.add_argument("--case", default="linears", choices=["linears", "attention", "fp16", "passes"],
+    ap.add_argument("--case", default="linears", choices=["linears", "attention", "fp16", "passes", "gemv"],
                     help="anything but 'linears' runs only that secondary configuration (profiler captures; no benchmark line)")
     args = ap.parse_args()
     M_TOKENS = args.tokens

@@ -1,5 +1,6 @@
 // Host-side plumbing of the cpmk_b200 C-ABI library: thread-local error text, per-device
 // capability check and the (device, stream)-keyed workspace.
+#include <cuda.h>
 #include <stdarg.h>
 #include <string.h>
 
@@ -47,6 +48,31 @@ int32_t current_device_info(DeviceInfo *info) {
         return CPMK_EARCH;
     }
     return CPMK_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+bool encode_tiled_3d(void *map_out, int esz, const void *ptr, const uint64_t dims[3], const uint64_t strides[2], const uint32_t box[3], bool swizzle128) {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        (void)cudaGetLastError();
+    });
+    if (!fn) return false;
+    const cuuint64_t d[3] = {dims[0], dims[1], dims[2]};
+    const cuuint64_t st[2] = {strides[0], strides[1]};
+    const cuuint32_t bx[3] = {box[0], box[1], box[2]};
+    const cuuint32_t es[3] = {1u, 1u, 1u};
+    const CUtensorMapDataType dt = esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : (esz == 4 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8);
+    return fn(static_cast<CUtensorMap *>(map_out), dt, 3, const_cast<void *>(ptr), d, st, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // At most this many (stream) workspaces per device; a slot is given back with cpmk_release_workspace.

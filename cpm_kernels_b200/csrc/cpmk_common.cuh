@@ -75,6 +75,11 @@ int32_t get_workspace(cudaStream_t stream, Workspace *ws);
 // Element-wise GELU over `count` fp16 values (cpmk_gelu.cu); in == out is allowed.
 int32_t launch_gelu(int64_t count, const void *in, void *out, cudaStream_t stream);
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time dependency on libcuda): a 3-d map
+// over `ptr` with extents dims[0] (contiguous) .. dims[2], byte strides of dimensions 1 and 2, a box, element type
+// fp16 (esz 2) / 8-bit (esz 1) / int32 (esz 4), 128-byte swizzle or none.  Returns false when the driver refuses.
+bool encode_tiled_3d(void *map_out, int esz, const void *ptr, const uint64_t dims[3], const uint64_t strides[2], const uint32_t box[3], bool swizzle128);
+
 inline cudaStream_t as_stream(cpmk_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

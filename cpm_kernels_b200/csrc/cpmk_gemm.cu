@@ -53,6 +53,7 @@ constexpr uint32_t kErrMmaWaitFull = 0x102;
 constexpr uint32_t kErrMmaWaitTmem = 0x103;
 constexpr uint32_t kErrEpilogueWait = 0x104;
 constexpr uint32_t kErrForwardWaitTile = 0x105;
+constexpr uint32_t kErrForwardWaitLoad = 0x106;
 
 struct GemmParams {
     int32_t R, C, K;              // out is (batch, R, C); reduction length K
@@ -65,11 +66,13 @@ struct GemmParams {
     const __half *scale_c;        // (bcast_c ? 1 : batch, C)
     int32_t bcast_r, bcast_c;
     int32_t tma_store;            // the two-CTA kernel writes its output with TMA stores (needs 16-byte row pitch)
-    int32_t n_dst;                // number of destinations each output tile is stored to (1, or one per GPU when scattering)
+    int32_t n_dst;                // number of destinations of the output (1, or one per GPU when scattering)
+    int32_t n_store;              // destinations the computing CTAs store to themselves: n_dst, or 1 when forwarding CTAs serve the others
     int32_t send_pairs;           // > 0: the last `send_pairs` CTA pairs of the grid forward finished tiles from destination 0 to the others
     uint32_t *flags;              // send_pairs > 0: one counter per (pair tile, CTA of the pair), zero at launch; 8 = all epilogue warps have stored
     __half *fwd_dst[8];           // send_pairs > 0: element (0, 0, 0) of every destination (0: this GPU's own, where the computing CTAs store)
     int64_t out_ld;               // row pitch of the destinations in elements
+    int32_t multicast;            // send_pairs > 0: destination 1 is a multicast address (one multimem store reaches every GPU)
     uint32_t *status;
     // tile index -> (batch, column block, row block) without integer division: multipliers and shifts for
     // tiles_r * tiles_c and for tiles_r (set_tile_divisors)
@@ -532,7 +535,7 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const O
         if (lane == 0) {
             // one store per piece and destination (peers' buffers are reached over NVLink)
             for (int i = 0; i < staged; ++i)
-                for (int d = 0; d < prm.n_dst; ++d)
+                for (int d = 0; d < prm.n_store; ++d)
                     tma_store_3d(&tmap_o->m[d], staging + (buf + (uint32_t)i) * kOutStageBytes, i == 0 ? staged_col0 : staged_col1,
                                  row_base + quarter * 32, b);
             bulk_commit();
@@ -609,77 +612,154 @@ __device__ __forceinline__ void epilogue_rows_tma(const GemmParams &prm, const O
 // Forwarding CTAs.  When the output goes to several GPUs, stores that cross NVLink are slow to drain: issued by the
 // CTAs that compute, they sit in the same per-SM TMA queue as the operand loads and in the same staging tiles the
 // epilogue wants back, and the main loop ends up waiting for the link (measured: GEMM time = compute + transfer).
-// So the computing CTAs store only to destination 0 -- this GPU's own buffer -- and signal each finished 128 x 256
+// So the computing CTAs can store only to destination 0 -- this GPU's own buffer -- and signal each finished 128 x 256
 // CTA tile through a counter; the last `send_pairs` CTA pairs of the same grid do nothing but wait for those counters
 // and copy finished tiles from destination 0 (out of L2, where they were just written) to every other destination.
-// The copy uses ordinary 16-byte loads and stores, a whole 512-byte tile row per warp instruction: TMA stores to a
-// peer were measured to hold up the TMA loads queued behind them on the same SM, plain stores do not.  A couple of
-// dozen SMs saturate the link; the others compute at full speed, and transfer and arithmetic overlap tile by tile
-// inside one kernel.  Only stores cross the link (no load touches a peer's memory, nothing is multicast).  The wait
-// for a tile is bounded.
+// Each forwarding warp keeps a ring of 4 KiB pieces (32 rows x 128 bytes) filled by TMA loads, which run ahead
+// unhindered because nothing else shares that SM's TMA queue, and empties it with ordinary 16-byte stores by all of its
+// lanes (a store that waits for the link then holds up nothing but the next store).  Transfer and arithmetic overlap
+// tile by tile inside one kernel.  Only stores cross the link (no load touches a peer's memory, nothing is multicast
+// by TMA).  The waits for a tile and for a load are bounded.
 // ------------------------------------------------------------------------------------------------
-constexpr int kFwdRows = kBM / kEpiWarps2;              // rows of a CTA tile per forwarding warp: 16
+constexpr int kFwdSlots = 6;                            // 4 KiB pieces per forwarding warp (8 warps: 192 KiB of the CTA's shared memory)
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
     uint32_t v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+// one 16-byte store that the NVLink switch replicates into every GPU's copy of a multicast-mapped buffer
+__device__ __forceinline__ void multimem_st_v4(void *mc_addr, const uint4 &v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 
-__device__ __forceinline__ void forward_tiles(const GemmParams &prm, int send_pair, uint32_t rank) {
+__device__ __forceinline__ void forward_tiles(const OutMaps &tmap_o, const GemmParams &prm, int send_pair, uint32_t rank) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t ring_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars_base = ring_base + kEpiWarps2 * kFwdSlots * kOutStageBytes;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ uint32_t fwd_abort;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kEpiWarps2 * kFwdSlots; ++i) mbar_init(bars_base + 8 * i, 1);
+        fwd_abort = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
     if (warp < 2) return;                                // as many forwarding warps as there are epilogue warps
-    const int w = warp - 2;
+    const int w = warp - 2, quarter = w & 3, half = w >> 2;
+    const uint32_t my_ring = ring_base + (uint32_t)w * kFwdSlots * kOutStageBytes;
+    const uint32_t my_bars = bars_base + 8u * (uint32_t)(w * kFwdSlots);
+    volatile uint32_t *abort_flag = &fwd_abort;
     const int64_t ld = prm.out_ld;
-    for (int tile = send_pair; tile < prm.total_tiles; tile += prm.send_pairs) {
-        int b, c_blk, r_blk;
-        tile_coords(prm, tile, b, c_blk, r_blk);
-        const int row0 = r_blk * (2 * kBM) + (int)rank * kBM + w * kFwdRows;
-        const int col = c_blk * kBN + lane * 8;           // this lane's eight columns (16 bytes) of every row
-        if (row0 >= prm.R) continue;                      // uniform across the warp
-        // lane 0 waits until all eight epilogue warps of the computing CTA have stored their part of the tile
+
+    // pieces are numbered in the order they are forwarded; piece q lives in slot q % kFwdSlots (all lanes keep the same counts)
+    int issued = 0, finished = 0;
+    int piece_col[kFwdSlots], piece_row[kFwdSlots], piece_b[kFwdSlots];
+    bool alive = true;
+    auto finish_one = [&]() {
+        const int slot = finished % kFwdSlots;
+        const uint32_t parity = (uint32_t)(finished / kFwdSlots) & 1u;
         int ok = 1;
-        if (lane == 0) {
-            const uint32_t *flag = prm.flags + ((size_t)tile * 2 + rank);
-            uint64_t t0 = 0;
-            for (uint32_t spin = 0; ld_acquire_gpu(flag) < (uint32_t)kEpiWarps2; ++spin) {
-                __nanosleep(64);
-                if ((spin & 0x3ffu) == 0x3ffu) {
-                    const uint64_t now = global_timer_ns();
-                    if (t0 == 0) t0 = now;
-                    else if (now - t0 > kWaitLimitNs) {
-                        atomicCAS(prm.status, 0u, kErrForwardWaitTile);
-                        ok = 0;
-                        break;
-                    }
-                }
-            }
+        if (lane == 0) ok = mbar_wait(my_bars + 8 * slot, parity, abort_flag, prm.status, kErrForwardWaitLoad) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { alive = false; return; }
+        (void)mbar_try_wait(my_bars + 8 * slot, parity);  // every lane observes the completed phase before it reads the piece
+        // lane l: 16-byte chunk l & 7 of rows (l >> 3), (l >> 3) + 4, ...: four 128-byte row segments per instruction;
+        // the piece lies in shared memory as TMA wrote it (chunk c of row r at chunk c ^ (r & 7))
+        const int chunk = lane & 7;
+        const int col = piece_col[slot] + chunk * 8;
+        const uint32_t src = my_ring + (uint32_t)slot * kOutStageBytes;
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int r = j * 4 + (lane >> 3);
+            v[j] = ld_shared_v4(src + (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4));
         }
-        ok = __shfl_sync(0xffffffffu, ok, 0);             // (also orders the other lanes' loads after lane 0's acquire)
-        if (!ok) return;
-        const bool col_ok = col < prm.C;                  // C % 8 == 0: the eight columns are in or out together
-        const int64_t offset = ((int64_t)b * prm.R + row0) * ld + col;
-        const __half *src = prm.fwd_dst[0] + offset;
-#pragma unroll
-        for (int part = 0; part < kFwdRows / 8; ++part) {
-            uint4 v[8];
-            bool in[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int r = part * 8 + i;
-                in[i] = col_ok && row0 + r < prm.R;
-                v[i] = in[i] ? __ldcg(reinterpret_cast<const uint4 *>(src + r * ld)) : make_uint4(0u, 0u, 0u, 0u);
-            }
+        if (col < prm.C) {
+            const int64_t offset = ((int64_t)piece_b[slot] * prm.R + piece_row[slot] + (lane >> 3)) * ld + col;
 #pragma unroll
             for (int d = 1; d < kMaxDst; ++d) {
                 if (d < prm.n_dst) {
                     __half *dst = prm.fwd_dst[d] + offset;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        if (in[i]) *reinterpret_cast<uint4 *>(dst + (part * 8 + i) * ld) = v[i];
+                    for (int j = 0; j < 8; ++j) {
+                        if (piece_row[slot] + j * 4 + (lane >> 3) < prm.R) {
+                            if (prm.multicast) multimem_st_v4(dst + (int64_t)(j * 4) * ld, v[j]);
+                            else *reinterpret_cast<uint4 *>(dst + (int64_t)(j * 4) * ld) = v[j];
+                        }
+                    }
                 }
             }
         }
+        __syncwarp();                                    // every lane has read the slot before it is loaded again
+        ++finished;
+    };
+    for (int tile = send_pair; alive && tile < prm.total_tiles; tile += prm.send_pairs) {
+        int b, c_blk, r_blk;
+        tile_coords(prm, tile, b, c_blk, r_blk);
+        const int row0 = r_blk * (2 * kBM) + (int)rank * kBM + quarter * 32;
+        const int col0 = c_blk * kBN + half * (kBN / 2);
+        if (row0 >= prm.R || col0 >= prm.C) continue;     // nothing of this warp's block is inside the output (uniform)
+        {
+            const uint32_t *flag = prm.flags + ((size_t)tile * 2 + rank);
+            int ready = 0;
+            if (lane == 0) ready = ld_acquire_gpu(flag) >= (uint32_t)kEpiWarps2 ? 1 : 0;
+            ready = __shfl_sync(0xffffffffu, ready, 0);
+            if (!ready) {
+                // not finished yet: what is loaded ahead belongs to tiles that are complete, forward it before waiting
+                while (alive && finished < issued) finish_one();
+                if (!alive) break;
+                int ok = 1;
+                if (lane == 0) {
+                    uint64_t t0 = 0;
+                    for (uint32_t spin = 0; ld_acquire_gpu(flag) < (uint32_t)kEpiWarps2; ++spin) {
+                        __nanosleep(64);
+                        if ((spin & 0x3ffu) == 0x3ffu) {
+                            const uint64_t now = global_timer_ns();
+                            if (t0 == 0) t0 = now;
+                            else if (now - t0 > kWaitLimitNs) {
+                                atomicCAS(prm.status, 0u, kErrForwardWaitTile);
+                                ok = 0;
+                                break;
+                            }
+                        }
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { alive = false; break; }
+            }
+        }
+#pragma unroll 1
+        for (int piece = 0; piece < 2 && alive; ++piece) {
+            const int col = col0 + piece * 64;
+            if (col >= prm.C) break;
+            if (issued - finished >= kFwdSlots) finish_one();      // the slot's previous piece has been forwarded
+            if (!alive) break;
+            const int slot = issued % kFwdSlots;
+            piece_col[slot] = col;
+            piece_row[slot] = row0;
+            piece_b[slot] = b;
+            if (lane == 0) {
+                // the slot was last read through the generic proxy: order those reads against the load that overwrites it
+                // (a fence over shared memory only: one over all state spaces would wait for the stores to the peers)
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_expect_tx(my_bars + 8 * slot, kOutStageBytes);
+                tma_load_3d(my_ring + (uint32_t)slot * kOutStageBytes, &tmap_o.m[0], col, row0, b, my_bars + 8 * slot);
+            }
+            ++issued;
+        }
+    }
+    while (alive && finished < issued) finish_one();
+    if (prm.multicast) __threadfence_system();
+    if (!alive) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);  // loads in flight land before the ring is released
     }
 }
 
@@ -712,7 +792,7 @@ __device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CU
     // the last send_pairs pairs of the grid forward finished tiles to the other destinations instead of computing
     const int pair = blockIdx.x >> 1, num_pairs = (gridDim.x >> 1) - prm.send_pairs;
     if (prm.send_pairs > 0 && pair >= num_pairs) {
-        forward_tiles(prm, pair - num_pairs, rank);
+        forward_tiles(tmap_o, prm, pair - num_pairs, rank);
         return;
     }
 
@@ -1167,11 +1247,14 @@ int32_t prepare_tc_kernels(int device) {
 template <bool DEQUANT>
 int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int aT, int bT, const void *A, const void *B,
                     const void *scale_x, const void *scale_y, int bx, int by, void *out, cudaStream_t stream, int n_dst = 1,
-                    void *const *dsts = nullptr, int64_t dst_ld = 0) {
+                    void *const *dsts = nullptr, int64_t dst_ld = 0, bool multicast = false) {
     // n_dst > 1 or dst_ld != m: the output tiles are scattered to several (possibly pitched) destinations; this is
     // implemented by the TMA-store epilogue of the two-CTA kernel only
+    // multicast: dsts[1] is a multicast address (every GPU's copy of the buffer at once); it can only be written by the
+    // forwarding CTAs' multimem stores
     const bool scatter = dsts != nullptr;
     if (!scatter) dst_ld = m;
+    CPMK_REQUIRE(!multicast || (scatter && n_dst == 2), "a multicast destination needs exactly two destinations: the local buffer and the multicast address");
     DeviceInfo info;
     int32_t rc = current_device_info(&info);
     if (rc) return rc;
@@ -1221,6 +1304,7 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
         prm.send_pairs = 0;
         prm.flags = nullptr;
         prm.out_ld = 0;
+        prm.multicast = 0;
         for (int d = 0; d < 8; ++d) prm.fwd_dst[d] = nullptr;
         prm.status = ws.status();
         rc = prepare_tc_kernels(info.device);
@@ -1257,8 +1341,13 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
                         const char *fe = getenv("CPMK_GEMM_FORWARD_SMS");
                         sms = fe ? atoi(fe) : 0;
                     }
-                    const int want = (sms + 1) / 2;
+                    int want = (sms + 1) / 2;
+                    if (multicast && want == 0) want = 8;               // a multicast address is only reachable through the forwarding CTAs
                     if (want > 0 && max_pairs - want >= 8 && (size_t)total * 2 * sizeof(uint32_t) <= kFlagBytes) send_pairs = want;
+                    if (multicast && send_pairs == 0) {
+                        set_error("the multicast form needs the forwarding CTAs (device too small or too many tiles: %lld)", (long long)total);
+                        return CPMK_EINVAL;
+                    }
                 }
                 const int compute_cap = max_pairs - send_pairs;
                 const int pairs = (int)(total < compute_cap ? total : compute_cap);
@@ -1268,14 +1357,17 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
                 if (send_pairs > 0) {
                     for (int d = 0; d < kMaxDst; ++d) prm.fwd_dst[d] = d < n_dst ? static_cast<__half *>(dsts[d]) : nullptr;
                     prm.out_ld = dst_ld;
+                    prm.multicast = multicast ? 1 : 0;
                     prm.flags = reinterpret_cast<uint32_t *>(ws.base + Workspace::kBytes - kFlagBytes);
                     CPMK_CUDA_TRY(cudaMemsetAsync(prm.flags, 0, (size_t)total * 2 * sizeof(uint32_t), stream));
                 }
                 OutMaps tmap_o;
                 memset(&tmap_o, 0, sizeof(tmap_o));
                 prm.n_dst = scatter ? n_dst : 1;
+                prm.n_store = send_pairs > 0 ? 1 : prm.n_dst;
                 prm.tma_store = (dst_ld * (DEQUANT ? 2 : 4)) % 16 == 0 && (scatter || !getenv("CPMK_GEMM_NO_TMA_STORE"));
-                for (int d = 0; prm.tma_store && d < prm.n_dst; ++d)
+                // (with forwarding CTAs only destination 0 is reached through a tensor map)
+                for (int d = 0; prm.tma_store && d < (send_pairs > 0 ? 1 : prm.n_dst); ++d)
                     prm.tma_store = encode_output(&tmap_o.m[d], scatter ? dsts[d] : out, n, m, dst_ld, batch, DEQUANT);
                 if (scatter && !prm.tma_store) {
                     set_error("scattered output needs a row pitch that is a multiple of 16 bytes and 16-byte aligned destinations");
@@ -1424,6 +1516,7 @@ int32_t launch_gemm_f16(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t
             prm.out = out;
             prm.tma_store = 1;
             prm.n_dst = 1;
+            prm.n_store = 1;
             prm.status = ws.status();
             prm.tiles_r = (int32_t)tiles_r; prm.tiles_c = (int32_t)tiles_c; prm.total_tiles = (int32_t)total;
             set_tile_divisors(&prm);
@@ -1477,6 +1570,14 @@ int32_t cpmk_gemm_int8_dequant_scatter(int32_t m, int32_t k, int32_t n, int32_t 
     }
     return launch_gemm<true>(m, k, n, batchA, batchB, aT != 0, bT != 0, A, B, scale_x, scale_y, broad_cast_x != 0, broad_cast_y != 0, nullptr,
                              as_stream(stream), n_dst, dst, dst_row_pitch);
+}
+
+int32_t cpmk_gemm_int8_dequant_multicast(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT, const void *A,
+                                         const void *B, const void *scale_x, const void *scale_y, int32_t broad_cast_x, int32_t broad_cast_y,
+                                         void *dst_local, void *dst_multicast, int64_t dst_row_pitch, cpmk_stream_t stream) {
+    void *dst[2] = {dst_local, dst_multicast};
+    return launch_gemm<true>(m, k, n, batchA, batchB, aT != 0, bT != 0, A, B, scale_x, scale_y, broad_cast_x != 0, broad_cast_y != 0, nullptr,
+                             as_stream(stream), 2, dst, dst_row_pitch, true);
 }
 
 int32_t cpmk_gemm_int8_dequant_gelu(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT, const void *A,

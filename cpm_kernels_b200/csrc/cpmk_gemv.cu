@@ -97,12 +97,15 @@ __global__ void __launch_bounds__(kBlock) gemv_rows_kernel(int32_t batch, int32_
 constexpr int kStreamRows = 8;                      // rows per stage = consumer warps
 constexpr int kStreamThreads = (kStreamRows + 1) * 32;
 constexpr int kStreamRingBytes = 200 * 1024;
+constexpr int kStreamVecBytes = 13 * 1024;           // the vector behind the ring (rows of up to 12.5 KiB)
 constexpr uint32_t kErrGemvProducer = 0x201;
 constexpr uint32_t kErrGemvConsumer = 0x202;
 
 // Rows longer than one stage slot are streamed in chunks of `chunk` halves (<= 4096): a stage then holds the
 // same chunk of eight consecutive rows, and each warp carries its row's sum across the chunks.
-template <bool SHARED>
+// PROBE: the same copy pipeline with the arithmetic left out (no vector loads, no sums): how long the matrix takes to
+// arrive through this launch shape; the consumers only fold one word per 16 bytes so that the reads are not elided.
+template <bool SHARED, bool PROBE = false>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int64_t rows_base, int64_t rows_extra, int32_t dim_out, int32_t dim_in, int32_t chunk,
                                                                              int32_t stages, const __half *__restrict__ mat,
                                                                              const __half *__restrict__ vec, __half *__restrict__ out,
@@ -110,6 +113,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int
     extern __shared__ __align__(128) uint8_t ring[];
     __shared__ __align__(8) uint64_t bars[32];       // full[stages], empty[stages]
     __shared__ uint32_t abort_word;
+    // the vector of the batch entry the consumers are working on, copied once per block (per batch entry) behind the
+    // ring: read out of shared memory it costs the consumers a short wait instead of a global load per 16 bytes of matrix
+    __half *xs = reinterpret_cast<__half *>(ring + (size_t)stages * chunk * 2 * kStreamRows);
     const uint32_t slot_bytes = (uint32_t)chunk * 2u;             // one row's chunk
     const uint32_t stage_bytes = slot_bytes * kStreamRows;
     const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + 16);
@@ -118,51 +124,71 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int chunks = (dim_in + chunk - 1) / chunk;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < stages; ++s) {
-            mbar_init(full_bar + 8 * s, 1);
-            mbar_init(empty_bar + 8 * s, kStreamRows);
-        }
-        abort_word = 0u;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    __syncthreads();
-
     // this block's rows [r0, r1): total_rows = rows_base * gridDim.x + rows_extra, the first rows_extra blocks take one more
     // (host-computed: a 64-bit division here would sit in front of the first copy)
     const int64_t bx = blockIdx.x;
     const int64_t r0 = bx * rows_base + (bx < rows_extra ? bx : rows_extra), r1 = r0 + rows_base + (bx < rows_extra ? 1 : 0);
     const int groups = (int)((r1 - r0 + kStreamRows - 1) / kStreamRows);
+    bool x_in_smem = false;
+
+    // Producer warp.  A single thread issuing eight copies one after another takes over a microsecond per stage
+    // (measured), which delays the first stage and barely keeps up afterwards: whole rows of a group are contiguous in
+    // memory and in the ring, so they travel as ONE copy; chunks of long rows are issued by one lane each.
+    // copy number t = g * chunks + c goes to stage t % stages
+    auto issue_copy = [&](int g, int c, uint32_t stage) {
+        const int64_t row = r0 + (int64_t)g * kStreamRows;
+        const int n = (int)((r1 - row) < kStreamRows ? (r1 - row) : kStreamRows);
+        const int c0 = c * chunk;
+        const uint32_t bytes = (uint32_t)((dim_in - c0) < chunk ? (dim_in - c0) : chunk) * 2u;
+        if (lane == 0) mbar_expect_tx(full_bar + 8 * stage, (uint32_t)n * bytes);
+        if (chunks == 1) {
+            if (lane == 0) bulk_load_1d(ring_base + stage * stage_bytes, mat + row * (int64_t)dim_in, (uint32_t)n * bytes, full_bar + 8 * stage);
+        } else {
+            __syncwarp();
+            if (lane < n)
+                bulk_load_1d(ring_base + stage * stage_bytes + (uint32_t)lane * slot_bytes, mat + (row + lane) * (int64_t)dim_in + c0, bytes,
+                             full_bar + 8 * stage);
+        }
+    };
+    const int total_copies = groups * chunks;
+    const int prologue = total_copies < stages ? total_copies : stages;
+    if (warp == kStreamRows) {
+        // the producer initialises the barriers itself and fills the whole ring before the block's first barrier, so the
+        // first bytes are on their way while the other warps are still setting up
+        if (lane == 0) {
+            for (int s = 0; s < stages; ++s) {
+                mbar_init(full_bar + 8 * s, 1);
+                mbar_init(empty_bar + 8 * s, kStreamRows);
+            }
+            abort_word = 0u;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncwarp();
+        for (int t = 0; t < prologue; ++t) issue_copy(t / chunks, t % chunks, (uint32_t)t);
+    } else if (!PROBE && r1 > r0) {
+        // When all rows of the block belong to one batch entry (always, for a single matrix) its vector is copied into
+        // shared memory once; a block that straddles two entries reads the vectors from global memory as it goes.
+        const bool one_matrix = SHARED || rows_base * gridDim.x + rows_extra == dim_out;
+        const int64_t b_lo = one_matrix ? 0 : r0 / dim_out, b_hi = one_matrix ? 0 : (r1 - 1) / dim_out;
+        if (b_lo == b_hi) {
+            x_in_smem = true;
+            const uint4 *srcv = reinterpret_cast<const uint4 *>(vec + b_lo * dim_in);
+            for (int i = threadIdx.x; i < (dim_in >> 3); i += kStreamRows * 32) reinterpret_cast<uint4 *>(xs)[i] = __ldg(srcv + i);
+        }
+    }
+    __syncthreads();
 
     if (warp == kStreamRows) {
-        // Producer warp.  A single thread issuing eight copies one after another takes over a microsecond per stage
-        // (measured), which delays the first stage and barely keeps up afterwards: whole rows of a group are
-        // contiguous in memory and in the ring, so they travel as ONE copy; chunks of long rows are issued by one
-        // lane each.
-        uint32_t stage = 0, phase = 0;
+        uint32_t stage = prologue == stages ? 0u : (uint32_t)prologue, phase = prologue == stages ? 1u : 0u;
         bool alive = true;
-        for (int g = 0; alive && g < groups; ++g) {
-            const int64_t row = r0 + (int64_t)g * kStreamRows;
-            const int n = (int)((r1 - row) < kStreamRows ? (r1 - row) : kStreamRows);
-            for (int c = 0; c < chunks; ++c) {
-                int ok = 1;
-                if (lane == 0) ok = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrGemvProducer) ? 1 : 0;
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) { alive = false; break; }
-                const int c0 = c * chunk;
-                const uint32_t bytes = (uint32_t)((dim_in - c0) < chunk ? (dim_in - c0) : chunk) * 2u;
-                if (lane == 0) mbar_expect_tx(full_bar + 8 * stage, (uint32_t)n * bytes);
-                if (chunks == 1) {
-                    if (lane == 0) bulk_load_1d(ring_base + stage * stage_bytes, mat + row * (int64_t)dim_in, (uint32_t)n * bytes, full_bar + 8 * stage);
-                } else {
-                    __syncwarp();
-                    if (lane < n)
-                        bulk_load_1d(ring_base + stage * stage_bytes + (uint32_t)lane * slot_bytes, mat + (row + lane) * (int64_t)dim_in + c0, bytes,
-                                     full_bar + 8 * stage);
-                }
-                if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
-            }
+        for (int t = prologue; alive && t < total_copies; ++t) {
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrGemvProducer) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { alive = false; break; }
+            issue_copy(t / chunks, t % chunks, stage);
+            if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
         }
     } else {
         uint32_t stage = 0, phase = 0;
@@ -178,15 +204,25 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int
                     const int c0 = c * chunk;
                     const int nvec = ((dim_in - c0) < chunk ? (dim_in - c0) : chunk) >> 3;
                     const uint4 *w = reinterpret_cast<const uint4 *>(ring + (size_t)stage * stage_bytes + (size_t)warp * slot_bytes);
-                    const uint4 *x = reinterpret_cast<const uint4 *>(vec + (int64_t)b * dim_in + c0);
+                    const uint4 *x = x_in_smem ? reinterpret_cast<const uint4 *>(xs + c0) : reinterpret_cast<const uint4 *>(vec + (int64_t)b * dim_in + c0);
                     int i = lane;
-                    for (; i + 32 < nvec; i += 64) {
-                        const uint4 w0 = w[i], w1 = w[i + 32];
-                        const uint4 x0 = __ldg(x + i), x1 = __ldg(x + i + 32);
-                        acc0 = dot8(w0, x0, acc0);
-                        acc1 = dot8(w1, x1, acc1);
+                    if (PROBE) {
+                        uint32_t fold = 0u;
+                        for (; i < nvec; i += 32) {
+                            const uint4 w0 = w[i];
+                            fold ^= w0.x ^ w0.y ^ w0.z ^ w0.w;
+                        }
+                        acc0 += fold == 0x9e3779b9u ? 1.f : 0.f;
+                    } else {
+                        // (generic loads: x is in shared memory, or in global memory when the block's rows span two batch entries)
+                        for (; i + 32 < nvec; i += 64) {
+                            const uint4 w0 = w[i], w1 = w[i + 32];
+                            const uint4 x0 = x[i], x1 = x[i + 32];
+                            acc0 = dot8(w0, x0, acc0);
+                            acc1 = dot8(w1, x1, acc1);
+                        }
+                        if (i < nvec) acc0 = dot8(w[i], x[i], acc0);
                     }
-                    if (i < nvec) acc0 = dot8(w[i], __ldg(x + i), acc0);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty_bar + 8 * stage);
@@ -194,7 +230,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int
             }
             if (alive && row < r1) {
                 const float v = warp_sum(acc0 + acc1);
-                if (lane == 0) out[row] = __float2half_rn(v);
+                if (lane == 0 && (!PROBE || v != 0.f)) out[row] = __float2half_rn(v);     // (the probe writes nothing unless a fold hits the magic word)
             }
         }
     }
@@ -215,9 +251,10 @@ constexpr int kTsCols = 2048;
 constexpr int kTsStages = 3;
 constexpr int kTsStageBytes = kStreamRows * kTsCols * 2;       // 32 KiB
 constexpr int kTsRingBytes = kTsStages * kTsStageBytes;        // 96 KiB
+constexpr int kTsVecFloats = 2048;                             // rows of the vector a block may keep in shared memory (8 KiB)
 
 __global__ void __launch_bounds__(kStreamThreads, 2) gemv_transpose_stream_kernel(int32_t dim_out, int32_t dim_in, int32_t rows_per_split,
-                                                                                  int32_t splits, const __half *__restrict__ mat,
+                                                                                  int32_t splits, int32_t x_in_smem, const __half *__restrict__ mat,
                                                                                   const __half *__restrict__ vec, __half *__restrict__ out,
                                                                                   float *__restrict__ partial, uint32_t *__restrict__ tickets,
                                                                                   uint32_t *status) {
@@ -227,6 +264,7 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_transpose_stream_kerne
     __shared__ uint32_t is_last;
     const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + kTsStages);
     const uint32_t ring_base = smem_u32(ring);
+    float *xs = reinterpret_cast<float *>(ring + kTsRingBytes);    // x_in_smem: this block's rows of the vector, as fp32
     volatile uint32_t *abort_flag = &abort_word;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int strip = blockIdx.x, split = blockIdx.y, b = blockIdx.z, batch = gridDim.z;
@@ -239,14 +277,32 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_transpose_stream_kerne
     const __half *base = mat + (int64_t)b * dim_in * dim_out + c0;
     const __half *x = vec + (int64_t)b * dim_in;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kTsStages; ++s) {
-            mbar_init(full_bar + 8 * s, 1);
-            mbar_init(empty_bar + 8 * s, kStreamRows);
+    // one lane per row segment: a single thread issuing the eight copies of a stage takes over a microsecond
+    auto issue_group = [&](int g, uint32_t stage) {
+        const int row = i0 + g * kStreamRows;
+        const int n = (i1 - row) < kStreamRows ? (i1 - row) : kStreamRows;
+        if (lane == 0) mbar_expect_tx(full_bar + 8 * stage, (uint32_t)n * seg_bytes);
+        __syncwarp();
+        if (lane < n)
+            bulk_load_1d(ring_base + stage * kTsStageBytes + (uint32_t)lane * (kTsCols * 2), base + (int64_t)(row + lane) * dim_out, seg_bytes,
+                         full_bar + 8 * stage);
+    };
+    const int prologue = groups < kTsStages ? groups : kTsStages;
+    if (warp == kStreamRows) {
+        // the producer initialises the barriers itself and fills the ring before the block's first barrier
+        if (lane == 0) {
+            for (int s = 0; s < kTsStages; ++s) {
+                mbar_init(full_bar + 8 * s, 1);
+                mbar_init(empty_bar + 8 * s, kStreamRows);
+            }
+            abort_word = 0u;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         }
-        abort_word = 0u;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        for (int g = 0; g < prologue; ++g) issue_group(g, (uint32_t)g);
+    } else if (x_in_smem) {
+        for (int i = threadIdx.x; i < i1 - i0; i += kStreamRows * 32) xs[i] = __half2float(__ldg(x + i0 + i));
     }
     __syncthreads();
 
@@ -255,23 +311,14 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_transpose_stream_kerne
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 
     if (warp == kStreamRows) {
-        {
-            // one lane per row segment: a single thread issuing the eight copies of a stage takes over a microsecond
-            uint32_t stage = 0, phase = 0;
-            for (int g = 0; g < groups; ++g) {
-                int ok = 1;
-                if (lane == 0) ok = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrGemvProducer) ? 1 : 0;
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
-                const int row = i0 + g * kStreamRows;
-                const int n = (i1 - row) < kStreamRows ? (i1 - row) : kStreamRows;
-                if (lane == 0) mbar_expect_tx(full_bar + 8 * stage, (uint32_t)n * seg_bytes);
-                __syncwarp();
-                if (lane < n)
-                    bulk_load_1d(ring_base + stage * kTsStageBytes + (uint32_t)lane * (kTsCols * 2), base + (int64_t)(row + lane) * dim_out, seg_bytes,
-                                 full_bar + 8 * stage);
-                if (++stage == kTsStages) { stage = 0; phase ^= 1u; }
-            }
+        uint32_t stage = prologue == kTsStages ? 0u : (uint32_t)prologue, phase = prologue == kTsStages ? 1u : 0u;
+        for (int g = prologue; g < groups; ++g) {
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrGemvProducer) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            issue_group(g, stage);
+            if (++stage == kTsStages) { stage = 0; phase ^= 1u; }
         }
     } else {
         const int t = threadIdx.x;                       // 0..255: columns c0 + 8 t .. + 7
@@ -281,8 +328,13 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_transpose_stream_kerne
             const int row = i0 + g * kStreamRows;
             const int n = (i1 - row) < kStreamRows ? (i1 - row) : kStreamRows;
             float xv[kStreamRows];
+            if (x_in_smem) {
 #pragma unroll
-            for (int r = 0; r < kStreamRows; ++r) xv[r] = r < n ? __half2float(__ldg(x + row + r)) : 0.f;
+                for (int r = 0; r < kStreamRows; ++r) xv[r] = r < n ? xs[g * kStreamRows + r] : 0.f;
+            } else {
+#pragma unroll
+                for (int r = 0; r < kStreamRows; ++r) xv[r] = r < n ? __half2float(__ldg(x + row + r)) : 0.f;
+            }
             if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kErrGemvConsumer)) break;
             if (col_ok) {
                 const uint8_t *src = ring + (size_t)stage * kTsStageBytes + (size_t)t * 16;
@@ -555,6 +607,23 @@ __global__ void __launch_bounds__(kBlock) gemv_int8_kernel(int32_t dim_out, int3
     }
 }
 
+// Reads `nvec` 16-byte vectors once, grid-stride, four loads in flight per thread, and folds them: the time any kernel
+// needs to pull that many bytes out of HBM (the floor the GEMVs are compared with).
+__global__ void __launch_bounds__(kBlock) read_probe_kernel(int64_t nvec, const uint4 *__restrict__ src, uint32_t *__restrict__ sink) {
+    uint32_t fold = 0u;
+    const int64_t stride = (int64_t)gridDim.x * kBlock;
+    int64_t i = (int64_t)blockIdx.x * kBlock + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+        const uint4 a = __ldcs(src + i), b = __ldcs(src + i + stride), c = __ldcs(src + i + 2 * stride), d = __ldcs(src + i + 3 * stride);
+        fold ^= a.x ^ a.y ^ a.z ^ a.w ^ b.x ^ b.y ^ b.z ^ b.w ^ c.x ^ c.y ^ c.z ^ c.w ^ d.x ^ d.y ^ d.z ^ d.w;
+    }
+    for (; i < nvec; i += stride) {
+        const uint4 a = __ldcs(src + i);
+        fold ^= a.x ^ a.y ^ a.z ^ a.w;
+    }
+    if (fold == 0x9e3779b9u) atomicAdd(sink, 1u);           // practically never: keeps the loads alive
+}
+
 int32_t check_gemv(int32_t batch, int32_t dim_out, int32_t dim_in) {
     CPMK_REQUIRE(batch >= 0 && dim_out >= 0 && dim_in >= 0, "negative size: batch=%d dim_out=%d dim_in=%d", batch, dim_out, dim_in);
     return CPMK_OK;
@@ -585,13 +654,13 @@ int32_t launch_gemv_rows(int32_t batch, int32_t dim_out, int32_t dim_in, const v
     // (rows that do not fit a stage slot could be streamed in chunks -- the kernel supports it -- but measured slower
     // than the register-staged kernel on a 4096 x 10240 matrix, so such shapes stay with that kernel)
     if ((!SHARED || batch == 1) && row_bytes >= 2048 && row_bytes * kStreamRows * 2 <= kStreamRingBytes && total_rows >= (int64_t)info.sm_count * 16 &&
-        info.max_smem_optin >= kStreamRingBytes + 1024 && !getenv("CPMK_GEMV_NO_STREAM")) {
+        info.max_smem_optin >= kStreamRingBytes + kStreamVecBytes + 1024 && !getenv("CPMK_GEMV_NO_STREAM")) {
         static std::once_flag attr_once[64];
         static cudaError_t attr_err[64];
         const int dev = info.device & 63;
         std::call_once(attr_once[dev], [dev] {
-            cudaError_t e = cudaFuncSetAttribute(gemv_rows_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes);
-            if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_rows_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes);
+            cudaError_t e = cudaFuncSetAttribute(gemv_rows_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes + kStreamVecBytes);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_rows_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes + kStreamVecBytes);
             attr_err[dev] = e;
         });
         if (attr_err[dev] == cudaSuccess) {
@@ -606,7 +675,7 @@ int32_t launch_gemv_rows(int32_t batch, int32_t dim_out, int32_t dim_in, const v
             }
             int stages = (int)(kStreamRingBytes / ((int64_t)chunk * 2 * kStreamRows));
             if (stages > 16) stages = 16;
-            const size_t smem = (size_t)stages * chunk * 2 * kStreamRows;
+            const size_t smem = (size_t)stages * chunk * 2 * kStreamRows + (size_t)dim_in * 2;        // ring + the vector
             gemv_rows_stream_kernel<SHARED><<<info.sm_count, kStreamThreads, smem, stream>>>(total_rows / info.sm_count, total_rows % info.sm_count,
                                                                                             dim_out, dim_in, chunk, stages, w, x, y, ws.status());
             CPMK_LAUNCH_CHECK();
@@ -705,13 +774,13 @@ int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in,
         return CPMK_OK;
     }
     // matrices of a few MB and more: the streaming kernel, two blocks per SM
-    if ((int64_t)dim_in * dim_out >= (int64_t(1) << 21) && dim_in >= 256 && aligned16(out) && info.max_smem_optin >= kTsRingBytes + 1024 &&
+    if ((int64_t)dim_in * dim_out >= (int64_t(1) << 21) && dim_in >= 256 && aligned16(out) && info.max_smem_optin >= kTsRingBytes + kTsVecFloats * 4 + 1024 &&
         !getenv("CPMK_GEMV_NO_STREAM")) {
         static std::once_flag attr_once[64];
         static cudaError_t attr_err[64];
         const int dev = info.device & 63;
         std::call_once(attr_once[dev], [dev] {
-            attr_err[dev] = cudaFuncSetAttribute(gemv_transpose_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTsRingBytes);
+            attr_err[dev] = cudaFuncSetAttribute(gemv_transpose_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTsRingBytes + kTsVecFloats * 4);
         });
         const int ts_strips = (dim_out + kTsCols - 1) / kTsCols;
         if (attr_err[dev] == cudaSuccess && (size_t)batch * ts_strips * sizeof(uint32_t) <= Workspace::kTicketBytes) {
@@ -734,7 +803,9 @@ int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in,
                 const dim3 grid(ts_strips, nsp, batch);
                 float *partial = reinterpret_cast<float *>(ws.scratch());
                 const bool two_kernels = nsp > 24;
-                gemv_transpose_stream_kernel<<<grid, kStreamThreads, kTsRingBytes, st>>>(dim_out, dim_in, rps, nsp, w, x, y, partial,
+                // this block's rows of the vector go to shared memory (as fp32) when they fit behind the ring
+                const int x_in_smem = rps <= kTsVecFloats ? 1 : 0;
+                gemv_transpose_stream_kernel<<<grid, kStreamThreads, kTsRingBytes + (x_in_smem ? rps * 4 : 0), st>>>(dim_out, dim_in, rps, nsp, x_in_smem, w, x, y, partial,
                                                                                          two_kernels ? nullptr : ws.tickets(), ws.status());
                 CPMK_LAUNCH_CHECK();
                 if (two_kernels) {
@@ -807,6 +878,47 @@ int32_t cpmk_gemv_broadcast_mat_int8(int32_t batch, int32_t dim_out, int32_t dim
         else { gemv_int8_kernel<1><<<blocks, kBlock, 0, st>>>(dim_out, dim_in, b, sm, w, sv, x, y, vec16); b += 1; }
         CPMK_LAUNCH_CHECK();
     }
+    return CPMK_OK;
+}
+
+int32_t cpmk_probe_read(int32_t mode, int32_t rows, int32_t row_elems, const void *src, void *sink, cpmk_stream_t stream) {
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    CPMK_REQUIRE(rows > 0 && row_elems > 0 && row_elems % 8 == 0 && src && sink && aligned16(src), "bad arguments (rows=%d row_elems=%d)", rows, row_elems);
+    cudaStream_t st = as_stream(stream);
+    if (mode == 0) {
+        const int64_t nvec = (int64_t)rows * row_elems / 8;
+        read_probe_kernel<<<info.sm_count * 8, kBlock, 0, st>>>(nvec, static_cast<const uint4 *>(src), static_cast<uint32_t *>(sink));
+        CPMK_LAUNCH_CHECK();
+        return CPMK_OK;
+    }
+    CPMK_REQUIRE(mode == 1, "mode must be 0 (plain read) or 1 (the row GEMV's copy pipeline)");
+    const int64_t row_bytes = (int64_t)row_elems * 2;
+    CPMK_REQUIRE(row_bytes >= 2048 && row_bytes * kStreamRows * 2 <= kStreamRingBytes && rows >= info.sm_count * 16,
+                 "mode 1 takes the shapes the streaming row GEMV takes (rows of 2 KiB to 12.5 KiB, at least %d rows)", info.sm_count * 16);
+    static std::once_flag attr_once[64];
+    static cudaError_t attr_err[64];
+    const int dev = info.device & 63;
+    std::call_once(attr_once[dev], [dev] {
+        attr_err[dev] = cudaFuncSetAttribute(gemv_rows_stream_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes + kStreamVecBytes);
+    });
+    CPMK_CUDA_TRY(attr_err[dev]);
+    Workspace ws;
+    rc = get_workspace(st, &ws);
+    if (rc) return rc;
+    int chunk = row_elems;
+    if (chunk > 4096) {
+        const int parts = (row_elems + 4095) / 4096;
+        chunk = ((row_elems + parts - 1) / parts + 7) / 8 * 8;
+    }
+    int stages = (int)(kStreamRingBytes / ((int64_t)chunk * 2 * kStreamRows));
+    if (stages > 16) stages = 16;
+    const size_t smem = (size_t)stages * chunk * 2 * kStreamRows + (size_t)row_elems * 2;
+    gemv_rows_stream_kernel<false, true><<<info.sm_count, kStreamThreads, smem, st>>>(rows / info.sm_count, rows % info.sm_count, rows, row_elems, chunk, stages,
+                                                                                        static_cast<const __half *>(src), static_cast<const __half *>(src),
+                                                                                        static_cast<__half *>(sink), ws.status());
+    CPMK_LAUNCH_CHECK();
     return CPMK_OK;
 }
 

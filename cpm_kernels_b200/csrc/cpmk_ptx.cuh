@@ -64,4 +64,38 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
+// 3-d tiled TMA load global -> shared of this CTA; completion bytes on `bar` (a barrier of this CTA).  The innermost
+// coordinate times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_tile_3d(uint32_t dst, const void *tensor_map, int32_t c0, int32_t c1, int32_t c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+        : "memory");
+}
+
+// thread-block cluster: rank and size, split barrier, and the shared::cluster address of a shared::cta address in
+// the CTA of another rank (for ld.shared::cluster)
+__device__ __forceinline__ uint32_t cluster_rank_of_cta() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_num_ctas() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t dsmem_address(uint32_t addr, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ uint16_t ld_dsmem_u16(uint32_t cluster_addr) {
+    uint16_t v;
+    asm volatile("ld.shared::cluster.u16 %0, [%1];" : "=h"(v) : "r"(cluster_addr) : "memory");
+    return v;
+}
+
 }  // namespace cpmk

@@ -5,6 +5,7 @@
 //
 // Replaces cuda/gemm.cu:6-205 of the reference (one 1024-thread block per row, 2-byte loads, 1-byte
 // stores, an fp32 division per element, grid.y = n <= 65535).
+#include <cuda.h>
 #include <stdlib.h>
 
 #include <mutex>
@@ -524,6 +525,163 @@ __global__ void __launch_bounds__(kCsThreads, 2) quant_cols_stream_kernel(int32_
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Resident-strip form of the fused column quantisation: the operand is read from HBM once.
+// A thread-block cluster owns a strip of 64 columns; each of its CTAs loads its share of the strip's rows into shared
+// memory with tiled TMA copies (128-row boxes of 16 KiB, all requested up front; the column maxima of a box are taken
+// as soon as it lands), the CTAs exchange their 64 column maxima through distributed shared memory, and every CTA
+// rounds its rows out of shared memory.  3 bytes per element reach HBM instead of 5, in one launch, with no scratch and
+// no tickets.  Up to 768 rows (96 KiB) per CTA, two or three CTAs per SM in different phases of their work, clusters of
+// 1 to 8 CTAs: operands of up to 6144 rows (taller ones stay with the two-pass kernels, which measured faster there).
+// ------------------------------------------------------------------------------------------------
+constexpr int kRsCols = 64;
+constexpr int kRsChunkRows = 128;
+constexpr int kRsChunkBytes = kRsCols * kRsChunkRows * 2;      // 16 KiB
+constexpr int kRsMaxChunks = 6;
+constexpr int kRsMaxCluster = 16;
+constexpr uint32_t kErrColqResident = 0x303;
+
+// The codes of eight neighbouring columns of one row, each column with its own scale (see cpmk_round_rule.h).
+__device__ __forceinline__ uint2 round8_per_column(const uint4 &v, const float (&s)[8], const float (&r_up)[8], const float (&r_dn)[8]) {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+    const float2 magic = make_float2(CPMK_ROUND_MAGIC, CPMK_ROUND_MAGIC);
+    uint32_t bits[8];
+    float2 bad = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        const float2 up = __ffma2_rn(f, make_float2(r_up[2 * j], r_up[2 * j + 1]), magic);
+        const float2 dn = __ffma2_rn(f, make_float2(r_dn[2 * j], r_dn[2 * j + 1]), magic);
+        const float2 d = __fadd2_rn(up, make_float2(-dn.x, -dn.y));
+        bad = __ffma2_rn(d, d, bad);
+        bits[2 * j] = __float_as_uint(dn.x);
+        bits[2 * j + 1] = __float_as_uint(dn.y);
+    }
+    const float bad_sum = bad.x + bad.y;
+    if (!(bad_sum == 0.f)) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(h[j]);
+            const float2 up = __ffma2_rn(f, make_float2(r_up[2 * j], r_up[2 * j + 1]), magic);
+            const float2 dn = __ffma2_rn(f, make_float2(r_dn[2 * j], r_dn[2 * j + 1]), magic);
+            // a tie inside the domain: up = dn + 1 (false for NaN / the out-of-domain marker), the even neighbour;
+            // anything else irregular: the reference expression
+            const bool fast_x = up.x == dn.x || up.x - dn.x == 1.f;
+            const bool fast_y = up.y == dn.y || up.y - dn.y == 1.f;
+            bits[2 * j] = fast_x ? resolve_tie(__float_as_uint(up.x), __float_as_uint(dn.x)) : (uint8_t)round_reference(f.x, s[2 * j]);
+            bits[2 * j + 1] = fast_y ? resolve_tie(__float_as_uint(up.y), __float_as_uint(dn.y)) : (uint8_t)round_reference(f.y, s[2 * j + 1]);
+        }
+    }
+    uint2 q;
+    q.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+    q.y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
+    return q;
+}
+
+__global__ void __launch_bounds__(kBlock, 2) quant_cols_resident_kernel(const __grid_constant__ CUtensorMap tmap, int32_t n, int32_t m, int32_t rows_per_cta,
+                                                                        int32_t chunks, __half *__restrict__ scale, int8_t *__restrict__ out,
+                                                                        uint32_t *status) {
+    extern __shared__ __align__(128) uint8_t strip[];            // [rows_per_cta][64] fp16, row after row
+    __shared__ __align__(8) uint64_t bars[kRsMaxChunks];
+    __shared__ __half2 red[kStripRows][kRsCols / 2 + 1];
+    __shared__ __align__(16) __half my_max[kRsCols];
+    __shared__ float col_s[kRsCols], col_up[kRsCols], col_dn[kRsCols];
+    __shared__ uint32_t abort_word;
+    volatile uint32_t *abort_flag = &abort_word;
+    const uint32_t rank = cluster_rank_of_cta(), cluster = cluster_num_ctas();
+    const int t = threadIdx.x, cl = t & 7, rl = t >> 3;
+    const int strip_idx = blockIdx.x / cluster, b = blockIdx.y;
+    const int c0 = strip_idx * kRsCols;
+    const int row0 = (int)rank * rows_per_cta;
+    const uint32_t strip_base = smem_u32(strip), bar_base = smem_u32(bars);
+
+    if (t == 0) {
+        for (int c = 0; c < chunks; ++c) mbar_init(bar_base + 8 * c, 1);
+        abort_word = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // rows beyond n (and columns beyond m) are filled with zeros by the copy and still count towards its bytes
+        for (int c = 0; c < chunks; ++c) {
+            mbar_expect_tx(bar_base + 8 * c, kRsChunkBytes);
+            tma_load_tile_3d(strip_base + c * kRsChunkBytes, &tmap, c0, row0 + c * kRsChunkRows, b, bar_base + 8 * c);
+        }
+    }
+    __syncthreads();
+
+    // ---- column maxima of this CTA's rows, box by box as they land ----
+    __half2 m2[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) m2[i] = __float2half2_rn(0.f);
+    bool alive = true;
+    for (int c = 0; c < chunks; ++c) {
+        if (!mbar_wait(bar_base + 8 * c, 0u, abort_flag, status, kErrColqResident)) { alive = false; break; }
+#pragma unroll
+        for (int i = 0; i < kRsChunkRows / kStripRows; ++i) {
+            const int r = c * kRsChunkRows + rl + i * kStripRows;
+            const uint4 v = *reinterpret_cast<const uint4 *>(strip + ((size_t)r * kRsCols + cl * 8) * 2);
+            const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) m2[j] = __hmax2(__habs2(h[j]), m2[j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) red[rl][cl * 4 + i] = m2[i];
+    __syncthreads();
+    if (t < kRsCols / 2) {
+        __half2 acc = red[0][t];
+#pragma unroll 8
+        for (int r = 1; r < kStripRows; ++r) acc = __hmax2(acc, red[r][t]);
+        reinterpret_cast<__half2 *>(my_max)[t] = acc;
+    }
+    // ---- exchange: every CTA of the cluster reads the 64 maxima of all of them ----
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (t < kRsCols) {
+        float amax = 0.f;
+        const uint32_t mine = smem_u32(&my_max[t]);
+        uint16_t peer[kRsMaxCluster];
+#pragma unroll
+        for (uint32_t r = 0; r < (uint32_t)kRsMaxCluster; ++r) peer[r] = r < cluster ? ld_dsmem_u16(dsmem_address(mine, r)) : (uint16_t)0;
+#pragma unroll
+        for (int r = 0; r < kRsMaxCluster; ++r) amax = fmaxf(amax, __half2float(__ushort_as_half(peer[r])));
+        const __half sh = scale_from_amax(amax);
+        const float s = __half2float(sh);
+        float r_up, r_dn;
+        cpmk_round_prepare(s, &r_up, &r_dn);
+        if (!(cpmk_scale_in_domain(s) && cpmk_round_domain_ok(amax, r_up))) r_up = __int_as_float(0x7fc00000);
+        col_s[t] = s;
+        col_up[t] = r_up;
+        col_dn[t] = r_dn;
+        if (rank == 0 && alive && c0 + t < m) scale[(int64_t)b * m + c0 + t] = sh;
+    }
+    // nobody reads this CTA's maxima after this arrival; the matching wait is at the end, so that no CTA exits earlier
+    cluster_arrive_release();
+    __syncthreads();
+
+    // ---- round this CTA's rows out of shared memory ----
+    const int col = c0 + cl * 8;
+    if (alive && !*abort_flag && col < m) {
+        float s[8], r_up[8], r_dn[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            s[j] = col_s[cl * 8 + j];
+            r_up[j] = col_up[cl * 8 + j];
+            r_dn[j] = col_dn[cl * 8 + j];
+        }
+        int8_t *obase = out + (int64_t)b * n * m + col;
+        const int r_end = min(rows_per_cta, n - row0);                // rows of this CTA inside the operand
+#pragma unroll 4
+        for (int r = rl; r < r_end; r += kStripRows) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(strip + ((size_t)r * kRsCols + cl * 8) * 2);
+            *reinterpret_cast<uint2 *>(obase + (int64_t)(row0 + r) * m) = round8_per_column(v, s, r_up, r_dn);
+        }
+    }
+    cluster_wait_acquire();
+    if (*abort_flag) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);          // let copies in flight land before the strip is released
+    }
+}
+
 // Any shape: one thread per column, the reference expressions (m not a multiple of 8).
 template <int MODE>
 __global__ void __launch_bounds__(kBlock) quant_cols_generic_kernel(int32_t batch, int32_t n, int32_t m, const __half *__restrict__ mat,
@@ -793,6 +951,70 @@ ColPlan plan_cols(int32_t batch, int32_t n, int32_t m, int sm_count, size_t part
     return p;
 }
 
+// Launches quant_cols_resident_kernel when the shape and the device admit it (*done says whether it did).
+int32_t launch_quant_cols_resident(int32_t batch, int32_t n, int32_t m, const __half *src, __half *sc, int8_t *dst, cudaStream_t stream,
+                                   const DeviceInfo &info, const Workspace &ws, bool *done) {
+    *done = false;
+    int cluster = 1;
+    while (cluster <= kRsMaxCluster && (n + cluster - 1) / cluster > kRsMaxChunks * kRsChunkRows) cluster <<= 1;
+    if (cluster > kRsMaxCluster) return CPMK_OK;
+    const int rows_per_cta = ((n + cluster - 1) / cluster + kRsChunkRows - 1) / kRsChunkRows * kRsChunkRows;
+    const int chunks = rows_per_cta / kRsChunkRows;
+    const size_t smem = (size_t)rows_per_cta * kRsCols * 2;
+    if (info.max_smem_optin < (int)smem + 8192 || batch > 65535) return CPMK_OK;
+    const int dev = info.device & 63;
+    static std::once_flag attr_once[64];
+    static cudaError_t attr_err[64];
+    std::call_once(attr_once[dev], [dev] {
+        cudaError_t e = cudaFuncSetAttribute(quant_cols_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRsMaxChunks * kRsChunkBytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(quant_cols_resident_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        attr_err[dev] = e;
+        (void)cudaGetLastError();
+    });
+    if (attr_err[dev] != cudaSuccess) return CPMK_OK;
+    const int64_t strips = (m + kRsCols - 1) / kRsCols;
+    if (strips * cluster >= (int64_t(1) << 31)) return CPMK_OK;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(strips * cluster), (unsigned)batch, 1);
+    cfg.blockDim = dim3(kBlock, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // a cluster of this size and footprint must fit the device (asked once per device and cluster size)
+    static int fits[64][kRsMaxCluster + 1];                  // 0: not asked, 1: fits, -1: does not
+    static std::mutex fits_mutex;
+    {
+        std::lock_guard<std::mutex> lock(fits_mutex);
+        if (fits[dev][cluster] == 0) {
+            int clusters = 0;
+            cudaLaunchConfig_t probe = cfg;
+            probe.dynamicSmemBytes = kRsMaxChunks * kRsChunkBytes;
+            const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, quant_cols_resident_kernel, &probe);
+            fits[dev][cluster] = (e == cudaSuccess && clusters > 0) ? 1 : -1;
+            (void)cudaGetLastError();
+        }
+        if (fits[dev][cluster] < 0) return CPMK_OK;
+    }
+    CUtensorMap tmap;
+    const uint64_t dims[3] = {(uint64_t)m, (uint64_t)n, (uint64_t)batch};
+    const uint64_t strides[2] = {(uint64_t)m * 2, (uint64_t)n * (uint64_t)m * 2};
+    const uint32_t box[3] = {(uint32_t)kRsCols, (uint32_t)kRsChunkRows, 1u};
+    if (!encode_tiled_3d(&tmap, 2, src, dims, strides, box, false)) return CPMK_OK;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, quant_cols_resident_kernel, tmap, n, m, (int32_t)rows_per_cta, (int32_t)chunks, sc, dst, ws.status());
+    if (e != cudaSuccess) {
+        set_error("kernel launch failed: %s (%s:%d)", cudaGetErrorString(e), __FILE__, __LINE__);
+        return CPMK_ECUDA;
+    }
+    *done = true;
+    return CPMK_OK;
+}
+
 // MODE 0: fused; 1: scale only; 2: round only with the caller's scale
 template <int MODE>
 int32_t launch_quant_cols(int32_t batch, int32_t n, int32_t m, const void *mat, void *scale, void *out, cudaStream_t stream) {
@@ -838,6 +1060,14 @@ int32_t launch_quant_cols(int32_t batch, int32_t n, int32_t m, const void *mat, 
         colmax_finish_kernel<<<(unsigned)blocks, kBlock, 0, stream>>>(batch, m, p.splits, partial, sc);
         CPMK_LAUNCH_CHECK();
         return CPMK_OK;
+    }
+    // The resident-strip kernel reads the operand once: any operand whose rows fit 8 CTAs of 768 rows, big enough to
+    // fill the machine.
+    if ((int64_t)batch * n * m >= (int64_t(1) << 21) && n <= 8 * kRsMaxChunks * kRsChunkRows && !getenv("CPMK_QUANT_NO_RESIDENT")) {
+        bool done = false;
+        rc = launch_quant_cols_resident(batch, n, m, src, sc, dst, stream, info, ws, &done);
+        if (rc) return rc;
+        if (done) return CPMK_OK;
     }
     // Operands of 64 MB and more (below that the register-staged kernels measured faster): the streaming kernels
     // (96 KiB ring, two blocks per SM).

@@ -3,7 +3,7 @@ from .base import DevicePointer, CUDAStream, round_up
 from .gemm import (gemm_calc_scale, gemm_calc_scale_transpose, gemm_round, gemm_round_transpose, gemm_scale,
                    gemm_int8, gemm_fp16, gemm_backward_round_scale, gemm_backward_scale_round, gemm_scale_x, gemm_scale_y,
                    gemm_quantize_rows, gemm_quantize_rows_pair, gemm_quantize_cols, gemm_int8_scale, gemm_int8_scale_gelu, gemm_int8_scale_scatter,
-                   gemm_quantize_rows_pair_scatter, linear_int8_scatter)
+                   gemm_quantize_rows_pair_scatter, linear_int8_scatter, gemm_int8_scale_multicast)
 from .gelu import gelu_forward, gelu_inplace_forward
 from .layernorm import layernorm_quantize_cols
 from .transpose import transpose

@@ -219,11 +219,25 @@ def linear_int8_scatter(tokens: int, k: int, n_local: int,
                         w: DevicePointer,          # (n_local, k)   fp16: this rank's rows of the weight
                         scale_x: DevicePointer, q_x: DevicePointer, scale_w: DevicePointer, q_w: DevicePointer,   # written
                         dst,                       # ctypes array of device addresses, or a list of them
-                        dst_row_pitch: int, stream: CUDAStream):
+                        dst_row_pitch: int, stream: CUDAStream, multicast: bool = False):
     """One column-parallel int8 linear in one call: quantise x and w (one launch), GEMM + dequantisation stored to every
     destination (one launch).  Every buffer is the caller's.  torch/gemm.py:86-113 for the sharded layout."""
     import ctypes
     if isinstance(dst, (list, tuple)):
         dst = (ctypes.c_void_p * len(dst))(*dst)
     cpmk.call("cpmk_linear_int8_scatter", tokens, k, n_local, x, w, scale_x, q_x, scale_w, q_w, len(dst), dst, dst_row_pitch,
-              stream_arg(stream))
+              int(bool(multicast)), stream_arg(stream))
+
+
+def gemm_int8_scale_multicast(m: int, k: int, n: int, batchA: int, batchB: int, aT: bool, bT: bool,
+                              A: DevicePointer, B: DevicePointer, scale_x: DevicePointer, scale_y: DevicePointer,
+                              broad_cast_x: bool, broad_cast_y: bool,
+                              dst_local: DevicePointer,        # this GPU's copy of the result slice
+                              dst_multicast: DevicePointer,    # the same slice at the buffer's multicast address
+                              dst_row_pitch: int, stream: CUDAStream):
+    """gemm_int8_scale whose result goes to this GPU's buffer and, through one multimem store per 16 bytes that the NVLink
+    switch replicates, to every GPU's copy of a multicast-mapped buffer.  No counterpart in the reference."""
+    assert m % 4 == 0 and n % 4 == 0 and k % 4 == 0
+    assert batchA == batchB or batchA == 1 or batchB == 1
+    cpmk.call("cpmk_gemm_int8_dequant_multicast", m, k, n, batchA, batchB, int(bool(aT)), int(bool(bT)), A, B, scale_x, scale_y,
+              int(bool(broad_cast_x)), int(bool(broad_cast_y)), dst_local, dst_multicast, dst_row_pitch, stream_arg(stream))

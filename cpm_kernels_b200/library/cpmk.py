@@ -30,7 +30,8 @@ SIGNATURES = {
     "cpmk_release_workspace": [_p],
     "cpmk_selftest_bounded_wait": [c_uint32, _p],
     "cpmk_quantize_rows_pair_scatter": [_i, _p, _i, POINTER(c_void_p), POINTER(c_void_p), _i, _p, _p, _p, _i, _p],
-    "cpmk_linear_int8_scatter": [_i, _i, _i, _p, _p, _p, _p, _p, _p, _i, POINTER(c_void_p), ctypes.c_int64, _p],
+    "cpmk_linear_int8_scatter": [_i, _i, _i, _p, _p, _p, _p, _p, _p, _i, POINTER(c_void_p), ctypes.c_int64, _i, _p],
+    "cpmk_gemm_int8_dequant_multicast": [_i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p, _p, ctypes.c_int64, _p],
     "cpmk_gemm_calc_scale": [_i, _i, _i, _p, _p, _p],
     "cpmk_gemm_calc_scale_transpose": [_i, _i, _i, _p, _p, _p],
     "cpmk_gemm_round": [_i, _i, _i, _p, _p, _p, _p],
@@ -56,6 +57,7 @@ SIGNATURES = {
     "cpmk_gemv_fp16": [_i, _i, _i, _p, _p, _p, _p],
     "cpmk_gemv_fp16_transpose": [_i, _i, _i, _p, _p, _p, _p],
     "cpmk_gemv_fp16_transpose_noalloc": [_i, _i, _i, _p, _p, _p, _p],
+    "cpmk_probe_read": [_i, _i, _i, _p, _p, _p],
     "cpmk_gemv_broadcast_mat_fp16": [_i, _i, _i, _p, _p, _p, _p],
     "cpmk_gemv_calc_scale": [_i, _i, _p, _p, _p],
     "cpmk_gemv_round": [_i, _i, _p, _p, _p, _p],

@@ -106,10 +106,14 @@ class SymmetricArena:
             self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
             self.handle = symm_mem.rendezvous(self.buf, self.group)
             self.base = [int(self.handle.buffer_ptrs[p]) for p in range(self.world)]
+            # the same allocation mapped through an NVLink multicast object (0 when the system has none): one store to
+            # multicast_base + offset lands in every rank's copy
+            self.multicast_base = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         else:
             self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
             self.handle = None
             self.base = [self.buf.data_ptr()]
+            self.multicast_base = 0
 
     def carve(self, shape, dtype: torch.dtype) -> Tuple[torch.Tensor, int]:
         """A (local tensor, offset) pair; the peers' copies are at ``peer_ptr(p, offset)``."""
@@ -211,14 +215,18 @@ class FusedColumnParallelInt8Linear:
             self._own[tokens] = ExchangeBuffers(arena, tokens, self.k, self.n_total)
         return self._own[tokens]
 
-    def _dsts(self, buf: ExchangeBuffers, slot: int, only_local: bool = False):
-        """(y destinations, code destinations, scale destinations) of this rank's contribution, as ctypes arrays."""
-        key = (id(buf), slot, only_local)
+    def _dsts(self, buf: ExchangeBuffers, slot: int, only_local: bool = False, multicast: bool = False):
+        """(y destinations, code destinations, scale destinations) of this rank's contribution, as ctypes arrays.
+        multicast: the y destinations are this rank's copy and the buffer's multicast address."""
+        key = (id(buf), slot, only_local, multicast)
         if key not in self._dst_cache:
             arena = buf.arena
             peers = [self.rank] if only_local else _peer_order(self.rank, self.world)
             rows = buf.tokens // self.world
             y = [arena.peer_ptr(p, buf.y_off[slot]) + 2 * self.rank * self.n_local for p in peers]
+            if multicast and not only_local:
+                assert arena.multicast_base, "the symmetric arena has no multicast mapping on this system"
+                y = [y[0], arena.multicast_base + buf.y_off[slot] + 2 * self.rank * self.n_local]
             qx = [arena.peer_ptr(p, buf.qx_off[slot]) + self.rank * rows * self.k for p in peers]
             sx = [arena.peer_ptr(p, buf.sx_off[slot]) + 2 * self.rank * rows for p in peers]
             self._dst_cache[key] = tuple((ctypes.c_void_p * len(v))(*v) for v in (y, qx, sx))
@@ -229,24 +237,28 @@ class FusedColumnParallelInt8Linear:
         return torch.cuda.current_stream().cuda_stream
 
     # ---- x present in full on every rank ----
-    def launch(self, x: torch.Tensor, slot: int = 0, only_local: bool = False) -> torch.Tensor:
+    def launch(self, x: torch.Tensor, slot: int = 0, only_local: bool = False, multicast: bool = False) -> torch.Tensor:
         """Quantise x and the weight rows, run the scattering GEMM (two launches, one library call); no barrier.
-        ``only_local``: store this rank's columns into its own y only (the compute phase without the exchange)."""
+        ``only_local``: store this rank's columns into its own y only (the compute phase without the exchange).
+        ``multicast``: reach the other ranks through the buffers' NVLink multicast mapping (one multimem store per 16
+        bytes, replicated by the switch) instead of one store per peer."""
         from .kernels import linear_int8_scatter
         assert x.ndim == 3 and x.size(0) == 1 and x.is_contiguous() and x.is_cuda and x.dtype == torch.half and x.size(2) == self.k
         tokens = x.size(1)
         buf = self._buffers_for(tokens)
-        y_dst, _, _ = self._dsts(buf, slot, only_local)
+        multicast = multicast and not only_local and self.world > 1
+        y_dst, _, _ = self._dsts(buf, slot, only_local, multicast)
         with torch.cuda.device(x.device):
             linear_int8_scatter(tokens, self.k, self.n_local, x.data_ptr(), self.weight.data_ptr(), buf.sx[slot].data_ptr(),
-                                buf.qx[slot].data_ptr(), self.scale_w.data_ptr(), self.q_w.data_ptr(), y_dst, self.n_total, self._stream())
+                                buf.qx[slot].data_ptr(), self.scale_w.data_ptr(), self.q_w.data_ptr(), y_dst, self.n_total, self._stream(),
+                                multicast=multicast)
         return buf.y[slot]
 
-    def forward(self, x: torch.Tensor, sync_before: bool = False, slot: int = 0) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, sync_before: bool = False, slot: int = 0, multicast: bool = False) -> torch.Tensor:
         buf = self._buffers_for(x.size(1))
         if sync_before:
             buf.arena.barrier(0)           # every rank is done reading the slot's previous contents
-        y = self.launch(x, slot)
+        y = self.launch(x, slot, multicast=multicast)
         buf.arena.barrier(1)               # every rank's stores have landed before anyone reads y
         return y
 

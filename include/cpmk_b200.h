@@ -168,9 +168,23 @@ int32_t cpmk_gemm_int8_dequant_scatter(int32_t m, int32_t k, int32_t n, int32_t 
  * x (tokens, k) and this rank's weight rows w (n_local, k), then cpmk_gemm_int8_dequant_scatter of the product into
  * `n_dst` destinations (y[:, r*n_local : (r+1)*n_local] of every rank).  scale_x (tokens), q_x (tokens, k), scale_w
  * (n_local), q_w (n_local, k) receive the quantised operands (what cpm_kernels/torch/gemm.py:107-112 saves for
- * backward).  Replaces the six launches and six allocations of cpm_kernels/torch/gemm.py:86-113 for this layout. */
+ * backward).  multicast != 0: n_dst is 2 and dst[1] is the multicast address of the result slice
+ * (cpmk_gemm_int8_dequant_multicast).  Replaces the six launches and six allocations of
+ * cpm_kernels/torch/gemm.py:86-113 for this layout. */
 int32_t cpmk_linear_int8_scatter(int32_t tokens, int32_t k, int32_t n_local, const void *x, const void *w, void *scale_x, void *q_x,
-                                 void *scale_w, void *q_w, int32_t n_dst, void *const *dst, int64_t dst_row_pitch, cpmk_stream_t stream);
+                                 void *scale_w, void *q_w, int32_t n_dst, void *const *dst, int64_t dst_row_pitch, int32_t multicast,
+                                 cpmk_stream_t stream);
+
+/* cpmk_gemm_int8_dequant_scatter for buffers that are also mapped through an NVLink multicast object (CUDA multicast
+ * objects; torch symmetric memory exposes the address as `multicast_ptr`): dst_local is this GPU's own copy of the
+ * result slice, dst_multicast the same slice at the multicast address.  The computing CTAs store to dst_local; the
+ * forwarding CTAs of the same grid copy every finished tile to dst_multicast with multimem.st, ONE store that the
+ * NVLink switch replicates into every GPU's copy -- each GPU then sends its slice once instead of once per peer.
+ * No counterpart in the reference. */
+int32_t cpmk_gemm_int8_dequant_multicast(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t batchB, int32_t aT, int32_t bT,
+                                         const void *A, const void *B, const void *scale_x, const void *scale_y,
+                                         int32_t broad_cast_x, int32_t broad_cast_y, void *dst_local, void *dst_multicast,
+                                         int64_t dst_row_pitch, cpmk_stream_t stream);
 
 /* Layer norm over the MIDDLE axis of mat (batch, n, m) fp16, per-row affine, and quantisation along that same axis,
  * without storing the intermediate tensors: what cpm_kernels runs as four kernels between a layer norm and the int8
@@ -256,6 +270,13 @@ int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in,
  *   All calls on a device share the one array: two calls that overlap on the GPU (different streams) race. */
 int32_t cpmk_gemv_fp16_transpose_noalloc(int32_t batch, int32_t dim_out, int32_t dim_in, const void *mat, const void *vec, void *out,
                                          cpmk_stream_t stream);
+
+/* Measurement aid, no counterpart in the reference: reads a (rows, row_elems) fp16 matrix once and computes nothing, so
+ * that the decode GEMVs can be compared with what merely reading the matrix costs.  mode 0: a plain grid-stride read
+ * (16-byte loads, four in flight per thread); mode 1: the launch shape and shared-memory copy pipeline of the streaming
+ * row GEMV with the arithmetic left out.  `sink` (at least rows * 2 bytes) is written only if a checksum happens to
+ * hit a magic value.  row_elems a multiple of 8, src 16-byte aligned. */
+int32_t cpmk_probe_read(int32_t mode, int32_t rows, int32_t row_elems, const void *src, void *sink, cpmk_stream_t stream);
 
 /* kernels/gemv.py:218-283 gemv_broadcast_mat_fp16 / _light -> cuda/gemv.cu:138-164.
  * mat (dim_out, dim_in) shared by all `batch` vectors. */

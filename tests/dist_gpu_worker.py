@@ -66,6 +66,18 @@ def main():
             assert (layer.buffers.qx[slot].cpu().numpy() == want["quant_A"]).all(), "gathered int8 codes differ from the unsharded codes"
             assert same(layer.buffers.sx[slot], want["scale_A"]), "gathered scales differ from the unsharded scales"
             dist.barrier()
+            # forwarding CTAs: the computing CTAs store to this rank's result only, a few CTAs of the grid copy finished
+            # tiles to the peers -- with plain stores, and (where the buffers have a multicast mapping) with multimem stores
+            for multicast in ((False, True) if arena.multicast_base else (False,)):
+                layer.buffers.y[slot].fill_(3.0)
+                torch.cuda.synchronize()
+                dist.barrier()
+                cpmk.set_gemm_forward_sms(16)
+                y = layer.forward(x.cuda(), sync_before=True, slot=slot, multicast=multicast)
+                torch.cuda.synchronize()
+                cpmk.set_gemm_forward_sms(-1)
+                assert same(y, want["out"]), "forwarding CTAs (multicast=%s): result differs from the oracle (slot %d)" % (multicast, slot)
+                dist.barrier()
     assert cpmk.read_status() == 0
     dist.barrier()
     dist.destroy_process_group()

@@ -72,6 +72,63 @@ def test_column_quantisation_matches_oracle(G, shape):
     G.assert_no_device_error()
 
 
+# the resident-strip kernel (operand read once; clusters of 1 to 8 CTAs hold a 64-column strip in shared memory)
+RESIDENT_SHAPES = [
+    (1, 4096, 10240),      # cluster of 8, 512 rows per CTA: the operand of the benchmark
+    (1, 6144, 1024),       # the tallest it takes: 8 x 768 rows
+    (1, 6145, 1024),       # one row too many: the two-pass kernels
+    (1, 10240, 4096),      # taller still: the two-pass streaming kernels
+    (2, 700, 2056),        # one CTA per strip; m % 64 = 8: a ragged last strip; rows not a multiple of the 128-row boxes
+    (1, 1500, 1416),       # cluster of 2, ragged rows and columns
+    (1, 3001, 1000),       # cluster of 4; the last CTA holds 697 of its 768 rows
+    (8, 4096, 512),        # batched: (batch, hidden, seq) activations
+]
+
+
+@pytest.mark.parametrize("shape", RESIDENT_SHAPES)
+def test_column_quantisation_resident_strips(G, shape):
+    x = randn_fp16(shape, seed=shape[1] * 13 + shape[2], std=1.0)
+    xh = np16(x)
+    want_s = ql.gemm_calc_scale_transpose(xh)
+    want_q = ql.gemm_round_transpose(xh, want_s)
+    xd = x.cuda()
+    for _ in range(2):
+        s, q = G.quantize(xd, transpose=True)
+        assert G.same_bits(s, want_s)
+        assert (G.host(q) == want_q).all()
+    G.assert_no_device_error()
+
+
+def test_column_quantisation_resident_strips_edge_columns(G):
+    """Columns that leave the division-free rule's domain, inside an operand large enough for the resident-strip
+    kernel: all zero (scale 0: 0/0), subnormal scale, NaN, +-inf, the largest finite value, exact .5 ties."""
+    x = randn_fp16((1, 2048, 1024), 77).numpy().copy()
+    x[0, :, 0] = 0
+    x[0, :, 1] = np.float16(6e-8) * (np.arange(2048) % 5)
+    x[0, :, 2] = np.float16(2e-5) * ((np.arange(2048) % 7) - 3)
+    x[0, 100, 3] = np.float16(np.nan)
+    x[0, 200, 4] = np.float16(np.inf)
+    x[0, 300, 4] = -np.float16(np.inf)
+    x[0, 5, 5] = np.float16(65504.0)
+    x[0, :, 6] = 0
+    x[0, 0, 6] = np.float16(127.0)                                   # scale exactly 1: k + 0.5 are exact ties
+    x[0, 1:200, 6] = (np.arange(199) % 100 - 50).astype(np.float16) + np.float16(0.5)
+    x[0, :, 7] = np.float16(-0.0)
+    x[0, :, 1023] = x[0, :, 6]
+    want_s = ql.gemm_calc_scale_transpose(x)
+    want_q = ql.gemm_round_transpose(x, want_s)
+    s, q = G.quantize(torch.from_numpy(x).cuda(), transpose=True)
+    assert G.same_bits(s, want_s)
+    assert (G.host(q) == want_q).all()
+    if ref_cuda.available():
+        ref = ref_cuda.ReferenceKernels()
+        xd = torch.from_numpy(x).cuda()
+        rs = ref.gemm_calc_scale_transpose(xd)
+        assert G.same_bits(s, rs)
+        assert (G.host(q) == G.host(ref.gemm_round_transpose(xd, rs))).all()
+    G.assert_no_device_error()
+
+
 def test_round_with_foreign_scales(G):
     """gemm_round / gemm_round_transpose take any scale, not only the absmax one: values far outside
     [-127, 127], zero, subnormal, inf and NaN scales must give what the reference expression gives."""
