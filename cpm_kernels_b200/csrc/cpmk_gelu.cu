@@ -31,6 +31,26 @@ __global__ void __launch_bounds__(256) gelu_direct_kernel(int64_t count, const _
     for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < count; i += (int64_t)gridDim.x * 256) out[i] = gelu_half(in[i]);
 }
 
+// grad[i] = gelu'(mat[i]) * grad_out[i]; eight elements per thread and step where the pointers allow 128-bit accesses
+__global__ void __launch_bounds__(256) gelu_backward_kernel(int64_t count, int vec_ok, const __half *__restrict__ grad_out, const __half *__restrict__ mat,
+                                                            __half *__restrict__ grad) {
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    int64_t done = 0;
+    if (vec_ok) {
+        const int64_t nvec = count >> 3;
+        for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < nvec; i += stride) {
+            const uint4 g = __ldcs(reinterpret_cast<const uint4 *>(grad_out) + i), x = __ldcs(reinterpret_cast<const uint4 *>(mat) + i);
+            const __half *gh = reinterpret_cast<const __half *>(&g), *xh = reinterpret_cast<const __half *>(&x);
+            __align__(16) __half o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = gelu_backward_half(gh[j], xh[j]);
+            __stcs(reinterpret_cast<uint4 *>(grad) + i, *reinterpret_cast<const uint4 *>(o));
+        }
+        done = nvec << 3;
+    }
+    for (int64_t i = done + (int64_t)blockIdx.x * 256 + threadIdx.x; i < count; i += stride) grad[i] = gelu_backward_half(grad_out[i], mat[i]);
+}
+
 // in == out is allowed (each element is read before it is written, by the same thread)
 __global__ void __launch_bounds__(kLutThreads, 1) gelu_lut_kernel(int64_t count, const __half *in, __half *out, const __half *__restrict__ table) {
     extern __shared__ __align__(16) unsigned short lut[];
@@ -130,9 +150,31 @@ int32_t launch_gelu(int64_t count, const void *in, void *out, cudaStream_t strea
     return CPMK_OK;
 }
 
+int32_t launch_gelu_backward(int64_t count, const void *grad_out, const void *mat, void *grad, cudaStream_t stream) {
+    DeviceInfo info;
+    int32_t rc = current_device_info(&info);
+    if (rc) return rc;
+    if (count == 0) return CPMK_OK;
+    CPMK_REQUIRE(grad_out && mat && grad, "null pointer");
+    CPMK_REQUIRE(((reinterpret_cast<uintptr_t>(grad_out) | reinterpret_cast<uintptr_t>(mat) | reinterpret_cast<uintptr_t>(grad)) & 1u) == 0,
+                 "pointers must be 2-byte aligned");
+    const int vec_ok = aligned16(grad_out) && aligned16(mat) && aligned16(grad);
+    const int64_t blocks = ceil_div64(vec_ok ? (count + 7) / 8 : count, 256);
+    const int grid = (int)(blocks < (int64_t)info.sm_count * 16 ? blocks : (int64_t)info.sm_count * 16);
+    gelu_backward_kernel<<<grid, 256, 0, stream>>>(count, vec_ok, static_cast<const __half *>(grad_out), static_cast<const __half *>(mat),
+                                                   static_cast<__half *>(grad));
+    CPMK_LAUNCH_CHECK();
+    return CPMK_OK;
+}
+
 }  // namespace cpmk
 
 using namespace cpmk;
+
+extern "C" int32_t cpmk_gelu_backward(int32_t batch, int32_t n, const void *grad_out, const void *mat, void *grad, cpmk_stream_t stream) {
+    CPMK_REQUIRE(batch >= 0 && n >= 0, "negative size: batch=%d n=%d", batch, n);
+    return launch_gelu_backward((int64_t)batch * n, grad_out, mat, grad, as_stream(stream));
+}
 
 extern "C" int32_t cpmk_gelu_forward(int32_t batch, int32_t n, const void *mat, void *out, cpmk_stream_t stream) {
     CPMK_REQUIRE(batch >= 0 && n >= 0, "negative size: batch=%d n=%d", batch, n);

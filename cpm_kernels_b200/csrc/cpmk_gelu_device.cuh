@@ -15,4 +15,22 @@ __device__ __forceinline__ float gelu_reference(float x) {
 
 __device__ __forceinline__ __half gelu_half(__half h) { return __float2half(gelu_reference(__half2float(h))); }
 
+// The derivative, exactly as the reference evaluates it (cuda/gelu.cu:33-42): double literals again, so the cubic and
+// the final sum run in binary64 around binary32 coshf / tanhf, sech2 is squared in binary32, and outside (-5, 5) the
+// derivative is the step function.  grad = half(gelu'(x) * grad_out), one binary32 product.
+__device__ __forceinline__ __half gelu_backward_half(__half grad_out, __half mat) {
+    float v = __half2float(grad_out);
+    float x = __half2float(mat);
+    float gelu_grad;
+    if (-5 < x && x < 5) {
+        float x3 = x * x * x;
+        float sech2 = 1.0 / coshf(0.797885 * x + 0.0356774 * x3);
+        sech2 = sech2 * sech2;
+        gelu_grad = 0.5 + (0.398942 * x + 0.0535161 * x3) * sech2 + 0.5 * tanhf(0.797885 * x + 0.0356774 * x3);
+    } else {
+        gelu_grad = x < 0 ? 0 : 1;
+    }
+    return __float2half(gelu_grad * v);
+}
+
 }  // namespace cpmk

@@ -51,6 +51,7 @@ SIGNATURES = {
     "cpmk_set_gemm_sm_margin": [_i],
     "cpmk_set_gemm_forward_sms": [_i],
     "cpmk_gelu_forward": [_i, _i, _p, _p, _p],
+    "cpmk_gelu_backward": [_i, _i, _p, _p, _p, _p],
     "cpmk_transpose": [_i, _i, _i, _p, _p, _p],
     "cpmk_gemm_int8_dequant_gelu": [_i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _i, _p, _p],
     "cpmk_gemm_fp16": [_i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p],

@@ -1,9 +1,9 @@
 """``gelu`` / ``gelu_inplace`` with the interface of cpm_kernels/torch/gelu.py: the activation that follows the
-feed-forward block's first linear.  Forward on the library's kernel (same bits as the reference's); the backward of
-the autograd function evaluates the reference's derivative formula (cuda/gelu.cu:20-44) with torch operations."""
+feed-forward block's first linear.  Forward and backward both run on the library's kernels, which evaluate the
+reference's expressions (cuda/gelu.cu:6-44) as the reference compiles them: same bits as its kernels."""
 import torch
 
-from ..kernels import gelu_forward, gelu_inplace_forward
+from ..kernels import gelu_forward, gelu_inplace_forward, gelu_backward
 
 
 class OpGeLU(torch.autograd.Function):
@@ -20,13 +20,13 @@ class OpGeLU(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output: torch.Tensor):
-        x = ctx.saved_tensors[0].float()
-        x3 = x * x * x
-        inner = 0.797885 * x + 0.0356774 * x3
-        sech2 = (1.0 / torch.cosh(inner)) ** 2
-        g = 0.5 + (0.398942 * x + 0.0535161 * x3) * sech2 + 0.5 * torch.tanh(inner)
-        g = torch.where((x > -5) & (x < 5), g, (x >= 0).float())
-        return (g * grad_output.float()).half()
+        """torch/gelu.py:17-32."""
+        assert grad_output.is_contiguous() and grad_output.is_cuda and grad_output.dtype == torch.half
+        x = ctx.saved_tensors[0]
+        grad = torch.empty_like(x)
+        with torch.cuda.device(x.device):
+            gelu_backward(x.size(0), x.stride(0), grad_output.data_ptr(), x.data_ptr(), grad.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        return grad
 
 
 def gelu(x: torch.Tensor) -> torch.Tensor:

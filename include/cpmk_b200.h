@@ -204,6 +204,11 @@ int32_t cpmk_layernorm_quantize_cols(int32_t batch, int32_t n, int32_t m, const 
  * fills on its stream (that call should not be inside a stream capture). */
 int32_t cpmk_gelu_forward(int32_t batch, int32_t n, const void *mat, void *out, cpmk_stream_t stream);
 
+/* grad[b, i] = gelu'(mat[b, i]) * grad_out[b, i] on fp16: replaces cpm_kernels/kernels/gelu.py:50-69 gelu_backward
+ * (cuda/gelu.cu:20-44), the backward pass of cpm_kernels.torch.gelu (torch/gelu.py:17-32).  The derivative is the
+ * reference's expression compiled as the reference compiles it: same bits as its kernel for every (mat, grad_out). */
+int32_t cpmk_gelu_backward(int32_t batch, int32_t n, const void *grad_out, const void *mat, void *grad, cpmk_stream_t stream);
+
 /* out[b, c, r] = in[b, r, c] on fp16: replaces cpm_kernels/kernels/transpose.py:11-27 transpose (cuda/transpose.cu:6-22);
  * `in` is (batch, n, m) contiguous, `out` (batch, m, n).  Pure data movement, same bits.  in and out must not overlap. */
 int32_t cpmk_transpose(int32_t batch, int32_t n, int32_t m, const void *in, void *out, cpmk_stream_t stream);

@@ -202,6 +202,22 @@ def gelu_forward(x: np.ndarray) -> np.ndarray:
     return bits.view(np.float16)
 
 
+def gelu_backward(grad_out: np.ndarray, mat: np.ndarray) -> np.ndarray:
+    """cuda/gelu.cu:20-44 cu_gelu_backward in binary64: grad = gelu'(mat) * grad_out with
+        gelu'(x) = 0.5 + (0.398942 x + 0.0535161 x^3) sech^2(u) + 0.5 tanh(u),  u = 0.797885 x + 0.0356774 x^3   for -5 < x < 5,
+        gelu'(x) = 0 (x < 0) or 1 otherwise.
+    The device evaluates coshf / tanhf in binary32 with its own (not correctly rounded) routines, so this restatement
+    pins the kernel to a tolerance (rtol 2e-3, atol 1e-3 on the fp16 result), not bit for bit; bit parity of the
+    backward kernel is checked against the reference's own device code where it is available."""
+    assert grad_out.dtype == np.float16 and mat.dtype == np.float16
+    with np.errstate(all="ignore"):
+        x = mat.astype(np.float64)
+        u = 0.797885 * x + 0.0356774 * x ** 3
+        g = 0.5 + (0.398942 * x + 0.0535161 * x ** 3) / np.cosh(u) ** 2 + 0.5 * np.tanh(u)
+        g = np.where((x > -5) & (x < 5), g, np.where(x < 0, 0.0, 1.0))
+        return g * grad_out.astype(np.float64)
+
+
 def transpose(x: np.ndarray) -> np.ndarray:
     """cuda/transpose.cu:6-22 cu_transpose: out[b, c, r] = in[b, r, c] for a (batch, n, m) array; no arithmetic."""
     assert x.ndim == 3

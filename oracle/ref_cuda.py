@@ -183,6 +183,15 @@ class ReferenceKernels:
                         [self._i(b), self._i(n), self._p(mat), self._p(out)])
         return out
 
+    def gelu_backward(self, grad_out: torch.Tensor, mat: torch.Tensor) -> torch.Tensor:
+        """kernels/gelu.py:50-69: the launch shape of gelu_forward."""
+        b, n = mat.shape
+        grad = torch.empty_like(mat)
+        threads = min(_round_up(n, 32), 1024)
+        self.drv.launch(self._fn("gelu", "cu_gelu_backward"), (b, _round_up(n, threads) // threads, 1), (threads, 1, 1), self._stream(),
+                        [self._i(b), self._i(n), self._p(grad_out), self._p(mat), self._p(grad)])
+        return grad
+
     # ---- cpm_kernels/kernels/transpose.py --------------------------------------------------------
     def transpose(self, mat: torch.Tensor) -> torch.Tensor:
         """kernels/transpose.py:11-27: grid (batch, round_up(n, 32) / 32, round_up(m, 32) / 32), block (32, 32)."""

@@ -81,3 +81,39 @@ def test_bmm_gelu(G):
     y2 = y.clone()
     ct.gelu_inplace(y2)
     assert torch.equal(y2.view(torch.int16), z.view(torch.int16))
+
+
+def test_backward_matches_the_references_own_kernel_on_every_input(G):
+    """gelu_backward for every fp16 x, against cu_gelu_backward compiled from the reference's source and run on the same
+    GPU (bit for bit), and against the binary64 restatement of its formula (to a tolerance: the device's coshf / tanhf
+    are not correctly rounded)."""
+    from oracle import ref_cuda
+    x = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.float16).reshape(4, 16384).cuda()
+    for scale in (1.0, -0.37, 24.0):
+        g = (randn_fp16((4, 16384), 17) * scale).half().cuda()
+        grad = torch.empty_like(x)
+        ck.gelu_backward(4, 16384, g.data_ptr(), x.data_ptr(), grad.data_ptr(), G.stream())
+        got = G.host(grad)
+        if ref_cuda.available():
+            want = ref_cuda.ReferenceKernels().gelu_backward(g, x)
+            assert (got.view(np.uint16) == G.host(want).view(np.uint16)).all()
+        exact = ql.gelu_backward(G.host(g), G.host(x))
+        finite = np.isfinite(exact) & (np.abs(exact) < 6e4)
+        assert np.isclose(got.astype(np.float64)[finite], exact[finite], rtol=2e-3, atol=1e-3).all()
+    G.assert_no_device_error()
+
+
+@pytest.mark.parametrize("batch,n", [(1, 5), (3, 1001), (2, 70000)])
+def test_autograd_backward_runs_on_the_kernel(G, batch, n):
+    """torch.gelu's backward (cpm_kernels/torch/gelu.py:17-32): odd sizes (scalar tail), unaligned views are refused."""
+    x = randn_fp16((batch, n), 6, 2.0)
+    g = randn_fp16((batch, n), 7, 0.5)
+    xd = x.cuda().requires_grad_()
+    y = ct.gelu(xd)
+    y.backward(gradient=g.cuda())
+    exact = ql.gelu_backward(np16(g), np16(x))
+    assert np.isclose(G.host(xd.grad).astype(np.float64), exact, rtol=2e-3, atol=1e-3).all()
+    if batch > 1:
+        with pytest.raises(AssertionError):
+            y2 = ct.gelu(x.cuda().requires_grad_())
+            y2.backward(gradient=g.cuda().t().contiguous().t())       # not contiguous
