@@ -254,7 +254,7 @@ constexpr int kTsRingBytes = kTsStages * kTsStageBytes;        // 96 KiB
 constexpr int kTsVecFloats = 2048;                             // rows of the vector a block may keep in shared memory (8 KiB)
 
 __global__ void __launch_bounds__(kStreamThreads, 2) gemv_transpose_stream_kernel(int32_t dim_out, int32_t dim_in, int32_t rows_per_split,
-                                                                                  int32_t splits, int32_t x_in_smem, int32_t cluster_y, const __half *__restrict__ mat,
+                                                                                  int32_t splits, int32_t x_in_smem, const __half *__restrict__ mat,
                                                                                   const __half *__restrict__ vec, __half *__restrict__ out,
                                                                                   float *__restrict__ partial, uint32_t *__restrict__ tickets,
                                                                                   uint32_t *status) {
@@ -358,63 +358,6 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_transpose_stream_kerne
         }
     }
     __syncthreads();
-    if (cluster_y > 1) {
-        // Many row ranges per strip (one matrix of a few thousand columns): the blocks of `cluster_y` neighbouring ranges
-        // form a thread-block cluster and add their sums through distributed shared memory -- block r of the cluster adds
-        // columns [r, r + 1) * 2048 / cluster_y of all of them, in rank order -- so that only splits / cluster_y partial
-        // rows per strip reach global memory, few enough for the ticket scheme below to finish in the same kernel.
-        const bool failed = *abort_flag != 0u;
-        if (failed) {
-            for (int i = 0; i < 1000; ++i) __nanosleep(1000);          // copies in flight land before the ring is reused
-        }
-        __syncthreads();
-        float *part = reinterpret_cast<float *>(ring);                  // 2048 sums of this block (the ring is free now)
-        const int t = threadIdx.x;
-        if (t < kStreamRows * 32) {
-            float4 *dst = reinterpret_cast<float4 *>(part + t * 8);
-            dst[0] = failed ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(acc[0], acc[1], acc[2], acc[3]);
-            dst[1] = failed ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(acc[4], acc[5], acc[6], acc[7]);
-        }
-        cluster_arrive_release();
-        cluster_wait_acquire();
-        const uint32_t rank = cluster_rank_of_cta();
-        const int seg = kTsCols / cluster_y;                            // columns this block adds up
-        const int clusters = splits / cluster_y, cluster_id = split / cluster_y;
-        const int col_local = (int)rank * seg + t;
-        const bool mine = t < seg && col_local < width;
-        float sum = 0.f;
-        if (t < seg) {
-            const uint32_t addr = smem_u32(part + col_local);
-            for (int q = 0; q < cluster_y; ++q) sum += ld_dsmem_f32(dsmem_address(addr, (uint32_t)q));
-        }
-        cluster_arrive_release();                                       // this block is done reading its peers
-        if (mine && !failed) {
-            if (clusters == 1) out[(int64_t)b * dim_out + c0 + col_local] = __float2half_rn(sum);
-            else partial[((int64_t)cluster_id * batch + b) * dim_out + c0 + col_local] = sum;
-        }
-        if (clusters > 1 && !failed) {
-            // the block that takes the last ticket of (batch entry, strip, rank) adds the clusters' partial rows in order
-            __threadfence();
-            __syncthreads();
-            uint32_t *ticket = tickets + ((size_t)b * gridDim.x + strip) * cluster_y + rank;
-            if (threadIdx.x == 0) {
-                const uint32_t tk = atomicAdd(ticket, 1u);
-                is_last = (tk == (uint32_t)clusters - 1u);
-                if (is_last) *ticket = 0u;
-            }
-            __syncthreads();
-            if (is_last) {
-                __threadfence();
-                if (mine) {
-                    float total = 0.f;
-                    for (int q = 0; q < clusters; ++q) total += __ldcg(partial + ((int64_t)q * batch + b) * dim_out + c0 + col_local);
-                    out[(int64_t)b * dim_out + c0 + col_local] = __float2half_rn(total);
-                }
-            }
-        }
-        cluster_wait_acquire();                                         // no block leaves while a peer may still read its sums
-        return;
-    }
     if (*abort_flag) {
         for (int i = 0; i < 1000; ++i) __nanosleep(1000);
         return;
@@ -851,63 +794,18 @@ int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in,
             int rps = (int)((dim_in + sp - 1) / sp);
             rps = (rps + kStreamRows - 1) / kStreamRows * kStreamRows;
             const int nsp = (dim_in + rps - 1) / rps;
-            // up to 24 row ranges: the block that takes the last ticket of a strip adds them; more than that (one matrix of
-            // a few thousand columns) and that serial tail would dominate: the ranges then form clusters of eight blocks that
-            // add their sums through distributed shared memory first (a second, wide kernel when clusters cannot be had)
+            // up to 24 row ranges: the block that takes the last ticket of a strip adds them; more than that (one
+            // matrix of a few thousand columns) and that serial tail would dominate, so a second, wide kernel adds them
             {
                 Workspace ws;
                 rc = get_workspace(st, &ws);
                 if (rc) return rc;
-                float *partial = reinterpret_cast<float *>(ws.scratch());
-                constexpr int kCl = 8;
-                const bool many = nsp > 24;
-                static int cluster_ok[64];                                 // 0: not asked, 1: clusters of 8 fit, -1: they do not
-                bool use_cluster = many && !getenv("CPMK_GEMV_NO_CLUSTER") &&
-                                   (size_t)batch * ts_strips * kCl * sizeof(uint32_t) <= Workspace::kTicketBytes;
-                int nsp_c = 0, rps_c = 0;
-                if (use_cluster) {
-                    nsp_c = (int)(sp / kCl) * kCl;
-                    if (nsp_c < kCl) nsp_c = kCl;
-                    rps_c = (int)((dim_in + nsp_c - 1) / nsp_c);
-                    rps_c = (rps_c + kStreamRows - 1) / kStreamRows * kStreamRows;
-                    const int x_c = rps_c <= kTsVecFloats ? 1 : 0;
-                    cudaLaunchConfig_t cfg = {};
-                    cfg.gridDim = dim3(ts_strips, nsp_c, batch);
-                    cfg.blockDim = dim3(kStreamThreads, 1, 1);
-                    cfg.dynamicSmemBytes = kTsRingBytes + (x_c ? rps_c * 4 : 0);
-                    cfg.stream = st;
-                    cudaLaunchAttribute attr[1];
-                    attr[0].id = cudaLaunchAttributeClusterDimension;
-                    attr[0].val.clusterDim.x = 1;
-                    attr[0].val.clusterDim.y = kCl;
-                    attr[0].val.clusterDim.z = 1;
-                    cfg.attrs = attr;
-                    cfg.numAttrs = 1;
-                    {
-                        std::lock_guard<std::mutex> lock(g_static_mutex);
-                        if (cluster_ok[dev] == 0) {
-                            int n_clusters = 0;
-                            const cudaError_t e = cudaOccupancyMaxActiveClusters(&n_clusters, gemv_transpose_stream_kernel, &cfg);
-                            cluster_ok[dev] = (e == cudaSuccess && n_clusters > 0) ? 1 : -1;
-                            (void)cudaGetLastError();
-                        }
-                        use_cluster = cluster_ok[dev] > 0;
-                    }
-                    if (use_cluster) {
-                        const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_transpose_stream_kernel, dim_out, dim_in, (int32_t)rps_c, (int32_t)nsp_c, (int32_t)x_c, (int32_t)kCl,
-                                                                 w, x, y, partial, ws.tickets(), ws.status());
-                        if (e != cudaSuccess) {
-                            set_error("kernel launch failed: %s (%s:%d)", cudaGetErrorString(e), __FILE__, __LINE__);
-                            return CPMK_ECUDA;
-                        }
-                        return CPMK_OK;
-                    }
-                }
                 const dim3 grid(ts_strips, nsp, batch);
-                const bool two_kernels = many;
+                float *partial = reinterpret_cast<float *>(ws.scratch());
+                const bool two_kernels = nsp > 24;
                 // this block's rows of the vector go to shared memory (as fp32) when they fit behind the ring
                 const int x_in_smem = rps <= kTsVecFloats ? 1 : 0;
-                gemv_transpose_stream_kernel<<<grid, kStreamThreads, kTsRingBytes + (x_in_smem ? rps * 4 : 0), st>>>(dim_out, dim_in, rps, nsp, x_in_smem, 1, w, x, y, partial,
+                gemv_transpose_stream_kernel<<<grid, kStreamThreads, kTsRingBytes + (x_in_smem ? rps * 4 : 0), st>>>(dim_out, dim_in, rps, nsp, x_in_smem, w, x, y, partial,
                                                                                          two_kernels ? nullptr : ws.tickets(), ws.status());
                 CPMK_LAUNCH_CHECK();
                 if (two_kernels) {

@@ -92,11 +92,6 @@ __device__ __forceinline__ uint32_t dsmem_address(uint32_t addr, uint32_t rank) 
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
     return out;
 }
-__device__ __forceinline__ float ld_dsmem_f32(uint32_t cluster_addr) {
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
-    return v;
-}
 __device__ __forceinline__ uint16_t ld_dsmem_u16(uint32_t cluster_addr) {
     uint16_t v;
     asm volatile("ld.shared::cluster.u16 %0, [%1];" : "=h"(v) : "r"(cluster_addr) : "memory");
