@@ -410,6 +410,13 @@ def run_ours(args) -> None:
         exchange = ("fused: the GEMM epilogue TMA-stores its output columns into every rank's full-width result over NVLink; activations present "
                     "on every rank; linears on %d streams, scattering GEMM grids leave %d SMs free; one rank barrier per step; results rotate "
                     "through %d buffers, so a step's exchange drains while the next step computes" % (len(lanes), lanes.sm_margin, SLOTS))
+        from cpm_kernels_b200.sharded import recommended_forward_sms
+        forward_sms = int(os.environ["CPMK_GEMM_FORWARD_SMS"]) if "CPMK_GEMM_FORWARD_SMS" in os.environ else recommended_forward_sms(world)
+        cpmk.set_gemm_forward_sms(forward_sms)
+        if forward_sms > 0:
+            exchange = exchange.replace("the GEMM epilogue TMA-stores its output columns into every rank's full-width result over NVLink",
+                                        "the GEMM's computing CTAs store their output columns into this rank's result and %d SMs of the same grid forward "
+                                        "each finished tile into every other rank's result over NVLink" % forward_sms)
         use_multicast = args.exchange == "multicast" and arena.multicast_base != 0
         if use_multicast:
             exchange = exchange.replace("fused: the GEMM epilogue TMA-stores its output columns into every rank's full-width result over NVLink",
