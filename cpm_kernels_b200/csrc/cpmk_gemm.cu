@@ -771,13 +771,16 @@ __device__ __forceinline__ void forward_tiles(const OutMaps &tmap_o, const GemmP
 // STAGES operand stages of 32 KiB and 7 - STAGES output staging tiles per epilogue warp share the same 224 KiB.
 // Five stages and two tiles are used; three and four (half as many proxy fences in the epilogue) measured the same on
 // reductions of a single stage, where the epilogue is all there is.
-template <bool DEQUANT, bool P_MN, bool Q_MN, bool F16, int STAGES>
+// EG: groups of eight epilogue warps.  With two groups (reductions of one or two stages, where the epilogue is all there
+// is) group g drains accumulator g, so the epilogues of two consecutive tiles run side by side; three operand stages and
+// two staging tiles per warp then fill the same shared memory.
+template <bool DEQUANT, bool P_MN, bool Q_MN, bool F16, int STAGES, int EG = 1>
 __device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CUtensorMap &tmap_q, const OutMaps &tmap_o, const GemmParams &prm) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t staging_base = tiles_base + STAGES * kStageBytes2;       // 1024-byte aligned: swizzle atoms
-    constexpr int kOutBufs = 7 - STAGES;                          // staging tiles per epilogue warp
-    const uint32_t bars_base = staging_base + kEpiWarps2 * kOutBufs * kOutStageBytes;
+    constexpr int kOutBufs = (7 - STAGES) / EG;                   // staging tiles per epilogue warp
+    const uint32_t bars_base = staging_base + EG * kEpiWarps2 * kOutBufs * kOutStageBytes;
     const uint32_t full_bar = bars_base;                          // used in the leader only
     const uint32_t empty_bar = bars_base + 8 * STAGES;
     const uint32_t tmem_full_bar = bars_base + 16 * STAGES;
@@ -886,21 +889,23 @@ __device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CU
     } else {
         // ---------------- epilogue (both CTAs; each owns 128 of the tile's 256 rows) ----------------
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;                // which 128 of the tile's 256 columns this warp writes
+        const int group = EG == 1 ? 0 : (warp - 2) >> 3; // which accumulator this warp's group drains (EG == 2)
+        const int half = ((warp - 2) & 7) >> 2;          // which 128 of the tile's 256 columns this warp writes
         constexpr bool kScales = DEQUANT && !F16;
-        uint32_t acc = 0, acc_phase = 0, out_buf = 0;
+        const int tile_step = EG * num_pairs, first_tile = pair + group * num_pairs;
+        uint32_t acc = (uint32_t)group, acc_phase = 0, out_buf = 0;
         auto scales_of = [&](int tile) {
             int b, c_blk, r_blk;
             tile_coords(prm, tile, b, c_blk, r_blk);
             return load_tile_scales(prm, b, r_blk * (2 * kBM) + (int)rank * kBM + quarter * 32 + lane, c_blk * kBN + half * (kBN / 2), lane);
         };
         TileScales ts = {(unsigned short)0, make_uint2(0u, 0u)}, ts_next = ts;
-        if (kScales && prm.tma_store && pair < prm.total_tiles) ts = scales_of(pair);
-        for (int tile = pair; tile < prm.total_tiles; tile += num_pairs) {
+        if (kScales && prm.tma_store && first_tile < prm.total_tiles) ts = scales_of(first_tile);
+        for (int tile = first_tile; tile < prm.total_tiles; tile += tile_step) {
             int b, c_blk, r_blk;
             tile_coords(prm, tile, b, c_blk, r_blk);
             // the next tile's scales travel while this tile is converted
-            if (kScales && prm.tma_store && tile + num_pairs < prm.total_tiles) ts_next = scales_of(tile + num_pairs);
+            if (kScales && prm.tma_store && tile + tile_step < prm.total_tiles) ts_next = scales_of(tile + tile_step);
             if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, prm.status, kErrEpilogueWait)) break;
             tcgen05_fence_after();
             if (F16 || prm.tma_store) {                  // (the fp16 GEMM is only launched with TMA stores)
@@ -920,8 +925,12 @@ __device__ __forceinline__ void tc2_pipeline(const CUtensorMap &tmap_p, const CU
                 __threadfence();
                 atomicAdd(prm.flags + ((size_t)tile * 2 + rank), 1u);
             }
-            acc ^= 1u;
-            if (acc == 0) acc_phase ^= 1u;
+            if (EG == 1) {
+                acc ^= 1u;
+                if (acc == 0) acc_phase ^= 1u;
+            } else {
+                acc_phase ^= 1u;                         // the group keeps its accumulator
+            }
         }
         if (lane == 0) bulk_wait_all();                  // this warp's output stores have completed
     }
@@ -945,6 +954,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads2, 1)
 gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ OutMaps tmap_o, const GemmParams prm) {
     tc2_pipeline<DEQUANT, P_MN, Q_MN, false, kStages2>(tmap_p, tmap_q, tmap_o, prm);
+}
+
+// The same kernel with two groups of epilogue warps (18 warps), for reductions of at most two stages (K <= 256): the
+// attention-score shape, whose time is its epilogue.
+constexpr int kTcThreads2E = (2 + 2 * kEpiWarps2) * 32;
+template <bool P_MN, bool Q_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads2E, 1)
+gemm_i8_tc2e_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
+                    const __grid_constant__ OutMaps tmap_o, const GemmParams prm) {
+    tc2_pipeline<true, P_MN, Q_MN, false, 3, 2>(tmap_p, tmap_q, tmap_o, prm);
 }
 
 // fp16 x fp16 -> fp16 with fp32 accumulation on the same pipeline (the reference's gemm_fp16, kernels/gemm.py:188-256)
@@ -1209,6 +1228,10 @@ int32_t prepare_tc_kernels(int device) {
         CPMK_SET_TC2(false, false, false); CPMK_SET_TC2(false, false, true); CPMK_SET_TC2(false, true, false); CPMK_SET_TC2(false, true, true);
         CPMK_SET_TC2(true, false, false); CPMK_SET_TC2(true, false, true); CPMK_SET_TC2(true, true, false); CPMK_SET_TC2(true, true, true);
 #undef CPMK_SET_TC2
+#define CPMK_SET_TC2E(P, Q) \
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_i8_tc2e_kernel<P, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTc2SmemBytes)
+        CPMK_SET_TC2E(false, false); CPMK_SET_TC2E(false, true); CPMK_SET_TC2E(true, false); CPMK_SET_TC2E(true, true);
+#undef CPMK_SET_TC2E
 #define CPMK_SET_F16(P, Q) \
         if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_f16_tc2_kernel<P, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTc2SmemBytes)
         CPMK_SET_F16(false, false); CPMK_SET_F16(false, true); CPMK_SET_F16(true, false); CPMK_SET_F16(true, true);
@@ -1372,6 +1395,18 @@ int32_t launch_gemm(int32_t m, int32_t k, int32_t n, int32_t batchA, int32_t bat
                 if (scatter && !prm.tma_store) {
                     set_error("scattered output needs a row pitch that is a multiple of 16 bytes and 16-byte aligned destinations");
                     return CPMK_EINVAL;
+                }
+                // short reductions are all epilogue: the form with two groups of epilogue warps (CPMK_GEMM_EPILOGUE_GROUPS=1: off)
+                const char *eg = getenv("CPMK_GEMM_EPILOGUE_GROUPS");
+                if (DEQUANT && prm.tma_store && !scatter && prm.num_kb <= 2 && !(eg && eg[0] == '1')) {
+                    if (!p_mn && !q_mn) gemm_i8_tc2e_kernel<false, false><<<grid, kTcThreads2E, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+                    else if (!p_mn && q_mn) gemm_i8_tc2e_kernel<false, true><<<grid, kTcThreads2E, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+                    else if (p_mn && !q_mn) gemm_i8_tc2e_kernel<true, false><<<grid, kTcThreads2E, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+                    else gemm_i8_tc2e_kernel<true, true><<<grid, kTcThreads2E, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
+                    CPMK_LAUNCH_CHECK();
+                    g_last_path = 1;
+                    g_last_variant = 2;
+                    return CPMK_OK;
                 }
                 if (!p_mn && !q_mn) gemm_i8_tc2_kernel<DEQUANT, false, false><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
                 else if (!p_mn && q_mn) gemm_i8_tc2_kernel<DEQUANT, false, true><<<grid, kTcThreads2, kTc2SmemBytes, stream>>>(tmap_p, tmap_q, tmap_o, prm);
