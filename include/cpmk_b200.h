@@ -271,7 +271,10 @@ int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in,
  * library workspace; nothing is allocated or freed, by this call or by anything it uses.
  *   Limits: dim_out % 8 == 0, mat 16-byte aligned, batch * dim_out <= 524288 and batch * ceil(dim_out / 256) <= 4096;
  *   beyond them the call returns CPMK_ENOMEM with a message and does nothing.
- *   The first call on each device looks up the array's device address; make that call before any stream capture.
+ *   The first call on each device looks up the array's device address, and -- under CUDA's default lazy module loading --
+ *   is also the moment the driver places the part of the library image that holds the array on that device (the one
+ *   allocation-like event in this entry point's life, and not one this code makes): make that call early, before any
+ *   stream capture and before the process's own pool takes the rest of the memory.
  *   All calls on a device share the one array: two calls that overlap on the GPU (different streams) race. */
 int32_t cpmk_gemv_fp16_transpose_noalloc(int32_t batch, int32_t dim_out, int32_t dim_in, const void *mat, const void *vec, void *out,
                                          cpmk_stream_t stream);
