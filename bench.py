@@ -209,6 +209,25 @@ def workload_name() -> str:
 # ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
+def bind_to_gpu_cpus(gpu_index: int):
+    """Run this process on the CPU cores next to its GPU (NVML's CPU affinity of the device, read only), so that the
+    pinned host buffers of the end-to-end leg are allocated on that NUMA node and its copies do not cross sockets.
+    Returns the number of cores bound to, or None when NVML or the cpuset does not allow it (nothing is changed then)."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return len(cpus)
+    except Exception:
+        return None
+
+
 class Run:
     """Process-wide state of one benchmark run: device, ranks, streams, timing helpers."""
 
@@ -221,6 +240,8 @@ class Run:
         self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
         torch.cuda.set_device(self.local_rank)
         self.dev = torch.device("cuda", self.local_rank)
+        self.all_cpus = os.sched_getaffinity(0)
+        self.cpu_affinity = bind_to_gpu_cpus(self.local_rank)
         self.saved_stdout = None
         if self.world > 1:
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -588,6 +609,7 @@ def run_ours(args) -> None:
         if world > 1:
             dist.destroy_process_group()
         return
+    os.sched_setaffinity(0, run.all_cpus)            # the CPU arm uses every core the process may use
     base = cpu_baseline() if (world == 1 and not args.kernels_only) else None
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
@@ -597,6 +619,7 @@ def run_ours(args) -> None:
                    "l2": "per-step working set (fp16 weights 302 MB + activations 134 MB + outputs 252 MB) exceeds the 126 MB L2; no explicit flush",
                    "weights": "re-quantised on every call, as the reference's bmm does"},
         "roofline": roofline, "e2e": e2e, "gpu_launches": 8 * args.steps, "clocks": clocks, "parity": parity,
+        "host": {"cpu_cores_bound_next_to_gpu": run.cpu_affinity},
         "cfg5": cfg5, "sustained": sustained, "reference_cuda": reference_cuda,
         "gemv": gemv, "other_configs": other, "phases": phases, "device_status_word": status,
         "peaks": {k: peaks.get(k) for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained", "source")},
