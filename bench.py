@@ -241,7 +241,8 @@ class Run:
         torch.cuda.set_device(self.local_rank)
         self.dev = torch.device("cuda", self.local_rank)
         self.all_cpus = os.sched_getaffinity(0)
-        self.cpu_affinity = bind_to_gpu_cpus(self.local_rank)
+        # (several ranks only: one rank keeps every core, which its CPU-baseline leg uses)
+        self.cpu_affinity = bind_to_gpu_cpus(self.local_rank) if self.world > 1 else None
         self.saved_stdout = None
         if self.world > 1:
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
