@@ -241,7 +241,7 @@ class Run:
         torch.cuda.set_device(self.local_rank)
         self.dev = torch.device("cuda", self.local_rank)
         self.all_cpus = os.sched_getaffinity(0)
-        # (several ranks only: one rank keeps every core, which its CPU-baseline leg uses)
+        # (several ranks: for the whole run; one rank: only around its end-to-end leg, its CPU-baseline leg uses every core)
         self.cpu_affinity = bind_to_gpu_cpus(self.local_rank) if self.world > 1 else None
         self.saved_stdout = None
         if self.world > 1:
@@ -635,6 +635,21 @@ def run_ours(args) -> None:
 def measure_e2e_single(run: Run, xs, ws, ct) -> dict:
     """One GPU (or the NCCL variant): the public bmm from pinned host activations to pinned host results, three-stage
     pipeline upload(i+1) || compute(i) || download(i-1)."""
+    torch, stream, args = run.torch, run.stream, run.args
+    # one rank: run on the cores next to the GPU while the pinned buffers are allocated (first touch puts them on that
+    # NUMA node) and the steps are issued; every core is given back before the CPU-baseline leg (several ranks are
+    # bound for the whole run)
+    bound_here = run.world == 1 and run.cpu_affinity is None
+    if bound_here:
+        run.cpu_affinity = bind_to_gpu_cpus(run.local_rank)
+    try:
+        return _measure_e2e_single(run, xs, ws, ct)
+    finally:
+        if bound_here:
+            os.sched_setaffinity(0, run.all_cpus)
+
+
+def _measure_e2e_single(run: Run, xs, ws, ct) -> dict:
     torch, stream, args = run.torch, run.stream, run.args
     host_x = [x.cpu().pin_memory() for x in xs]
     host_y = [torch.empty((1, M_TOKENS, w.shape[1]), dtype=torch.half).pin_memory() for w in ws]

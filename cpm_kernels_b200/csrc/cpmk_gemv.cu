@@ -30,6 +30,18 @@ __device__ __forceinline__ float dot8(const uint4 &a, const uint4 &b, float acc)
     return acc;
 }
 
+// the same with the second operand already widened to fp32 (four float2)
+__device__ __forceinline__ float dot8f(const uint4 &a, const float2 *y, float acc) {
+    const __half2 *x = reinterpret_cast<const __half2 *>(&a);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 fx = __half22float2(x[i]);
+        acc = fmaf(fx.x, y[i].x, acc);
+        acc = fmaf(fx.y, y[i].y, acc);
+    }
+    return acc;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -98,6 +110,7 @@ constexpr int kStreamRows = 8;                      // rows per stage = consumer
 constexpr int kStreamThreads = (kStreamRows + 1) * 32;
 constexpr int kStreamRingBytes = 200 * 1024;
 constexpr int kStreamVecBytes = 13 * 1024;           // the vector behind the ring (rows of up to 12.5 KiB)
+constexpr int kXregPieces = 16;                     // 16-byte pieces of the vector per lane in the register-resident form: rows of <= 4096 halves
 constexpr uint32_t kErrGemvProducer = 0x201;
 constexpr uint32_t kErrGemvConsumer = 0x202;
 
@@ -105,7 +118,11 @@ constexpr uint32_t kErrGemvConsumer = 0x202;
 // same chunk of eight consecutive rows, and each warp carries its row's sum across the chunks.
 // PROBE: the same copy pipeline with the arithmetic left out (no vector loads, no sums): how long the matrix takes to
 // arrive through this launch shape; the consumers only fold one word per 16 bytes so that the reads are not elided.
-template <bool SHARED, bool PROBE = false>
+// XREG: ONE matrix (the caller guarantees it) with rows of at most 4096 halves in one chunk: every consumer lane keeps
+// its share of the vector (the 16-byte pieces lane, lane + 32, ... of it, widened to fp32) in 128 registers for the
+// whole kernel, so the consumers read only the matrix out of shared memory (batch 1: 17.7 -> 15.6 us on 10240 x 4096).
+// With per-batch matrices the same form measured slower than the vector in shared memory (batch 4: 70 against 60-66 us).
+template <bool SHARED, bool PROBE = false, bool XREG = false>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int64_t rows_base, int64_t rows_extra, int32_t dim_out, int32_t dim_in, int32_t chunk,
                                                                              int32_t stages, const __half *__restrict__ mat,
                                                                              const __half *__restrict__ vec, __half *__restrict__ out,
@@ -130,6 +147,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int
     const int64_t r0 = bx * rows_base + (bx < rows_extra ? bx : rows_extra), r1 = r0 + rows_base + (bx < rows_extra ? 1 : 0);
     const int groups = (int)((r1 - r0 + kStreamRows - 1) / kStreamRows);
     bool x_in_smem = false;
+    float2 xf[XREG ? 4 * kXregPieces : 1];
 
     // Producer warp.  A single thread issuing eight copies one after another takes over a microsecond per stage
     // (measured), which delays the first stage and barely keeps up afterwards: whole rows of a group are contiguous in
@@ -166,6 +184,17 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int
         }
         __syncwarp();
         for (int t = 0; t < prologue; ++t) issue_copy(t / chunks, t % chunks, (uint32_t)t);
+    } else if (XREG) {
+        const uint4 *srcv = reinterpret_cast<const uint4 *>(vec);
+        const int nv = dim_in >> 3;
+#pragma unroll
+        for (int j = 0; j < kXregPieces; ++j) {
+            const int idx = lane + 32 * j;
+            const uint4 v = idx < nv ? __ldg(srcv + idx) : make_uint4(0u, 0u, 0u, 0u);
+            const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) xf[4 * j + e] = __half22float2(h[e]);
+        }
     } else if (!PROBE && r1 > r0) {
         // When all rows of the block belong to one batch entry (always, for a single matrix) its vector is copied into
         // shared memory once; a block that straddles two entries reads the vectors from global memory as it goes.
@@ -197,7 +226,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int
             const int64_t row = r0 + (int64_t)g * kStreamRows + warp;
             // (one matrix: every row belongs to batch entry 0; otherwise one division per group, overlapped with the copy)
             const int b = (SHARED || rows_base * gridDim.x + rows_extra == dim_out) ? 0 : (int)((row < r1 ? row : r0) / dim_out);
-            float acc0 = 0.f, acc1 = 0.f;
+            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
             for (int c = 0; c < chunks; ++c) {
                 if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kErrGemvConsumer)) { alive = false; break; }
                 if (row < r1) {
@@ -206,7 +235,19 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int
                     const uint4 *w = reinterpret_cast<const uint4 *>(ring + (size_t)stage * stage_bytes + (size_t)warp * slot_bytes);
                     const uint4 *x = x_in_smem ? reinterpret_cast<const uint4 *>(xs + c0) : reinterpret_cast<const uint4 *>(vec + (int64_t)b * dim_in + c0);
                     int i = lane;
-                    if (PROBE) {
+                    if (XREG) {
+                        // four pieces at a time: their shared-memory loads are issued together, four independent sums
+#pragma unroll
+                        for (int j = 0; j < kXregPieces; j += 4) {
+                            uint4 wv[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) wv[u] = lane + 32 * (j + u) < nvec ? w[lane + 32 * (j + u)] : make_uint4(0u, 0u, 0u, 0u);
+                            acc0 = dot8f(wv[0], &xf[4 * j], acc0);
+                            acc1 = dot8f(wv[1], &xf[4 * j + 4], acc1);
+                            acc2 = dot8f(wv[2], &xf[4 * j + 8], acc2);
+                            acc3 = dot8f(wv[3], &xf[4 * j + 12], acc3);
+                        }
+                    } else if (PROBE) {
                         uint32_t fold = 0u;
                         for (; i < nvec; i += 32) {
                             const uint4 w0 = w[i];
@@ -229,7 +270,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int
                 if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
             }
             if (alive && row < r1) {
-                const float v = warp_sum(acc0 + acc1);
+                const float v = warp_sum((acc0 + acc1) + (acc2 + acc3));
                 if (lane == 0 && (!PROBE || v != 0.f)) out[row] = __float2half_rn(v);     // (the probe writes nothing unless a fold hits the magic word)
             }
         }
@@ -661,6 +702,8 @@ int32_t launch_gemv_rows(int32_t batch, int32_t dim_out, int32_t dim_in, const v
         std::call_once(attr_once[dev], [dev] {
             cudaError_t e = cudaFuncSetAttribute(gemv_rows_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes + kStreamVecBytes);
             if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_rows_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes + kStreamVecBytes);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_rows_stream_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes + kStreamVecBytes);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_rows_stream_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes + kStreamVecBytes);
             attr_err[dev] = e;
         });
         if (attr_err[dev] == cudaSuccess) {
@@ -676,8 +719,13 @@ int32_t launch_gemv_rows(int32_t batch, int32_t dim_out, int32_t dim_in, const v
             int stages = (int)(kStreamRingBytes / ((int64_t)chunk * 2 * kStreamRows));
             if (stages > 16) stages = 16;
             const size_t smem = (size_t)stages * chunk * 2 * kStreamRows + (size_t)dim_in * 2;        // ring + the vector
-            gemv_rows_stream_kernel<SHARED><<<info.sm_count, kStreamThreads, smem, stream>>>(total_rows / info.sm_count, total_rows % info.sm_count,
-                                                                                            dim_out, dim_in, chunk, stages, w, x, y, ws.status());
+            // one matrix with rows of at most 4096 halves: the vector lives in the consumers' registers (CPMK_GEMV_NO_XREG=1: in shared memory)
+            if ((SHARED || batch == 1) && dim_in <= 32 * 8 * kXregPieces && !getenv("CPMK_GEMV_NO_XREG"))
+                gemv_rows_stream_kernel<SHARED, false, true><<<info.sm_count, kStreamThreads, smem, stream>>>(total_rows / info.sm_count, total_rows % info.sm_count,
+                                                                                                             dim_out, dim_in, chunk, stages, w, x, y, ws.status());
+            else
+                gemv_rows_stream_kernel<SHARED><<<info.sm_count, kStreamThreads, smem, stream>>>(total_rows / info.sm_count, total_rows % info.sm_count,
+                                                                                                dim_out, dim_in, chunk, stages, w, x, y, ws.status());
             CPMK_LAUNCH_CHECK();
             return CPMK_OK;
         }

@@ -26,6 +26,7 @@ def close(got_fp16, want_f64):
 
 ROWS = [(16, 2222, 128), (1, 10240, 4096), (4, 1024, 4096), (3, 37, 24), (2, 9, 4100), (1, 5, 30), (2, 8, 7),
         (3, 1000, 1032), (2, 2371, 6400),
+        (1, 2371, 1032), (1, 5000, 2056), (1, 2400, 4088), (1, 3000, 3072),   # one matrix, rows <= 4096: the vector lives in registers
         (4, 10240, 4096), (16, 10240, 4096)]                       # configuration 3 with per-batch matrices at full size                          # streaming kernel: ragged row groups, longest rows it takes
 
 
@@ -68,7 +69,8 @@ def test_gemv_fp16_transpose(G, batch, dim_out, dim_in):
     G.assert_no_device_error()
 
 
-@pytest.mark.parametrize("batch,dim_out,dim_in", [(16, 22222, 4444), (1, 10240, 4096), (4, 10240, 4096), (16, 10240, 4096), (5, 33, 64), (3, 7, 10)])
+@pytest.mark.parametrize("batch,dim_out,dim_in", [(16, 22222, 4444), (1, 10240, 4096), (4, 10240, 4096), (16, 10240, 4096), (5, 33, 64), (3, 7, 10),
+                                                  (1, 2999, 2056)])
 def test_gemv_broadcast_mat_fp16(G, batch, dim_out, dim_in):
     ssk = float(dim_in) ** 0.25
     mat = randn_fp16((dim_out, dim_in), 5, 1.0 / ssk)
