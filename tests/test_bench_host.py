@@ -26,7 +26,7 @@ def test_missing_traffic_record_gives_null_not_a_built_in_number(monkeypatch, tm
 
 
 def test_operation_count_of_the_workload():
-    # 2 * M * N * K over the four CPM-Bee-10B linears at M = 4096 (4.12e11 + 1.37e11 + 3.44e11 + 3.44e11)
+    # 2 * M * N * K over the four CPM-Bee-10B linears at M = 4096: 4.12e11 + 1.37e11 + 3.44e11 + 3.44e11
     assert abs(bench.total_ops(4096) - 1.237e12) / 1.237e12 < 1e-3
     assert bench.total_ops(16384) == 4 * bench.total_ops(4096)
 
