@@ -64,6 +64,23 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
+// L2 eviction priorities for bulk copies: lines fetched with evict_last stay in L2 ahead of everything fetched
+// normally (for data a following pass reads again), lines touched with evict_first are the first to go.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void bulk_load_1d_hint(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+}
+
 // 3-d tiled TMA load global -> shared of this CTA; completion bytes on `bar` (a barrier of this CTA).  The innermost
 // coordinate times the element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_tile_3d(uint32_t dst, const void *tensor_map, int32_t c0, int32_t c1, int32_t c2, uint32_t bar) {

@@ -381,6 +381,9 @@ __global__ void __launch_bounds__(kCsThreads, 2) quant_cols_stream_kernel(int32_
         // producer warp, one lane per row segment: a single thread issuing the eight copies of a stage one after another
         // took ~2600 cycles per stage (measured), about as long as the consumers need for it
         uint32_t stage = 0, phase = 0;
+        // the maxima pass asks L2 to keep what it reads, the rounding pass (which reads the same rows again, last first)
+        // releases it
+        const uint64_t policy = PASS == 0 ? l2_policy_evict_last() : l2_policy_evict_first();
         for (int gi = 0; gi < groups; ++gi) {
             const int g = PASS == 0 ? gi : groups - 1 - gi;
             int ok = 1;
@@ -392,8 +395,8 @@ __global__ void __launch_bounds__(kCsThreads, 2) quant_cols_stream_kernel(int32_
             if (lane == 0) mbar_expect_tx(full_bar + 8 * stage, (uint32_t)nr * seg_bytes);
             __syncwarp();
             if (lane < nr)
-                bulk_load_1d(ring_base + stage * kCsStageBytes + (uint32_t)lane * (kCsCols * 2), base + (int64_t)(row + lane) * m, seg_bytes,
-                             full_bar + 8 * stage);
+                bulk_load_1d_hint(ring_base + stage * kCsStageBytes + (uint32_t)lane * (kCsCols * 2), base + (int64_t)(row + lane) * m, seg_bytes,
+                                  full_bar + 8 * stage, policy);
             if (++stage == kCsStages) { stage = 0; phase ^= 1u; }
         }
     } else {
