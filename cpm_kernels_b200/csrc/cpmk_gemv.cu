@@ -8,6 +8,7 @@
 
 #include <mutex>
 
+#include <cuda.h>
 #include "cpmk_common.cuh"
 #include "cpmk_ptx.cuh"
 
@@ -448,6 +449,123 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_transpose_stream_kerne
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Transposed form for ONE matrix without partial sums: a block owns a strip of `width` columns (a multiple of 16, chosen
+// so that the strips just cover the SMs: 80 columns of a 10240-column matrix, 128 strips on 148 SMs) over ALL rows, so nothing
+// has to be added across blocks and no second kernel runs.  The strip's 160-byte row segments are gathered by tiled TMA
+// loads, 128 rows per box, into a ring of up to 16 boxes (one elected thread issues one copy per box); 8 consumer
+// warps: thread t owns 8 columns (t mod width/8) and every (256 / (width/8))-th row, keeps 8 fp32 sums, and the block
+// adds its row lanes through shared memory at the end in a fixed order.  The vector sits in shared memory.
+// ------------------------------------------------------------------------------------------------
+constexpr int kTpRows = 128;                       // rows per box
+constexpr int kTpMaxWidth = 128;                   // columns per strip (box inner extent of at most 256 bytes)
+constexpr int kTpMaxStages = 16;
+constexpr int kTpRedBytes = 256 * 8 * 4;           // one fp32 sum per consumer thread and column
+constexpr uint32_t kErrGemvStripProducer = 0x203;
+constexpr uint32_t kErrGemvStripConsumer = 0x204;
+
+__global__ void __launch_bounds__(kStreamThreads, 1) gemv_transpose_strip_kernel(const __grid_constant__ CUtensorMap tmap, int32_t dim_out, int32_t dim_in,
+                                                                                 int32_t width, int32_t stages, const __half *__restrict__ vec,
+                                                                                 __half *__restrict__ out, uint32_t *status) {
+    extern __shared__ __align__(128) uint8_t ring[];               // stages boxes, then the vector (fp16), then the row lanes' sums
+    __shared__ __align__(8) uint64_t bars[2 * kTpMaxStages];
+    __shared__ uint32_t abort_word;
+    const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + kTpMaxStages);
+    const uint32_t ring_base = smem_u32(ring);
+    volatile uint32_t *abort_flag = &abort_word;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int strip = blockIdx.x, b = blockIdx.y;
+    const int c0 = strip * width;
+    const uint32_t stage_bytes = (uint32_t)(kTpRows * width * 2);
+    const int x_halves = (dim_in + 63) / 64 * 64;                  // keeps what follows 128-byte aligned
+    __half *xs = reinterpret_cast<__half *>(ring + (size_t)stages * stage_bytes);
+    float *red = reinterpret_cast<float *>(xs + x_halves);
+    const int groups = (dim_in + kTpRows - 1) / kTpRows;
+    const int prologue = groups < stages ? groups : stages;
+
+    if (warp == kStreamRows) {
+        if (lane == 0) {
+            for (int s = 0; s < stages; ++s) {
+                mbar_init(full_bar + 8 * s, 1);
+                mbar_init(empty_bar + 8 * s, kStreamRows);
+            }
+            abort_word = 0u;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // rows beyond dim_in and columns beyond dim_out are filled with zeros by the copy and count towards its bytes
+            for (int g = 0; g < prologue; ++g) {
+                mbar_expect_tx(full_bar + 8 * g, stage_bytes);
+                tma_load_tile_3d(ring_base + (uint32_t)g * stage_bytes, &tmap, c0, g * kTpRows, b, full_bar + 8 * g);
+            }
+        }
+    } else {
+        const __half *x = vec + (int64_t)b * dim_in;
+        for (int i = threadIdx.x; i < dim_in; i += kStreamRows * 32) xs[i] = __ldg(x + i);
+    }
+    __syncthreads();
+
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    const int col_groups = width >> 3;
+    const int row_lanes = (kStreamRows * 32) / col_groups;
+    const int t = threadIdx.x;
+    const int rl = t / col_groups, cg = t - rl * col_groups;
+    const bool active = warp < kStreamRows && rl < row_lanes;
+
+    if (warp == kStreamRows) {
+        if (lane == 0) {
+            uint32_t stage = prologue == stages ? 0u : (uint32_t)prologue, phase = prologue == stages ? 1u : 0u;
+            for (int g = prologue; g < groups; ++g) {
+                if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrGemvStripProducer)) break;
+                mbar_expect_tx(full_bar + 8 * stage, stage_bytes);
+                tma_load_tile_3d(ring_base + stage * stage_bytes, &tmap, c0, g * kTpRows, b, full_bar + 8 * stage);
+                if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else {
+        uint32_t stage = 0, phase = 0;
+        for (int g = 0; g < groups; ++g) {
+            if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kErrGemvStripConsumer)) break;
+            if (active) {
+                const uint8_t *src = ring + (size_t)stage * stage_bytes + (size_t)cg * 16;
+                const int row0 = g * kTpRows;
+#pragma unroll 4
+                for (int r = rl; r < kTpRows; r += row_lanes) {
+                    // (rows beyond dim_in hold zeros; the vector is not read there)
+                    const float xv = row0 + r < dim_in ? __half2float(xs[row0 + r]) : 0.f;
+                    const uint4 w = *reinterpret_cast<const uint4 *>(src + (size_t)r * (size_t)(width * 2));
+                    const __half2 *h = reinterpret_cast<const __half2 *>(&w);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __half22float2(h[j]);
+                        acc[2 * j] = fmaf(f.x, xv, acc[2 * j]);
+                        acc[2 * j + 1] = fmaf(f.y, xv, acc[2 * j + 1]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar + 8 * stage);
+            if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);          // let copies in flight land before the ring is released
+        return;
+    }
+    if (active) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) red[rl * width + cg * 8 + j] = acc[j];
+    }
+    __syncthreads();
+    if (t < width && c0 + t < dim_out) {
+        float total = 0.f;
+        for (int r = 0; r < row_lanes; ++r) total += red[r * width + t];
+        out[(int64_t)b * dim_out + c0 + t] = __float2half_rn(total);
+    }
+}
+
 // Any dim_in / alignment: one warp per row, scalar loads.
 __global__ void __launch_bounds__(kBlock) gemv_rows_generic_kernel(int32_t batch, int32_t dim_out, int32_t dim_in, int shared,
                                                                    const __half *__restrict__ mat, const __half *__restrict__ vec,
@@ -829,6 +947,42 @@ int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in,
         gemv_transpose_generic_kernel<<<(unsigned)blocks, kBlock, 0, st>>>(batch, dim_out, dim_in, w, x, y);
         CPMK_LAUNCH_CHECK();
         return CPMK_OK;
+    }
+    // one matrix of a few MB and more whose strips cover the SMs: whole columns per block, no partial sums (CPMK_GEMV_NO_STRIP=1: off)
+    if (batch == 1 && (int64_t)dim_in * dim_out >= (int64_t(1) << 21) && dim_in >= 1024 && dim_in <= 16384 && aligned16(out) && !getenv("CPMK_GEMV_NO_STRIP") &&
+        !getenv("CPMK_GEMV_NO_STREAM")) {
+        // strips of a multiple of 16 columns: row segments that start and end on 32-byte sectors (with multiples of 8 the
+        // segments of neighbouring strips share sectors, and a fifth more bytes crossed L2: 18.6 against 17.3 us)
+        const int width = (int)((dim_out + (int64_t)info.sm_count * 16 - 1) / ((int64_t)info.sm_count * 16)) * 16;
+        const int strips_tp = (dim_out + width - 1) / width;
+        const size_t stage_bytes = (size_t)kTpRows * width * 2;
+        const size_t tail_bytes = (size_t)((dim_in + 63) / 64 * 64) * 2 + kTpRedBytes;
+        int stages = (int)((kStreamRingBytes - tail_bytes) / stage_bytes);
+        if (stages > kTpMaxStages) stages = kTpMaxStages;
+        // worth it when the strips use most of the SMs (at least 3 in 4) and a few boxes fit the ring
+        // (row segments of at least 128 bytes: with 64-byte segments -- 4096 columns on 148 SMs -- the gather measured slower
+        // than the kernels below, 26.9 against 19.1 us on 10240 x 4096)
+        if (width >= 64 && width <= kTpMaxWidth && stages >= 4 && strips_tp * 4 >= info.sm_count * 3 && strips_tp <= info.sm_count && info.max_smem_optin >= kStreamRingBytes + 1024) {
+            static std::once_flag attr_once[64];
+            static cudaError_t attr_err[64];
+            const int dev = info.device & 63;
+            std::call_once(attr_once[dev], [dev] {
+                attr_err[dev] = cudaFuncSetAttribute(gemv_transpose_strip_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes);
+            });
+            CUtensorMap tmap;
+            const uint64_t dims[3] = {(uint64_t)dim_out, (uint64_t)dim_in, 1u};
+            const uint64_t strides[2] = {(uint64_t)dim_out * 2, (uint64_t)dim_in * (uint64_t)dim_out * 2};
+            const uint32_t box[3] = {(uint32_t)width, (uint32_t)kTpRows, 1u};
+            if (attr_err[dev] == cudaSuccess && encode_tiled_3d(&tmap, 2, mat, dims, strides, box, false)) {
+                Workspace ws;
+                rc = get_workspace(st, &ws);
+                if (rc) return rc;
+                gemv_transpose_strip_kernel<<<dim3(strips_tp, 1), kStreamThreads, (size_t)stages * stage_bytes + tail_bytes, st>>>(tmap, dim_out, dim_in, width,
+                                                                                                                                    stages, x, y, ws.status());
+                CPMK_LAUNCH_CHECK();
+                return CPMK_OK;
+            }
+        }
     }
     // matrices of a few MB and more: the streaming kernel, two blocks per SM
     if ((int64_t)dim_in * dim_out >= (int64_t(1) << 21) && dim_in >= 256 && aligned16(out) && info.max_smem_optin >= kTsRingBytes + kTsVecFloats * 4 + 1024 &&

@@ -49,7 +49,8 @@ def test_gemv_fp16(G, batch, dim_out, dim_in):
 COLS = [(16, 128, 2222), (1, 10240, 4096), (1, 4096, 10240), (4, 1024, 4096), (3, 40, 24), (2, 12, 9), (2, 264, 100),
         (4, 4096, 2048), (8, 2056, 1000), (16, 10240, 1024),
         (4, 10240, 4096), (16, 10240, 4096), (4, 4096, 10240),
-        (2, 4096, 8192), (1, 3000, 5000)]                         # many row ranges per strip: clusters of eight blocks add them (batches; ragged strip, empty ranges)      # the last three take the shared-memory streaming kernel
+        (2, 4096, 8192), (1, 3000, 5000),                         # many row ranges per strip (batches; ragged strip, empty ranges)
+        (1, 10008, 3000), (1, 9472, 1024), (1, 18944, 1100), (1, 9480, 16384)]   # one matrix, whole columns per block: ragged last strip and last box, fewer boxes than ring slots, the widest strip, the longest vector
 
 
 @pytest.mark.parametrize("batch,dim_out,dim_in", COLS)
