@@ -119,10 +119,12 @@ constexpr uint32_t kErrGemvConsumer = 0x202;
 // same chunk of eight consecutive rows, and each warp carries its row's sum across the chunks.
 // PROBE: the same copy pipeline with the arithmetic left out (no vector loads, no sums): how long the matrix takes to
 // arrive through this launch shape; the consumers only fold one word per 16 bytes so that the reads are not elided.
-// XREG: ONE matrix (the caller guarantees it) with rows of at most 4096 halves in one chunk: every consumer lane keeps
+// XREG: ONE matrix per block (the caller guarantees it: one matrix, or a grid row per batch entry) with rows of at most 4096 halves in one chunk: every consumer lane keeps
 // its share of the vector (the 16-byte pieces lane, lane + 32, ... of it, widened to fp32) in 128 registers for the
 // whole kernel, so the consumers read only the matrix out of shared memory (batch 1: 17.7 -> 15.6 us on 10240 x 4096).
-// With per-batch matrices the same form measured slower than the vector in shared memory (batch 4: 70 against 60-66 us).
+// With per-batch matrices the launcher gives every batch entry its own row of the grid (sm_count / batch blocks), so that no
+// block's rows belong to two entries (batch 4 on 10240 x 4096: 59.5 -> 53.6 us; letting blocks straddle entries and fall back to
+// global loads of the vector measured 70 us).
 template <bool SHARED, bool PROBE = false, bool XREG = false>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int64_t rows_base, int64_t rows_extra, int32_t dim_out, int32_t dim_in, int32_t chunk,
                                                                              int32_t stages, const __half *__restrict__ mat,
@@ -141,6 +143,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_rows_stream_kernel(int
     volatile uint32_t *abort_flag = &abort_word;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int chunks = (dim_in + chunk - 1) / chunk;
+    // gridDim.y > 1: per-batch matrices with the blocks of row blockIdx.y of the grid sharing out the rows of entry
+    // blockIdx.y, so that no block's rows belong to two entries and each block sees one matrix and one vector
+    mat += (int64_t)blockIdx.y * dim_out * dim_in;
+    vec += (int64_t)blockIdx.y * dim_in;
+    out += (int64_t)blockIdx.y * dim_out;
 
     // this block's rows [r0, r1): total_rows = rows_base * gridDim.x + rows_extra, the first rows_extra blocks take one more
     // (host-computed: a 64-bit division here would sit in front of the first copy)
@@ -847,7 +854,14 @@ int32_t launch_gemv_rows(int32_t batch, int32_t dim_out, int32_t dim_in, const v
             if (stages > 16) stages = 16;
             const size_t smem = (size_t)stages * chunk * 2 * kStreamRows + (size_t)dim_in * 2;        // ring + the vector
             // one matrix with rows of at most 4096 halves: the vector lives in the consumers' registers (CPMK_GEMV_NO_XREG=1: in shared memory)
-            if ((SHARED || batch == 1) && dim_in <= 32 * 8 * kXregPieces && !getenv("CPMK_GEMV_NO_XREG"))
+            const bool xreg = dim_in <= 32 * 8 * kXregPieces && !getenv("CPMK_GEMV_NO_XREG");
+            // per-batch matrices: sm_count / batch blocks per entry (a 2-d grid), each entry's rows shared out among its own
+            // blocks, so that every block works on one matrix with one vector
+            const int per_entry = SHARED ? 0 : info.sm_count / batch;
+            if (xreg && !SHARED && batch > 1 && per_entry >= 4 && dim_out >= per_entry * 16 && !getenv("CPMK_GEMV_NO_ENTRY_GRID"))
+                gemv_rows_stream_kernel<false, false, true><<<dim3(per_entry, batch), kStreamThreads, smem, stream>>>(dim_out / per_entry, dim_out % per_entry, dim_out, dim_in,
+                                                                                                                  chunk, stages, w, x, y, ws.status());
+            else if (xreg && (SHARED || batch == 1))
                 gemv_rows_stream_kernel<SHARED, false, true><<<info.sm_count, kStreamThreads, smem, stream>>>(total_rows / info.sm_count, total_rows % info.sm_count,
                                                                                                              dim_out, dim_in, chunk, stages, w, x, y, ws.status());
             else
