@@ -460,11 +460,12 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_transpose_stream_kerne
 // Transposed form for ONE matrix without partial sums: a block owns a strip of `width` columns (a multiple of 16, chosen
 // so that the strips just cover the SMs: 80 columns of a 10240-column matrix, 128 strips on 148 SMs) over ALL rows, so nothing
 // has to be added across blocks and no second kernel runs.  The strip's 160-byte row segments are gathered by tiled TMA
-// loads, 128 rows per box, into a ring of up to 16 boxes (one elected thread issues one copy per box); 8 consumer
-// warps: thread t owns 8 columns (t mod width/8) and every (256 / (width/8))-th row, keeps 8 fp32 sums, and the block
-// adds its row lanes through shared memory at the end in a fixed order.  The vector sits in shared memory.
+// loads, 256 rows per box (the largest box a tiled copy takes: the fewer copies per byte the better), into a ring of three
+// to sixteen boxes (one elected thread issues one copy per box); 8 consumer warps: thread t owns 8 columns (t mod width/8)
+// and every (256 / (width/8))-th row, keeps 8 fp32 sums, and the block adds its row lanes through shared memory at the
+// end in a fixed order.  The vector sits in shared memory.
 // ------------------------------------------------------------------------------------------------
-constexpr int kTpRows = 128;                       // rows per box
+constexpr int kTpRows = 256;                       // rows per box (the largest extent a tiled copy takes)
 constexpr int kTpMaxWidth = 128;                   // columns per strip (box inner extent of at most 256 bytes)
 constexpr int kTpMaxStages = 16;
 constexpr int kTpRedBytes = 256 * 8 * 4;           // one fp32 sum per consumer thread and column
@@ -472,7 +473,7 @@ constexpr uint32_t kErrGemvStripProducer = 0x203;
 constexpr uint32_t kErrGemvStripConsumer = 0x204;
 
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_transpose_strip_kernel(const __grid_constant__ CUtensorMap tmap, int32_t dim_out, int32_t dim_in,
-                                                                                 int32_t width, int32_t stages, const __half *__restrict__ vec,
+                                                                                 int32_t width, int32_t stages, int32_t box_rows, const __half *__restrict__ vec,
                                                                                  __half *__restrict__ out, uint32_t *status) {
     extern __shared__ __align__(128) uint8_t ring[];               // stages boxes, then the vector (fp16), then the row lanes' sums
     __shared__ __align__(8) uint64_t bars[2 * kTpMaxStages];
@@ -483,11 +484,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_transpose_strip_kernel
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int strip = blockIdx.x, b = blockIdx.y;
     const int c0 = strip * width;
-    const uint32_t stage_bytes = (uint32_t)(kTpRows * width * 2);
+    const uint32_t stage_bytes = (uint32_t)(box_rows * width * 2);
     const int x_halves = (dim_in + 63) / 64 * 64;                  // keeps what follows 128-byte aligned
     __half *xs = reinterpret_cast<__half *>(ring + (size_t)stages * stage_bytes);
     float *red = reinterpret_cast<float *>(xs + x_halves);
-    const int groups = (dim_in + kTpRows - 1) / kTpRows;
+    const int groups = (dim_in + box_rows - 1) / box_rows;
     const int prologue = groups < stages ? groups : stages;
 
     if (warp == kStreamRows) {
@@ -502,7 +503,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_transpose_strip_kernel
             // rows beyond dim_in and columns beyond dim_out are filled with zeros by the copy and count towards its bytes
             for (int g = 0; g < prologue; ++g) {
                 mbar_expect_tx(full_bar + 8 * g, stage_bytes);
-                tma_load_tile_3d(ring_base + (uint32_t)g * stage_bytes, &tmap, c0, g * kTpRows, b, full_bar + 8 * g);
+                tma_load_tile_3d(ring_base + (uint32_t)g * stage_bytes, &tmap, c0, g * box_rows, b, full_bar + 8 * g);
             }
         }
     } else {
@@ -526,7 +527,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_transpose_strip_kernel
             for (int g = prologue; g < groups; ++g) {
                 if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, status, kErrGemvStripProducer)) break;
                 mbar_expect_tx(full_bar + 8 * stage, stage_bytes);
-                tma_load_tile_3d(ring_base + stage * stage_bytes, &tmap, c0, g * kTpRows, b, full_bar + 8 * stage);
+                tma_load_tile_3d(ring_base + stage * stage_bytes, &tmap, c0, g * box_rows, b, full_bar + 8 * stage);
                 if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -536,9 +537,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_transpose_strip_kernel
             if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, status, kErrGemvStripConsumer)) break;
             if (active) {
                 const uint8_t *src = ring + (size_t)stage * stage_bytes + (size_t)cg * 16;
-                const int row0 = g * kTpRows;
+                const int row0 = g * box_rows;
 #pragma unroll 4
-                for (int r = rl; r < kTpRows; r += row_lanes) {
+                for (int r = rl; r < box_rows; r += row_lanes) {
                     // (rows beyond dim_in hold zeros; the vector is not read there)
                     const float xv = row0 + r < dim_in ? __half2float(xs[row0 + r]) : 0.f;
                     const uint4 w = *reinterpret_cast<const uint4 *>(src + (size_t)r * (size_t)(width * 2));
@@ -969,14 +970,17 @@ int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in,
         // segments of neighbouring strips share sectors, and a fifth more bytes crossed L2: 18.6 against 17.3 us)
         const int width = (int)((dim_out + (int64_t)info.sm_count * 16 - 1) / ((int64_t)info.sm_count * 16)) * 16;
         const int strips_tp = (dim_out + width - 1) / width;
-        const size_t stage_bytes = (size_t)kTpRows * width * 2;
+        // boxes of 256 rows (the most a tiled copy takes) when three of them fit the ring, else 128: the larger the box the
+        // fewer copies per byte (10240 x 4096 with 80-column strips: 25.4 us with 64-row boxes, 17.9 with 128, 15.5 with 256)
         const size_t tail_bytes = (size_t)((dim_in + 63) / 64 * 64) * 2 + kTpRedBytes;
+        const int box_rows = (kStreamRingBytes - tail_bytes) / ((size_t)kTpRows * width * 2) < 3 ? kTpRows / 2 : kTpRows;
+        const size_t stage_bytes = (size_t)box_rows * width * 2;
         int stages = (int)((kStreamRingBytes - tail_bytes) / stage_bytes);
         if (stages > kTpMaxStages) stages = kTpMaxStages;
-        // worth it when the strips use most of the SMs (at least 3 in 4) and a few boxes fit the ring
-        // (row segments of at least 128 bytes: with 64-byte segments -- 4096 columns on 148 SMs -- the gather measured slower
-        // than the kernels below, 26.9 against 19.1 us on 10240 x 4096)
-        if (width >= 64 && width <= kTpMaxWidth && stages >= 4 && strips_tp * 4 >= info.sm_count * 3 && strips_tp <= info.sm_count && info.max_smem_optin >= kStreamRingBytes + 1024) {
+        // worth it when the strips use most of the SMs (at least 3 in 4), a few boxes fit the ring and the row segments are at
+        // least 64 bytes
+        if (width >= 32 && width <= kTpMaxWidth && stages >= 3 && strips_tp * 4 >= info.sm_count * 3 && strips_tp <= info.sm_count &&
+            info.max_smem_optin >= kStreamRingBytes + 1024) {
             static std::once_flag attr_once[64];
             static cudaError_t attr_err[64];
             const int dev = info.device & 63;
@@ -986,13 +990,13 @@ int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in,
             CUtensorMap tmap;
             const uint64_t dims[3] = {(uint64_t)dim_out, (uint64_t)dim_in, 1u};
             const uint64_t strides[2] = {(uint64_t)dim_out * 2, (uint64_t)dim_in * (uint64_t)dim_out * 2};
-            const uint32_t box[3] = {(uint32_t)width, (uint32_t)kTpRows, 1u};
+            const uint32_t box[3] = {(uint32_t)width, (uint32_t)box_rows, 1u};
             if (attr_err[dev] == cudaSuccess && encode_tiled_3d(&tmap, 2, mat, dims, strides, box, false)) {
                 Workspace ws;
                 rc = get_workspace(st, &ws);
                 if (rc) return rc;
                 gemv_transpose_strip_kernel<<<dim3(strips_tp, 1), kStreamThreads, (size_t)stages * stage_bytes + tail_bytes, st>>>(tmap, dim_out, dim_in, width,
-                                                                                                                                    stages, x, y, ws.status());
+                                                                                                                                    stages, box_rows, x, y, ws.status());
                 CPMK_LAUNCH_CHECK();
                 return CPMK_OK;
             }
