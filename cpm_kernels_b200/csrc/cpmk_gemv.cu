@@ -466,7 +466,7 @@ __global__ void __launch_bounds__(kStreamThreads, 2) gemv_transpose_stream_kerne
 // end in a fixed order.  The vector sits in shared memory.
 // ------------------------------------------------------------------------------------------------
 constexpr int kTpRows = 256;                       // rows per box (the largest extent a tiled copy takes)
-constexpr int kTpMaxWidth = 128;                   // columns per strip (box inner extent of at most 256 bytes)
+constexpr int kTpMaxWidth = 256;                   // columns per strip (the largest inner extent of a box)
 constexpr int kTpMaxStages = 16;
 constexpr int kTpRedBytes = 256 * 8 * 4;           // one fp32 sum per consumer thread and column
 constexpr uint32_t kErrGemvStripProducer = 0x203;
@@ -963,24 +963,33 @@ int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in,
         CPMK_LAUNCH_CHECK();
         return CPMK_OK;
     }
-    // one matrix of a few MB and more whose strips cover the SMs: whole columns per block, no partial sums (CPMK_GEMV_NO_STRIP=1: off)
-    if (batch == 1 && (int64_t)dim_in * dim_out >= (int64_t(1) << 21) && dim_in >= 1024 && dim_in <= 16384 && aligned16(out) && !getenv("CPMK_GEMV_NO_STRIP") &&
-        !getenv("CPMK_GEMV_NO_STREAM")) {
-        // strips of a multiple of 16 columns: row segments that start and end on 32-byte sectors (with multiples of 8 the
-        // segments of neighbouring strips share sectors, and a fifth more bytes crossed L2: 18.6 against 17.3 us)
-        const int width = (int)((dim_out + (int64_t)info.sm_count * 16 - 1) / ((int64_t)info.sm_count * 16)) * 16;
-        const int strips_tp = (dim_out + width - 1) / width;
-        // boxes of 256 rows (the most a tiled copy takes) when three of them fit the ring, else 128: the larger the box the
-        // fewer copies per byte (10240 x 4096 with 80-column strips: 25.4 us with 64-row boxes, 17.9 with 128, 15.5 with 256)
+    // matrices of a few MB and more: whole columns per block, no partial sums (CPMK_GEMV_NO_STRIP=1: off)
+    if ((int64_t)dim_in * dim_out >= (int64_t(1) << 21) && dim_in >= 1024 && dim_in <= 16384 && aligned16(out) && batch <= 65535 && !getenv("CPMK_GEMV_NO_STRIP") &&
+        !getenv("CPMK_GEMV_NO_STREAM") && info.max_smem_optin >= kStreamRingBytes + 1024) {
+        // Strips of a multiple of 16 columns: row segments that start and end on 32-byte sectors (with multiples of 8 the
+        // segments of neighbouring strips share sectors, and a fifth more bytes crossed L2: 18.6 against 17.3 us).  Among the
+        // widths of 32 to 256 columns, the one whose strips x batch entries fill whole waves of the SMs best (the widest one
+        // within two percent of the best): 80 columns for one 10240-column matrix (128 blocks), 144 for four (288 blocks).
+        // Boxes of 256 rows (the most a tiled copy takes) when three of them fit the ring, else 128: the larger the box the
+        // fewer copies per byte (10240 x 4096 with 80-column strips: 25.4 us with 64-row boxes, 17.9 with 128, 15.5 with 256).
         const size_t tail_bytes = (size_t)((dim_in + 63) / 64 * 64) * 2 + kTpRedBytes;
-        const int box_rows = (kStreamRingBytes - tail_bytes) / ((size_t)kTpRows * width * 2) < 3 ? kTpRows / 2 : kTpRows;
+        int width = 0, box_rows = 0, stages = 0;
+        double best = 0.0;
+        for (int w_try = 32; w_try <= kTpMaxWidth; w_try += 16) {
+            const int rows_try = (kStreamRingBytes - tail_bytes) / ((size_t)kTpRows * w_try * 2) < 3 ? kTpRows / 2 : kTpRows;
+            int stages_try = (int)((kStreamRingBytes - tail_bytes) / ((size_t)rows_try * w_try * 2));
+            if (stages_try > kTpMaxStages) stages_try = kTpMaxStages;
+            if (stages_try < 3) break;
+            const int64_t blocks = (int64_t)((dim_out + w_try - 1) / w_try) * batch;
+            const int64_t waves = (blocks + info.sm_count - 1) / info.sm_count;
+            const double fill = (double)blocks / (double)(waves * info.sm_count);
+            if (fill > best) best = fill;
+            if (fill >= best - 0.02) { width = w_try; box_rows = rows_try; stages = stages_try; }
+        }
+        // (the loop keeps the last width within two percent of the best fill seen SO FAR; a later, better fill replaces it)
         const size_t stage_bytes = (size_t)box_rows * width * 2;
-        int stages = (int)((kStreamRingBytes - tail_bytes) / stage_bytes);
-        if (stages > kTpMaxStages) stages = kTpMaxStages;
-        // worth it when the strips use most of the SMs (at least 3 in 4), a few boxes fit the ring and the row segments are at
-        // least 64 bytes
-        if (width >= 32 && width <= kTpMaxWidth && stages >= 3 && strips_tp * 4 >= info.sm_count * 3 && strips_tp <= info.sm_count &&
-            info.max_smem_optin >= kStreamRingBytes + 1024) {
+        const int strips_tp = width ? (dim_out + width - 1) / width : 0;
+        if (width && best >= 0.75) {
             static std::once_flag attr_once[64];
             static cudaError_t attr_err[64];
             const int dev = info.device & 63;
@@ -988,15 +997,15 @@ int32_t cpmk_gemv_fp16_transpose(int32_t batch, int32_t dim_out, int32_t dim_in,
                 attr_err[dev] = cudaFuncSetAttribute(gemv_transpose_strip_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes);
             });
             CUtensorMap tmap;
-            const uint64_t dims[3] = {(uint64_t)dim_out, (uint64_t)dim_in, 1u};
+            const uint64_t dims[3] = {(uint64_t)dim_out, (uint64_t)dim_in, (uint64_t)batch};
             const uint64_t strides[2] = {(uint64_t)dim_out * 2, (uint64_t)dim_in * (uint64_t)dim_out * 2};
             const uint32_t box[3] = {(uint32_t)width, (uint32_t)box_rows, 1u};
             if (attr_err[dev] == cudaSuccess && encode_tiled_3d(&tmap, 2, mat, dims, strides, box, false)) {
                 Workspace ws;
                 rc = get_workspace(st, &ws);
                 if (rc) return rc;
-                gemv_transpose_strip_kernel<<<dim3(strips_tp, 1), kStreamThreads, (size_t)stages * stage_bytes + tail_bytes, st>>>(tmap, dim_out, dim_in, width,
-                                                                                                                                    stages, box_rows, x, y, ws.status());
+                gemv_transpose_strip_kernel<<<dim3(strips_tp, batch), kStreamThreads, (size_t)stages * stage_bytes + tail_bytes, st>>>(tmap, dim_out, dim_in, width,
+                                                                                                                                        stages, box_rows, x, y, ws.status());
                 CPMK_LAUNCH_CHECK();
                 return CPMK_OK;
             }
